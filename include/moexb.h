@@ -1,0 +1,182 @@
+/* moexb.h - C ABI of the B200 (sm_100a) MoE expert-FFN path.
+ *
+ * The reference engine ("moex") has no plugin or FFI boundary: its expert layer is a set of inline C++ launch wrappers
+ * in src/kernels.cuh that Engine (src/moex.cu) calls on one CUDA stream, plus the CPU expert class in
+ * src/cpu_expert.h and the GGUF block code in src/gguf.h. Each entry point below stands behind one of those functions,
+ * with the same argument order, buffer shapes and ownership rules, and names the function it replaces (file:line in
+ * the reference tree). Differences that a C ABI forces:
+ *   - every function returns an int status (MOEXB_OK = 0, negative = error) instead of exiting; the text of the last
+ *     error on the calling thread is moexb_last_error();
+ *   - the reference's global "zero-point experts" switch g_zp (kernels.cuh:427) is an explicit `fmt` argument;
+ *   - cudaStream_t is passed as void*.
+ * As in the reference, the pointer-level entry points allocate nothing, never synchronise and never read device memory
+ * on the host, so they can be captured in a CUDA graph; all buffers are device pointers owned by the caller unless a
+ * parameter says "host". Geometry is fixed like the reference's constexprs (kernels.cuh:422): hidden H = 2048, expert
+ * intermediate I = 512, quantisation group 64, so one expert holds 3*H*I = 3,145,728 int4 weights.
+ */
+#ifndef MOEXB_H
+#define MOEXB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOEXB_H_DIM 2048
+#define MOEXB_I_DIM 512
+#define MOEXB_GROUP 64
+#define MOEXB_Q_BYTES 1572864u /* packed nibbles of one expert, kernels.cuh:423 */
+
+enum {
+    MOEXB_OK = 0,
+    MOEXB_ERR_ARG = -1,         /* bad argument (null pointer, size out of range, unknown format) */
+    MOEXB_ERR_CUDA = -2,        /* a CUDA runtime call failed; see moexb_last_error() */
+    MOEXB_ERR_UNSUPPORTED = -3, /* valid request that this build does not implement */
+    MOEXB_ERR_NOMEM = -4
+};
+
+/* Expert blob formats. A blob is [gate I x H | up I x H | down H x I] packed int4 (byte k = element 2k in the low
+ * nibble, 2k+1 in the high nibble, rows contiguous along the input dimension), followed by its scale part. */
+enum {
+    MOEXB_FMT_SYM_F32 = 0, /* two's-complement nibbles in [-8,7], one f32 scale per 64: the reference container layout
+                              (kernels.cuh:413-415, EXPERT_BYTES_SYM = 1,769,472) */
+    MOEXB_FMT_SYM_F16 = 1, /* same nibbles, one fp16 scale per 64 (1,671,168 bytes) */
+    MOEXB_FMT_ZP = 2       /* unsigned nibbles, w = d*sc*u + dm*mn with [sc u8, mn i8] per 32 and half2 (d, dm) per 256:
+                              the reference zero-point layout that holds GGUF Q4_K exactly (kernels.cuh:416-421,
+                              EXPERT_BYTES_ZP = 1,818,624) */
+};
+
+/* Activation element types accepted by the layer-level calls. */
+enum { MOEXB_F32 = 0, MOEXB_BF16 = 1 };
+
+/* Work list of the multi-token path, identical to kernels.cuh:688-689. */
+typedef struct { const uint8_t* slot; int start, count; } moexb_pair_item; /* pairs[start, start+count) use this expert */
+typedef struct { int t, p; float w; } moexb_pair;                          /* token row, output row of ypair, routing weight */
+
+const char* moexb_last_error(void);
+int moexb_version(void);
+size_t moexb_expert_bytes(int fmt); /* 0 for an unknown format */
+
+/* ---- router ------------------------------------------------------------------------------------------------------ */
+
+/* y[r][o] = sum_i W[o][i] * x[r][i], fp32 accumulation in a fixed order (lane j of 32 takes elements 128c+4j..4j+3 for
+ * c = 0,1,..; the 32 partial sums are combined by a xor-butterfly 16,8,4,2,1), so that the CPU oracle reproduces the
+ * logits bit for bit and the selected experts cannot differ. Replaces gemv_f16 (kernels.cuh:73-96; call sites
+ * moex.cu:1093, 1414). I must be a multiple of 128. W is F16 as the reference uploads the router (moex.cu:752-758). */
+int moexb_gemv_f16(const void* W, const float* x, float* y, int I, int O, void* stream, int rows);
+/* The same with fp32 weights. */
+int moexb_gemv_f32(const float* W, const float* x, float* y, int I, int O, void* stream, int rows);
+
+/* Softmax over E logits per token, then the K largest (ties -> lower index), in descending order; w = probability,
+ * divided by the sum over the selected K when norm != 0. logits [T][ld] with ld >= E (ld lets the shared-expert gate
+ * logit ride along as column E, as the reference appends it as router row E, moex.cu:876). Replaces router_topk
+ * (kernels.cuh:373-411). E multiple of 32, E <= 1024, K <= 32. */
+int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, float* w, void* stream, int T, int ld);
+
+/* ---- routed experts, one token (decode) ---------------------------------------------------------------------------- */
+
+/* act[k][I] = silu(gate_k x) * (up_k x); out[H] = sum_k w[k] * (down_k act_k), k in rank order. slots: device array of
+ * K blob pointers; nh: optional device count of valid entries (<= K; 0 gives zeros). Replaces experts_forward
+ * (kernels.cuh:597-673). K <= 16. */
+int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
+                          float* out, void* stream, const int* nh);
+
+/* ---- routed experts, T tokens grouped by expert -------------------------------------------------------------------- */
+
+/* For every pair of every item: act[p][I] = silu(gate x_t) * (up x_t), ypair[p][H] = w * (down act[p]).
+ * Replaces pairs_forward / pairs_forward_dev (kernels.cuh:686-778): fp32 SIMT math, any token count per item.
+ * In the _dev form the item count is read on the device (*nitems <= max_items), so a captured graph needs no host value. */
+int moexb_pairs_forward(int fmt, const moexb_pair_item* items, int n_items, const moexb_pair* pairs, const float* X,
+                        float* act, float* ypair, void* stream);
+int moexb_pairs_forward_dev(int fmt, const moexb_pair_item* items, const int* nitems, int max_items,
+                            const moexb_pair* pairs, const float* X, float* act, float* ypair, void* stream);
+
+/* moe[t][d] = sum_{r<K} ypair[t*K+r][d] (rank order) + (ycpu ? ycpu[t][d] : 0). Replaces pairs_reduce_k
+ * (kernels.cuh:744-753). use_cpu: optional device flag, ycpu is added only if *use_cpu != 0. */
+int moexb_pairs_reduce(const float* ypair, const float* ycpu, float* moe, int K, int D, int T, const int* use_cpu,
+                       void* stream);
+/* out[t][d] += sh[t][d] * sigmoid(gl[t*gl_stride]). Replaces gated_add_k / gated_add_rows_k (kernels.cuh:973-977,
+ * 1101-1106). */
+int moexb_gated_add_rows(float* out, const float* sh, const float* gl, int gl_stride, int D, int T, void* stream);
+
+/* Shared expert held as one int4 blob of the routed experts' shape: out[t] += sigmoid(gl[t*gl_stride]) *
+ * down(silu(gate x_t) * up x_t) for t < T. scratch: >= T*(I + H + 3) + 4 floats, 16-byte aligned. Stands behind shared_expert_add
+ * (kernels.cuh:2018-2028) and shared_rows (moex.cu:1674-1682), whose dense int8/int6 weight matrices are replaced by
+ * an expert blob. */
+int moexb_shared_expert_add(int fmt, const uint8_t* blob, const float* gl, int gl_stride, const float* X, int T,
+                            float* out, float* scratch, void* stream);
+
+/* Bucket the T*K (token, rank) pairs by expert id: items in ascending expert id, pairs in token order inside an
+ * expert, p = t*K + rank, as the host loop at moex.cu:1466-1486 and route_export_k (kernels.cuh:1020-1054) do.
+ * slot_table: E blob pointers (null = expert not held here: its pairs are dropped, which is how an expert-parallel
+ * rank sees only its own experts). items: E entries; pairs: T*K entries; nitems: 1 int; counts: E ints of scratch. */
+int moexb_group_pairs(const int* idx, const float* w, int T, int K, int E, const uint8_t* const* slot_table,
+                      moexb_pair_item* items, moexb_pair* pairs, int* nitems, int* counts, void* stream);
+
+/* ---- formats -------------------------------------------------------------------------------------------------------- */
+
+/* Every weight of a blob as fp32, in blob order [gate | up | down] (3*H*I floats): q*scale for the symmetric formats
+ * (ref/qwen36_ref.py:45-59), (d*sc)*u + dm*mn for zero point (gguf.h:332-335). For the bit-exact weight check. */
+int moexb_dequant(int fmt, const uint8_t* blob, float* out, void* stream);
+/* n values (a multiple of 256) of raw GGUF Q4_K super-blocks (144 bytes each) as fp32: y = (d*s_j)*q - dmin*m_j.
+ * Replaces gg_dequant(GG_Q4_K, ...) (gguf.h:98-110). */
+int moexb_q4k_dequant(const uint8_t* blocks, long long n, float* y, void* stream);
+/* One expert from raw Q4_K tensors (gate [I][H], up [I][H], down [H][I], rows of cols/256 super-blocks) to a
+ * MOEXB_FMT_ZP blob, bit-preserving. Replaces gg_q4k_zp / gg_zp_row / the per-expert body of gg_experts
+ * (gguf.h:261-270, 302-330, 666-694). */
+int moexb_q4k_to_zp(const uint8_t* gate, const uint8_t* up, const uint8_t* down, uint8_t* blob, void* stream);
+
+/* ---- synthetic experts (seeded, identical bytes on host and device) ----------------------------------------------- */
+
+typedef struct moexb_ctx moexb_ctx;     /* one per process and device: stream-ordered workspace, synthetic tables */
+typedef struct moexb_layer moexb_layer; /* one MoE layer resident in HBM: E routed experts + 1 shared + router */
+
+/* Fill dst (device) with n consecutive experts e0..e0+n-1 of `layer` in format fmt (blob stride =
+ * moexb_expert_bytes(fmt)); MOEXB_FMT_ZP experts are synthetic Q4_K super-blocks converted as moexb_q4k_to_zp does. */
+int moexb_synth_experts(moexb_ctx* ctx, int fmt, unsigned seed, int layer, int e0, int n, uint8_t* dst, void* stream);
+/* The same bytes for one expert, written to host memory; needs no GPU. */
+int moexb_synth_expert_host(int fmt, unsigned seed, int layer, int expert, uint8_t* dst_host);
+/* Raw Q4_K tensors of one synthetic expert on the host: gate, up (I*H/256*144 bytes each), down (H*I/256*144). */
+int moexb_synth_q4k_host(unsigned seed, int layer, int expert, uint8_t* gate, uint8_t* up, uint8_t* down);
+
+/* ---- resident layers -------------------------------------------------------------------------------------------------- */
+
+/* max_tokens, max_experts (routed experts per layer, a multiple of 32 up to 1024) and top_k (<= 15) bound the
+ * layer-level calls; their workspace (about max_tokens * (top_k + 1) * 10 KB) is allocated here, once. */
+int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moexb_ctx** out);
+int moexb_ctx_destroy(moexb_ctx* ctx);
+
+/* Allocates the image of one layer: n_routed experts (ids 0..n_routed-1) and the shared expert (id n_routed), each a
+ * blob of format fmt, plus the router [n_routed+1][H] (row n_routed = the shared expert's gate vector).
+ * first_local/n_local select the routed experts this process holds (expert parallelism); the others take no memory and
+ * their pairs are dropped by moexb_group_pairs. router_dtype: MOEXB_F32, or 2 for F16 as the reference stores it. */
+int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype,
+                       moexb_layer** out);
+int moexb_layer_destroy(moexb_layer* layer);
+/* Device pointer of expert e's blob (e == n_routed: shared expert); null if not held. */
+uint8_t* moexb_layer_blob(moexb_layer* layer, int e);
+/* Device array of n_routed+1 blob pointers (null = not held), usable as `slot_table`. */
+const uint8_t* const* moexb_layer_slot_table(moexb_layer* layer);
+/* Copies one expert blob (format of the layer, moexb_expert_bytes(fmt) bytes, host memory) into expert e's place; the
+ * role of the reference's slot admission copy (moex.cu:257) with every expert resident. */
+int moexb_layer_upload_expert(moexb_layer* layer, int e, const uint8_t* blob_host);
+/* Copies router weights from the host: W [n_routed+1][H] in the layer's router dtype. */
+int moexb_layer_set_router(moexb_layer* layer, const void* W_host);
+void* moexb_layer_router(moexb_layer* layer);
+/* Fills all held experts with synthetic weights (moexb_synth_experts with this layer's format). */
+int moexb_layer_fill_synth(moexb_layer* layer, unsigned seed, int layer_index, void* stream);
+
+/* One MoE layer for T tokens: router logits -> top-K softmax (renormalised) -> routed experts -> rank-order combine ->
+ * + sigmoid(gate) * shared expert. X [T][H] of x_dtype; out [T][H] f32. The sequence the reference runs at
+ * moex.cu:1093-1107 (decode) and moex.cu:1414-1415, 1466-1617 (chunk). Optional outputs (may be null): idx_out [T][K],
+ * w_out [T][K]. flags bit 0: skip the shared expert; bit 1: X is the layer input before RMSNorm, so normalise it first
+ * (unit weight, eps 1e-6) and write out = X + moe(norm(X)) - the residual block the 40-layer stack chains. */
+int moexb_layer_forward(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x_dtype, int T, int K, float* out,
+                        int* idx_out, float* w_out, int flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

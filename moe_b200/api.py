@@ -1,0 +1,196 @@
+"""Host-side mirror of the reference's expert-layer entry points (src/kernels.cuh of the reference) on torch tensors.
+
+Every function forwards to the C ABI with raw device pointers on torch's current stream; argument names and order
+follow the reference functions named in include/moexb.h. Nothing here computes: without the CUDA library these raise.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import EH, EI, F32, BF16, F16, check, lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        assert t.is_cuda and t.is_contiguous(), "device-resident contiguous tensor expected"
+        return t.data_ptr()
+    return int(t)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def expert_bytes(fmt):
+    return lib().moexb_expert_bytes(fmt)
+
+
+def gemv_f16(W, x, y=None, rows=1):
+    """y[r] = W . x[r]; W [O][I] float16 (reference gemv_f16, kernels.cuh:93)."""
+    O, I = W.shape
+    y = torch.empty(rows, O, device=x.device, dtype=torch.float32) if y is None else y
+    check(lib().moexb_gemv_f16(_ptr(W), _ptr(x), _ptr(y), I, O, _stream(), rows))
+    return y
+
+
+def gemv_f32(W, x, y=None, rows=1):
+    O, I = W.shape
+    y = torch.empty(rows, O, device=x.device, dtype=torch.float32) if y is None else y
+    check(lib().moexb_gemv_f32(_ptr(W), _ptr(x), _ptr(y), I, O, _stream(), rows))
+    return y
+
+
+def router_topk(logits, E, K, norm=True, T=1, ld=None):
+    """(idx [T][K] int32, w [T][K] f32) (reference router_topk, kernels.cuh:409)."""
+    ld = E if ld is None else ld
+    idx = torch.empty(T, K, device=logits.device, dtype=torch.int32)
+    w = torch.empty(T, K, device=logits.device, dtype=torch.float32)
+    check(lib().moexb_router_topk(_ptr(logits), E, K, int(norm), _ptr(idx), _ptr(w), _stream(), T, ld))
+    return idx, w
+
+
+def experts_forward(fmt, slots, w, K, x, act=None, out=None, nh=None):
+    """One token through K experts (reference experts_forward, kernels.cuh:662). slots: int64 tensor of blob pointers."""
+    act = torch.empty(K * EI, device=x.device, dtype=torch.float32) if act is None else act
+    out = torch.empty(EH, device=x.device, dtype=torch.float32) if out is None else out
+    check(lib().moexb_experts_forward(fmt, _ptr(slots), _ptr(w), K, _ptr(x), _ptr(act), _ptr(out), _stream(), _ptr(nh)))
+    return out
+
+
+def pairs_forward(fmt, items, n_items, pairs, X, act, ypair):
+    """reference pairs_forward (kernels.cuh:767). items / pairs: uint8 tensors holding PairItem / Pair records."""
+    check(lib().moexb_pairs_forward(fmt, _ptr(items), n_items, _ptr(pairs), _ptr(X), _ptr(act), _ptr(ypair), _stream()))
+    return ypair
+
+
+def pairs_forward_dev(fmt, items, nitems, max_items, pairs, X, act, ypair):
+    check(lib().moexb_pairs_forward_dev(fmt, _ptr(items), _ptr(nitems), max_items, _ptr(pairs), _ptr(X), _ptr(act),
+                                        _ptr(ypair), _stream()))
+    return ypair
+
+
+def pairs_reduce(ypair, ycpu, moe, K, D, T, use_cpu=None):
+    check(lib().moexb_pairs_reduce(_ptr(ypair), _ptr(ycpu), _ptr(moe), K, D, T, _ptr(use_cpu), _stream()))
+    return moe
+
+
+def gated_add_rows(out, sh, gl, gl_stride, D, T):
+    check(lib().moexb_gated_add_rows(_ptr(out), _ptr(sh), _ptr(gl), gl_stride, D, T, _stream()))
+    return out
+
+
+def shared_expert_add(fmt, blob, gl, gl_stride, X, T, out, scratch=None):
+    if scratch is None:
+        scratch = torch.empty(T * (EI + EH + 3) + 4, device=X.device, dtype=torch.float32)
+    check(lib().moexb_shared_expert_add(fmt, _ptr(blob), _ptr(gl), gl_stride, _ptr(X), T, _ptr(out), _ptr(scratch), _stream()))
+    return out
+
+
+def group_pairs(idx, w, T, K, E, slot_table):
+    """Device pair grouping; returns (items uint8 [E*16], pairs uint8 [T*K*12], nitems int32 [1])."""
+    dev = idx.device
+    items = torch.zeros(E * C.sizeof(_lib.PairItem), device=dev, dtype=torch.uint8)
+    pairs = torch.zeros(T * K * C.sizeof(_lib.Pair), device=dev, dtype=torch.uint8)
+    nitems = torch.zeros(1, device=dev, dtype=torch.int32)
+    counts = torch.zeros(E, device=dev, dtype=torch.int32)
+    check(lib().moexb_group_pairs(_ptr(idx), _ptr(w), T, K, E, _ptr(slot_table), _ptr(items), _ptr(pairs), _ptr(nitems),
+                                  _ptr(counts), _stream()))
+    return items, pairs, nitems
+
+
+def dequant(fmt, blob):
+    out = torch.empty(3 * EH * EI, device=blob.device, dtype=torch.float32)
+    check(lib().moexb_dequant(fmt, _ptr(blob), _ptr(out), _stream()))
+    return out
+
+
+def q4k_dequant(blocks, n):
+    y = torch.empty(n, device=blocks.device, dtype=torch.float32)
+    check(lib().moexb_q4k_dequant(_ptr(blocks), n, _ptr(y), _stream()))
+    return y
+
+
+def q4k_to_zp(gate, up, down):
+    blob = torch.empty(expert_bytes(_lib.FMT_ZP), device=gate.device, dtype=torch.uint8)
+    check(lib().moexb_q4k_to_zp(_ptr(gate), _ptr(up), _ptr(down), _ptr(blob), _stream()))
+    return blob
+
+
+def synth_expert_host(fmt, seed, layer, expert):
+    """The synthetic expert (layer, expert) as a numpy uint8 blob; runs on the CPU."""
+    out = np.empty(expert_bytes(fmt), dtype=np.uint8)
+    check(lib().moexb_synth_expert_host(fmt, seed, layer, expert, out.ctypes.data))
+    return out
+
+
+def synth_q4k_host(seed, layer, expert):
+    nb = EH * EI // 256 * 144
+    g, u, d = (np.empty(nb, dtype=np.uint8) for _ in range(3))
+    check(lib().moexb_synth_q4k_host(seed, layer, expert, g.ctypes.data, u.ctypes.data, d.ctypes.data))
+    return g, u, d
+
+
+class Context:
+    """moexb_ctx: workspace of the layer-level calls on one device."""
+
+    def __init__(self, device=0, max_tokens=64, max_experts=256, top_k=8):
+        h = C.c_void_p()
+        check(lib().moexb_ctx_create(device, max_tokens, max_experts, top_k, C.byref(h)))
+        self.h, self.device, self.max_tokens, self.top_k = h, device, max_tokens, top_k
+
+    def synth_experts(self, fmt, seed, layer, e0, n, dst):
+        check(lib().moexb_synth_experts(self.h, fmt, seed, layer, e0, n, _ptr(dst), _stream()))
+
+    def close(self):
+        if self.h:
+            lib().moexb_ctx_destroy(self.h)
+            self.h = None
+
+
+class Layer:
+    """moexb_layer: one MoE layer resident in HBM (routed experts [first_local, first_local+n_local), shared expert,
+    router with the shared gate vector as its last row)."""
+
+    def __init__(self, ctx, fmt, n_routed=256, first_local=0, n_local=None, router_dtype=F32):
+        n_local = n_routed - first_local if n_local is None else n_local
+        h = C.c_void_p()
+        check(lib().moexb_layer_create(ctx.h, fmt, n_routed, first_local, n_local, router_dtype, C.byref(h)))
+        self.h, self.ctx, self.fmt, self.n_routed, self.router_dtype = h, ctx, fmt, n_routed, router_dtype
+        self.first_local, self.n_local = first_local, n_local
+
+    def blob_ptr(self, e):
+        return lib().moexb_layer_blob(self.h, e)
+
+    def slot_table(self):
+        return lib().moexb_layer_slot_table(self.h)
+
+    def set_router(self, W):
+        """W: numpy [n_routed+1][H], float32 or float16 matching router_dtype."""
+        W = np.ascontiguousarray(W, dtype=np.float32 if self.router_dtype == F32 else np.float16)
+        assert W.shape == (self.n_routed + 1, EH)
+        check(lib().moexb_layer_set_router(self.h, W.ctypes.data))
+
+    def fill_synth(self, seed, layer_index):
+        check(lib().moexb_layer_fill_synth(self.h, seed, layer_index, _stream()))
+
+    def upload_blob(self, e, blob):
+        """Copy a host blob (numpy uint8 of expert_bytes(fmt)) into expert e's place."""
+        blob = np.ascontiguousarray(blob, dtype=np.uint8)
+        assert blob.size == expert_bytes(self.fmt)
+        check(lib().moexb_layer_upload_expert(self.h, e, blob.ctypes.data))
+
+    def forward(self, X, T, K=8, out=None, idx=None, w=None, flags=0):
+        """moexb_layer_forward. X: [T][H] float32 or bfloat16 device tensor."""
+        x_dtype = BF16 if X.dtype == torch.bfloat16 else F32
+        out = torch.empty(T, EH, device=X.device, dtype=torch.float32) if out is None else out
+        check(lib().moexb_layer_forward(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), flags, _stream()))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().moexb_layer_destroy(self.h)
+            self.h = None

@@ -1,0 +1,94 @@
+// Shared device helpers of the expert-FFN kernels: geometry, blob accessors, nibble unpacking, warp reductions.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "moexb.h"
+
+namespace moexb {
+
+// Geometry of one expert, fixed like the reference's constexprs (kernels.cuh:422-426).
+constexpr int EH = 2048;                                  // hidden size: inputs of gate/up, outputs of down
+constexpr int EI = 512;                                   // expert intermediate size
+constexpr int EGS = 64;                                   // weights per scale group
+constexpr size_t Q_BYTES = (size_t)3 * EH * EI / 2;       // 1,572,864 bytes of packed nibbles
+constexpr size_t CHUNKS = (size_t)3 * EH * EI / 32;       // 98,304 chunks of 32 weights (one 16-byte load each)
+constexpr size_t DOWN_Q_OFF = (size_t)2 * EI * (EH / 2);  // byte offset of the down matrix in the nibble area
+constexpr size_t DOWN_C_OFF = (size_t)2 * EI * (EH / 32); // first chunk of the down matrix
+
+enum : int { FMT_SYM_F32 = 0, FMT_SYM_F16 = 1, FMT_ZP = 2 };
+
+__host__ __device__ constexpr size_t expert_bytes(int fmt) {
+    return fmt == FMT_SYM_F32 ? Q_BYTES + CHUNKS / 2 * 4 : fmt == FMT_SYM_F16 ? Q_BYTES + CHUNKS / 2 * 2
+         : fmt == FMT_ZP ? Q_BYTES + CHUNKS * 2 + CHUNKS / 8 * 4 : 0;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Streaming 16-byte load: expert weights are read once per step, so they should not displace the activations and
+// router weights that stay hot in L1/L2.
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// (scale, zero) of 32-weight chunk g32 of a blob: symmetric formats (s, 0) with s shared by chunks 2g, 2g+1;
+// zero point (d*sc, dm*mn) with [sc u8, mn i8] per chunk and half2 (d, dm) per 8 chunks (kernels.cuh:416-421).
+template <int FMT>
+__device__ __forceinline__ float2 chunk_scale(const uint8_t* __restrict__ blob, size_t g32) {
+    const uint8_t* sp = blob + Q_BYTES;
+    if constexpr (FMT == FMT_SYM_F32) return make_float2(__ldg(reinterpret_cast<const float*>(sp) + (g32 >> 1)), 0.f);
+    else if constexpr (FMT == FMT_SYM_F16) return make_float2(__half2float(__ldg(reinterpret_cast<const __half*>(sp) + (g32 >> 1))), 0.f);
+    else {
+        const uchar2 cm = __ldg(reinterpret_cast<const uchar2*>(sp) + g32);
+        const float2 dd = __half22float2(__ldg(reinterpret_cast<const __half2*>(sp + CHUNKS * 2) + (g32 >> 3)));
+        return make_float2(dd.x * (float)cm.x, dd.y * (float)(int8_t)cm.y);
+    }
+}
+
+// Nibble n (0..7) of word q as an exact float: the integer is or-ed into the mantissa of 2^23 and 2^23 (+8 for the
+// two's-complement formats, whose nibbles were xor-ed with 8 beforehand) is subtracted again. No int->float converts.
+template <bool SIGNED>
+__device__ __forceinline__ float nib(uint32_t q, int n) {
+    return __uint_as_float(0x4B000000u | ((q >> (4 * n)) & 0xFu)) - (SIGNED ? 8388616.f : 8388608.f);
+}
+
+// Activations in shared memory are read 32 consecutive floats per lane (the 32 inputs of one 16-byte weight load);
+// 4 floats of padding after every 32 rotate the lanes over the banks, so the float4 reads do not conflict.
+__host__ __device__ constexpr int pad32(int i) { return i + (i >> 5) * 4; }
+__host__ __device__ constexpr int pad32_size(int n) { return n + n / 8; }
+
+// 32 weights of one 16-byte load times 32 consecutive inputs at x (16-byte aligned; padded shared or global memory),
+// fp32 fused multiply-adds, scaled: s * sum(q x) for the symmetric formats, s * sum(u x) + m * sum(x) for zero point.
+template <int FMT>
+__device__ __forceinline__ float dot32(uint4 q, const float* __restrict__ x, float2 sm) {
+    constexpr bool Z = FMT == FMT_ZP;
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float acc = 0.f, sx = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (!Z) w[j] ^= 0x88888888u;
+        const float4 a = *reinterpret_cast<const float4*>(x + 8 * j), b = *reinterpret_cast<const float4*>(x + 8 * j + 4);
+        const float xs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int n = 0; n < 8; n++) {
+            acc = fmaf(nib<!Z>(w[j], n), xs[n], acc);
+            if (Z) sx += xs[n];
+        }
+    }
+    return Z ? fmaf(sm.x, acc, sm.y * sx) : acc * sm.x;
+}
+
+}  // namespace moexb

@@ -1,0 +1,481 @@
+// C ABI of the B200 expert-FFN path (declared in include/moexb.h): argument checks, launches, resident layers.
+#include "moexb.h"
+#include "common.cuh"
+#include "router.cuh"
+#include "experts_simt.cuh"
+#include "formats.cuh"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+using namespace moexb;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define REQUIRE(cond, ...) do { if (!(cond)) return fail(MOEXB_ERR_ARG, __VA_ARGS__); } while (0)
+#define CUDA_TRY(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) return fail(MOEXB_ERR_CUDA, "%s: %s", #x, cudaGetErrorString(e_)); } while (0)
+#define LAUNCHED(name) do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return fail(MOEXB_ERR_CUDA, "launch of %s: %s", name, cudaGetErrorString(e_)); } while (0)
+
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool fmt_ok(int fmt) { return fmt == FMT_SYM_F32 || fmt == FMT_SYM_F16 || fmt == FMT_ZP; }
+
+// Calls f.template operator()<FMT>() for the run-time format.
+template <class F>
+int by_fmt(int fmt, F&& f) {
+    switch (fmt) {
+        case FMT_SYM_F32: return f.template operator()<FMT_SYM_F32>();
+        case FMT_SYM_F16: return f.template operator()<FMT_SYM_F16>();
+        case FMT_ZP: return f.template operator()<FMT_ZP>();
+    }
+    return fail(MOEXB_ERR_ARG, "unknown expert format %d", fmt);
+}
+
+// ---- half-normal quantile tables of the synthetic generator ---------------------------------------------------------
+
+float half_to_float_host(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// table[i] = fp16 bits of sigma * q, q = the (i + 0.5) / N quantile of |N(0, 1)|, found by bisection on erf.
+void build_table(double sigma, uint16_t* table) {
+    for (int i = 0; i < SYNTH_TABLE_N; i++) {
+        const double p = (i + 0.5) / SYNTH_TABLE_N;
+        double lo = 0, hi = 10;
+        for (int it = 0; it < 80; it++) {
+            const double mid = 0.5 * (lo + hi);
+            if (std::erf(mid / std::sqrt(2.0)) < p) lo = mid; else hi = mid;
+        }
+        table[i] = __half_as_ushort(__float2half_rn((float)(sigma * 0.5 * (lo + hi))));
+    }
+}
+struct Tables { uint16_t s[SYNTH_TABLE_N], d[SYNTH_TABLE_N]; };
+const Tables& host_tables() {
+    static Tables t;
+    static std::once_flag once;
+    std::call_once(once, [] { build_table(0.02, t.s); build_table(0.01, t.d); });
+    return t;
+}
+
+}  // namespace
+
+struct moexb_ctx {
+    int device = 0, max_tokens = 0, max_experts = 0, top_k = 0;
+    uint16_t *table_s = nullptr, *table_d = nullptr;  // device copies of the synthetic tables
+    // workspace of the layer-level calls
+    float *xf = nullptr, *xn = nullptr, *logits = nullptr, *w = nullptr, *act = nullptr, *ypair = nullptr, *moe = nullptr;
+    int *idx = nullptr, *counts = nullptr, *nitems = nullptr;
+    moexb_pair_item* items = nullptr;
+    moexb_pair* pairs = nullptr;
+    const uint8_t** slots = nullptr;  // decode: K+1 blob pointers
+    float* wts = nullptr;             // decode: K+1 weights
+    std::vector<void*> owned;
+};
+
+struct moexb_layer {
+    moexb_ctx* ctx = nullptr;
+    int fmt = 0, n_routed = 0, first_local = 0, n_local = 0, router_dtype = 0;
+    uint8_t* image = nullptr;               // n_local + 1 blobs: the held routed experts, then the shared expert
+    void* router = nullptr;                 // [n_routed + 1][H]
+    const uint8_t** slot_table = nullptr;   // device, n_routed + 1 pointers
+    std::vector<const uint8_t*> slot_host;
+};
+
+extern "C" {
+
+const char* moexb_last_error(void) { return g_err; }
+int moexb_version(void) { return 1; }
+size_t moexb_expert_bytes(int fmt) { return fmt_ok(fmt) ? expert_bytes(fmt) : 0; }
+
+// ---- router ------------------------------------------------------------------------------------------------------
+
+}  // extern "C"
+template <typename WT>
+static int gemv_any(const WT* W, const float* x, float* y, int I, int O, void* stream, int rows) {
+    REQUIRE(W && x && y, "gemv: null pointer");
+    REQUIRE(I > 0 && I % 128 == 0 && O > 0 && rows > 0, "gemv: I=%d must be a positive multiple of 128, O=%d, rows=%d", I, O, rows);
+    if (rows >= 16) {
+        constexpr int WARPS = 4, TO = 4, TR = 8;
+        gemm_rows_k<WT, WARPS, TO, TR><<<dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, 0, S(stream)>>>(W, x, y, I, O, rows);
+    } else {
+        constexpr int WARPS = 8;
+        gemv_rows_k<WT, WARPS><<<dim3((O + WARPS - 1) / WARPS, rows), WARPS * 32, 0, S(stream)>>>(W, x, y, I, O);
+    }
+    LAUNCHED("gemv");
+    return MOEXB_OK;
+}
+extern "C" {
+int moexb_gemv_f16(const void* W, const float* x, float* y, int I, int O, void* stream, int rows) {
+    return gemv_any(static_cast<const __half*>(W), x, y, I, O, stream, rows);
+}
+int moexb_gemv_f32(const float* W, const float* x, float* y, int I, int O, void* stream, int rows) {
+    return gemv_any(W, x, y, I, O, stream, rows);
+}
+
+static int topk_launch(const float* logits, int E, int K, int norm, int* idx, float* w, void* stream, int T, int ld,
+                       const uint8_t* const* slot_table, const uint8_t** slots_out, float* wts_out) {
+    REQUIRE(logits && idx && w, "router_topk: null pointer");
+    REQUIRE(E > 0 && E % 32 == 0 && E <= 1024, "router_topk: E=%d must be a multiple of 32 up to 1024", E);
+    REQUIRE(K > 0 && K < 32 && K <= E, "router_topk: K=%d out of range", K);
+    REQUIRE(T > 0 && ld >= E, "router_topk: T=%d, ld=%d", T, ld);
+    constexpr int WARPS = 4;
+    router_topk_k<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out);
+    LAUNCHED("router_topk");
+    return MOEXB_OK;
+}
+int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, float* w, void* stream, int T, int ld) {
+    return topk_launch(logits, E, K, norm, idx, w, stream, T, ld, nullptr, nullptr, nullptr);
+}
+
+// ---- routed experts ------------------------------------------------------------------------------------------------
+
+int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
+                          float* out, void* stream, const int* nh) {
+    REQUIRE(slots && w && x && act && out, "experts_forward: null pointer");
+    REQUIRE(K > 0 && K <= 16, "experts_forward: K=%d out of range 1..16", K);
+    return by_fmt(fmt, [&]<int FMT>() {
+        constexpr int WARPS = 8;
+        decode_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, K), WARPS * 32, 0, S(stream)>>>(slots, K, nh, x, act);
+        LAUNCHED("decode_gate_up");
+        decode_down_k<FMT, WARPS, 16><<<EH / WARPS, WARPS * 32, K * pad32_size(EI) * sizeof(float), S(stream)>>>(slots, w, K, nh, act, out);
+        LAUNCHED("decode_down");
+        return (int)MOEXB_OK;
+    });
+}
+
+static int pairs_launch(int fmt, const moexb_pair_item* items, const int* nitems, int grid_items, const moexb_pair* pairs,
+                        const float* X, float* act, float* ypair, void* stream) {
+    REQUIRE(items && pairs && X && act && ypair, "pairs_forward: null pointer");
+    REQUIRE(grid_items > 0 && grid_items <= 65535, "pairs_forward: %d items", grid_items);
+    return by_fmt(fmt, [&]<int FMT>() {
+        constexpr int WARPS = 8;
+        pairs_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, grid_items), WARPS * 32, 0, S(stream)>>>(items, pairs, X, act, nitems);
+        LAUNCHED("pairs_gate_up");
+        pairs_down_k<FMT, WARPS><<<dim3(EH / WARPS, grid_items), WARPS * 32, 0, S(stream)>>>(items, pairs, act, ypair, nitems);
+        LAUNCHED("pairs_down");
+        return (int)MOEXB_OK;
+    });
+}
+int moexb_pairs_forward(int fmt, const moexb_pair_item* items, int n_items, const moexb_pair* pairs, const float* X,
+                        float* act, float* ypair, void* stream) {
+    if (n_items == 0) return fmt_ok(fmt) ? MOEXB_OK : fail(MOEXB_ERR_ARG, "unknown expert format %d", fmt);
+    return pairs_launch(fmt, items, nullptr, n_items, pairs, X, act, ypair, stream);
+}
+int moexb_pairs_forward_dev(int fmt, const moexb_pair_item* items, const int* nitems, int max_items,
+                            const moexb_pair* pairs, const float* X, float* act, float* ypair, void* stream) {
+    REQUIRE(nitems, "pairs_forward_dev: null item count");
+    return pairs_launch(fmt, items, nitems, max_items, pairs, X, act, ypair, stream);
+}
+
+int moexb_pairs_reduce(const float* ypair, const float* ycpu, float* moe, int K, int D, int T, const int* use_cpu, void* stream) {
+    REQUIRE(ypair && moe, "pairs_reduce: null pointer");
+    REQUIRE(K > 0 && D > 0 && D % 4 == 0 && T > 0 && T <= 65535, "pairs_reduce: K=%d D=%d T=%d", K, D, T);
+    pairs_reduce_k<<<dim3((D / 4 + 255) / 256, T), 256, 0, S(stream)>>>(ypair, ycpu, moe, K, D, use_cpu);
+    LAUNCHED("pairs_reduce");
+    return MOEXB_OK;
+}
+
+int moexb_gated_add_rows(float* out, const float* sh, const float* gl, int gl_stride, int D, int T, void* stream) {
+    REQUIRE(out && sh && gl, "gated_add_rows: null pointer");
+    REQUIRE(D > 0 && T > 0 && T <= 65535 && gl_stride >= 0, "gated_add_rows: D=%d T=%d", D, T);
+    gated_add_rows_k<<<dim3((D + 255) / 256, T), 256, 0, S(stream)>>>(out, sh, gl, gl_stride, D);
+    LAUNCHED("gated_add_rows");
+    return MOEXB_OK;
+}
+
+int moexb_group_pairs(const int* idx, const float* w, int T, int K, int E, const uint8_t* const* slot_table,
+                      moexb_pair_item* items, moexb_pair* pairs, int* nitems, int* counts, void* stream) {
+    REQUIRE(idx && w && slot_table && items && pairs && nitems && counts, "group_pairs: null pointer");
+    REQUIRE(T > 0 && K > 0 && E > 0 && E <= 1024, "group_pairs: T=%d K=%d E=%d", T, K, E);
+    constexpr int WARPS = 8;
+    group_count_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(idx, T * K, E, counts);
+    LAUNCHED("group_count");
+    group_scatter_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(idx, w, T, K, E, slot_table, counts, items, pairs, nitems, nullptr, 0);
+    LAUNCHED("group_scatter");
+    return MOEXB_OK;
+}
+
+int moexb_shared_expert_add(int fmt, const uint8_t* blob, const float* gl, int gl_stride, const float* X, int T,
+                            float* out, float* scratch, void* stream) {
+    REQUIRE(blob && gl && X && out && scratch, "shared_expert_add: null pointer");
+    REQUIRE(T > 0 && T <= 65535, "shared_expert_add: T=%d", T);
+    // The shared expert is one item holding every token with weight 1; the gate enters in gated_add_rows.
+    // scratch: act [T][I], sh [T][H], then the item and its T pairs.
+    float *act = scratch, *sh = scratch + (size_t)T * EI;
+    moexb_pair_item* item = reinterpret_cast<moexb_pair_item*>(sh + (size_t)T * EH);
+    moexb_pair* pairs = reinterpret_cast<moexb_pair*>(item + 1);
+    identity_pairs_k<<<(T + 255) / 256, 256, 0, S(stream)>>>(blob, T, item, pairs);
+    LAUNCHED("identity_pairs");
+    int rc = pairs_launch(fmt, item, nullptr, 1, pairs, X, act, sh, stream);
+    if (rc != MOEXB_OK) return rc;
+    gated_add_rows_k<<<dim3((EH + 255) / 256, T), 256, 0, S(stream)>>>(out, sh, gl, gl_stride, EH);
+    LAUNCHED("gated_add_rows");
+    return MOEXB_OK;
+}
+
+// ---- formats ---------------------------------------------------------------------------------------------------------
+
+int moexb_dequant(int fmt, const uint8_t* blob, float* out, void* stream) {
+    REQUIRE(blob && out, "dequant: null pointer");
+    return by_fmt(fmt, [&]<int FMT>() {
+        dequant_k<FMT><<<(unsigned)((CHUNKS + 255) / 256), 256, 0, S(stream)>>>(blob, out);
+        LAUNCHED("dequant");
+        return (int)MOEXB_OK;
+    });
+}
+
+int moexb_q4k_dequant(const uint8_t* blocks, long long n, float* y, void* stream) {
+    REQUIRE(blocks && y, "q4k_dequant: null pointer");
+    REQUIRE(n > 0 && n % 256 == 0, "q4k_dequant: n=%lld must be a positive multiple of 256", n);
+    const long long threads = n / 256 * 4;
+    q4k_dequant_k<<<(unsigned)((threads + 255) / 256), 256, 0, S(stream)>>>(blocks, n / 256, y);
+    LAUNCHED("q4k_dequant");
+    return MOEXB_OK;
+}
+
+int moexb_q4k_to_zp(const uint8_t* gate, const uint8_t* up, const uint8_t* down, uint8_t* blob, void* stream) {
+    REQUIRE(gate && up && down && blob, "q4k_to_zp: null pointer");
+    q4k_to_zp_k<<<(unsigned)((CHUNKS / 8 + 127) / 128), 128, 0, S(stream)>>>(gate, up, down, blob);
+    LAUNCHED("q4k_to_zp");
+    return MOEXB_OK;
+}
+
+// ---- synthetic experts --------------------------------------------------------------------------------------------------
+
+static int synth_launch(int fmt, unsigned seed, int layer, int e0, int n, uint8_t* dst, const uint16_t* ts, const uint16_t* td, void* stream) {
+    REQUIRE(dst && ts && td, "synth_experts: null pointer");
+    REQUIRE(n > 0 && n <= 65535 && e0 >= 0 && layer >= 0, "synth_experts: layer=%d e0=%d n=%d", layer, e0, n);
+    return by_fmt(fmt, [&]<int FMT>() {
+        const size_t work = FMT == FMT_ZP ? CHUNKS / 8 : Q_BYTES / 4;
+        synth_experts_k<FMT><<<dim3((unsigned)((work + 255) / 256), n), 256, 0, S(stream)>>>(seed, layer, e0, dst, ts, td);
+        LAUNCHED("synth_experts");
+        return (int)MOEXB_OK;
+    });
+}
+
+int moexb_synth_expert_host(int fmt, unsigned seed, int layer, int expert, uint8_t* dst) {
+    REQUIRE(dst && fmt_ok(fmt), "synth_expert_host: bad argument");
+    const Tables& t = host_tables();
+    if (fmt == FMT_ZP) {
+        for (size_t sb = 0; sb < CHUNKS / 8; sb++) {
+            uint8_t blk[144], *qb, *cs, *sup;
+            synth_q4k_block(seed, layer, expert, sb, t.d, blk);
+            zp_block_dst(dst, sb, qb, cs, sup);
+            q4k_block_to_zp(blk, qb, cs, sup);
+        }
+        return MOEXB_OK;
+    }
+    for (size_t i = 0; i < Q_BYTES / 4; i++) {
+        const uint32_t w = synth_nibble_word(seed, layer, expert, i);
+        memcpy(dst + 4 * i, &w, 4);
+    }
+    for (size_t g = 0; g < CHUNKS / 2; g++) {
+        const uint16_t h = synth_scale_h(seed, layer, expert, g, t.s);
+        if (fmt == FMT_SYM_F16) memcpy(dst + Q_BYTES + 2 * g, &h, 2);
+        else { const float f = half_to_float_host(h); memcpy(dst + Q_BYTES + 4 * g, &f, 4); }
+    }
+    return MOEXB_OK;
+}
+
+int moexb_synth_q4k_host(unsigned seed, int layer, int expert, uint8_t* gate, uint8_t* up, uint8_t* down) {
+    REQUIRE(gate && up && down, "synth_q4k_host: null pointer");
+    const Tables& t = host_tables();
+    constexpr size_t NB = (size_t)EH * EI / 256;
+    for (size_t sb = 0; sb < 3 * NB; sb++) {
+        uint8_t* d = sb < NB ? gate + sb * 144 : sb < 2 * NB ? up + (sb - NB) * 144 : down + (sb - 2 * NB) * 144;
+        synth_q4k_block(seed, layer, expert, sb, t.d, d);
+    }
+    return MOEXB_OK;
+}
+
+// ---- context and resident layers -----------------------------------------------------------------------------------------
+
+}  // extern "C"
+template <class T>
+static int dev_alloc(moexb_ctx* ctx, T** p, size_t n) {
+    void* v = nullptr;
+    cudaError_t e = cudaMalloc(&v, n * sizeof(T));
+    if (e != cudaSuccess) return fail(MOEXB_ERR_NOMEM, "cudaMalloc of %zu bytes: %s", n * sizeof(T), cudaGetErrorString(e));
+    ctx->owned.push_back(v);
+    *p = static_cast<T*>(v);
+    return MOEXB_OK;
+}
+
+extern "C" {
+int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moexb_ctx** out) {
+    REQUIRE(out, "ctx_create: null output");
+    REQUIRE(max_tokens > 0 && max_tokens <= 65535 && max_experts > 0 && max_experts % 32 == 0 && max_experts <= 1024 && top_k > 0 && top_k <= 15,
+            "ctx_create: max_tokens=%d max_experts=%d top_k=%d", max_tokens, max_experts, top_k);
+    CUDA_TRY(cudaSetDevice(device));
+    moexb_ctx* c = new (std::nothrow) moexb_ctx;
+    if (!c) return fail(MOEXB_ERR_NOMEM, "out of host memory");
+    c->device = device; c->max_tokens = max_tokens; c->max_experts = max_experts; c->top_k = top_k;
+    const size_t T = max_tokens, P = T * (top_k + 1);
+    int rc = MOEXB_OK;
+    auto A = [&](auto** p, size_t n) { if (rc == MOEXB_OK) rc = dev_alloc(c, p, n); };
+    A(&c->table_s, SYNTH_TABLE_N); A(&c->table_d, SYNTH_TABLE_N);
+    A(&c->xf, T * EH); A(&c->xn, T * EH); A(&c->logits, T * (max_experts + 1)); A(&c->w, T * top_k); A(&c->idx, T * top_k);
+    A(&c->act, P * EI); A(&c->ypair, P * EH); A(&c->moe, T * EH);
+    A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
+    A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
+    if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
+    const Tables& t = host_tables();
+    cudaError_t e = cudaMemcpy(c->table_s, t.s, sizeof t.s, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(c->table_d, t.d, sizeof t.d, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { moexb_ctx_destroy(c); return fail(MOEXB_ERR_CUDA, "table upload: %s", cudaGetErrorString(e)); }
+    *out = c;
+    return MOEXB_OK;
+}
+
+int moexb_ctx_destroy(moexb_ctx* ctx) {
+    if (!ctx) return MOEXB_OK;
+    for (void* p : ctx->owned) cudaFree(p);
+    delete ctx;
+    return MOEXB_OK;
+}
+
+int moexb_synth_experts(moexb_ctx* ctx, int fmt, unsigned seed, int layer, int e0, int n, uint8_t* dst, void* stream) {
+    REQUIRE(ctx, "synth_experts: null context");
+    return synth_launch(fmt, seed, layer, e0, n, dst, ctx->table_s, ctx->table_d, stream);
+}
+
+int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype, moexb_layer** out) {
+    REQUIRE(ctx && out, "layer_create: null pointer");
+    REQUIRE(fmt_ok(fmt), "layer_create: unknown expert format %d", fmt);
+    REQUIRE(n_routed > 0 && n_routed % 32 == 0 && n_routed <= ctx->max_experts, "layer_create: n_routed=%d (context allows %d)", n_routed, ctx->max_experts);
+    REQUIRE(first_local >= 0 && n_local >= 0 && first_local + n_local <= n_routed, "layer_create: local experts [%d, %d) outside 0..%d", first_local, first_local + n_local, n_routed);
+    REQUIRE(router_dtype == MOEXB_F32 || router_dtype == 2, "layer_create: router dtype %d", router_dtype);
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    moexb_layer* L = new (std::nothrow) moexb_layer;
+    if (!L) return fail(MOEXB_ERR_NOMEM, "out of host memory");
+    L->ctx = ctx; L->fmt = fmt; L->n_routed = n_routed; L->first_local = first_local; L->n_local = n_local; L->router_dtype = router_dtype;
+    const size_t eb = expert_bytes(fmt);
+    cudaError_t e = cudaMalloc((void**)&L->image, (size_t)(n_local + 1) * eb);
+    if (e == cudaSuccess) e = cudaMalloc(&L->router, (size_t)(n_routed + 1) * EH * (router_dtype == MOEXB_F32 ? 4 : 2));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&L->slot_table, (size_t)(n_routed + 1) * sizeof(void*));
+    if (e == cudaSuccess) {
+        L->slot_host.assign(n_routed + 1, nullptr);
+        for (int i = 0; i < n_local; i++) L->slot_host[first_local + i] = L->image + (size_t)i * eb;
+        L->slot_host[n_routed] = L->image + (size_t)n_local * eb;
+        e = cudaMemcpy(L->slot_table, L->slot_host.data(), L->slot_host.size() * sizeof(void*), cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) { moexb_layer_destroy(L); return fail(MOEXB_ERR_NOMEM, "layer_create: %s", cudaGetErrorString(e)); }
+    *out = L;
+    return MOEXB_OK;
+}
+
+int moexb_layer_destroy(moexb_layer* L) {
+    if (!L) return MOEXB_OK;
+    cudaFree(L->image); cudaFree(L->router); cudaFree((void*)L->slot_table);
+    delete L;
+    return MOEXB_OK;
+}
+
+uint8_t* moexb_layer_blob(moexb_layer* L, int e) {
+    if (!L || e < 0 || e > L->n_routed) return nullptr;
+    return const_cast<uint8_t*>(L->slot_host[e]);
+}
+const uint8_t* const* moexb_layer_slot_table(moexb_layer* L) { return L ? L->slot_table : nullptr; }
+void* moexb_layer_router(moexb_layer* L) { return L ? L->router : nullptr; }
+
+int moexb_layer_upload_expert(moexb_layer* L, int e, const uint8_t* blob_host) {
+    REQUIRE(L && blob_host, "layer_upload_expert: null pointer");
+    REQUIRE(e >= 0 && e <= L->n_routed && L->slot_host[e], "layer_upload_expert: expert %d is not held by this layer", e);
+    CUDA_TRY(cudaMemcpy(const_cast<uint8_t*>(L->slot_host[e]), blob_host, expert_bytes(L->fmt), cudaMemcpyHostToDevice));
+    return MOEXB_OK;
+}
+
+int moexb_layer_set_router(moexb_layer* L, const void* W_host) {
+    REQUIRE(L && W_host, "layer_set_router: null pointer");
+    CUDA_TRY(cudaMemcpy(L->router, W_host, (size_t)(L->n_routed + 1) * EH * (L->router_dtype == MOEXB_F32 ? 4 : 2), cudaMemcpyHostToDevice));
+    return MOEXB_OK;
+}
+
+int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void* stream) {
+    REQUIRE(L, "layer_fill_synth: null layer");
+    const size_t eb = expert_bytes(L->fmt);
+    if (L->n_local) {
+        const int rc = synth_launch(L->fmt, seed, layer_index, L->first_local, L->n_local, L->image, L->ctx->table_s, L->ctx->table_d, stream);
+        if (rc != MOEXB_OK) return rc;
+    }
+    return synth_launch(L->fmt, seed, layer_index, L->n_routed, 1, L->image + (size_t)L->n_local * eb, L->ctx->table_s, L->ctx->table_d, stream);
+}
+
+// Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
+static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode_slots) {
+    const int E = L->n_routed, ld = E + 1;
+    int rc = L->router_dtype == MOEXB_F32 ? gemv_any(static_cast<const float*>(L->router), xf, c->logits, EH, ld, stream, T)
+                                          : gemv_any(static_cast<const __half*>(L->router), xf, c->logits, EH, ld, stream, T);
+    if (rc != MOEXB_OK) return rc;
+    return topk_launch(c->logits, E, K, 1, c->idx, c->w, stream, T, ld, L->slot_table, decode_slots ? c->slots : nullptr, decode_slots ? c->wts : nullptr);
+}
+
+int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype, int T, int K, float* out, int* idx_out,
+                        float* w_out, int flags, void* stream) {
+    REQUIRE(c && L && X && out, "layer_forward: null pointer");
+    REQUIRE(L->ctx == c, "layer_forward: layer belongs to another context");
+    REQUIRE(T > 0 && T <= c->max_tokens, "layer_forward: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
+    REQUIRE(K > 0 && K <= c->top_k, "layer_forward: K=%d exceeds the context's top_k=%d", K, c->top_k);
+    REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "layer_forward: x_dtype=%d", x_dtype);
+    const bool shared = !(flags & 1), block = flags & 2;
+    const bool all_local = L->n_local == L->n_routed;
+    const int E = L->n_routed, ld = E + 1;
+    cudaStream_t st = S(stream);
+    const size_t n = (size_t)T * EH;
+    const float* xin;  // the layer input as f32
+    if (x_dtype == MOEXB_BF16) {
+        bf16_to_f32_k<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), c->xf, n);
+        LAUNCHED("bf16_to_f32");
+        xin = c->xf;
+    } else xin = static_cast<const float*>(X);
+    const float* xf = xin;  // what the router and the experts see
+    if (block) {
+        rmsnorm_rows_k<<<T, 256, 0, st>>>(xin, c->xn, EH, 1e-6f);
+        LAUNCHED("rmsnorm");
+        xf = c->xn;
+    }
+    float* moe = block ? c->moe : out;
+    const bool decode = T == 1 && all_local && shared;
+    int rc = layer_route(c, L, xf, T, K, stream, decode);
+    if (rc != MOEXB_OK) return rc;
+    if (decode) {
+        // one token: the K routed experts and the shared expert (weight sigmoid(gate logit)) as K+1 decode experts
+        rc = moexb_experts_forward(L->fmt, c->slots, c->wts, K + 1, xf, c->act, moe, stream, nullptr);
+        if (rc != MOEXB_OK) return rc;
+    } else {
+        constexpr int WARPS = 8;
+        group_count_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, T * K, E, c->counts);
+        LAUNCHED("group_count");
+        group_scatter_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->counts, c->items, c->pairs,
+                                                                                 c->nitems, shared ? c->logits + E : nullptr, ld);
+        LAUNCHED("group_scatter");
+        // pairs of experts that are not held here are never written: their ypair rows must read as zero
+        if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
+        rc = pairs_launch(L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
+        if (rc != MOEXB_OK) return rc;
+        rc = moexb_pairs_reduce(c->ypair, shared ? c->ypair + (size_t)T * K * EH : nullptr, moe, K, EH, T, nullptr, stream);
+        if (rc != MOEXB_OK) return rc;
+    }
+    if (block) {
+        residual_add_k<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(xin, c->moe, out, n);
+        LAUNCHED("residual_add");
+    }
+    if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    if (w_out) CUDA_TRY(cudaMemcpyAsync(w_out, c->w, (size_t)T * K * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return MOEXB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,188 @@
+// Router kernels: logits in a pinned fp32 summation order, softmax + top-K selection, pair grouping by expert.
+#pragma once
+#include "common.cuh"
+
+namespace moexb {
+
+__device__ __forceinline__ float4 ld_w4(const float* W, size_t k) { return __ldg(reinterpret_cast<const float4*>(W + k)); }
+__device__ __forceinline__ float4 ld_w4(const __half* W, size_t k) {
+    const uint2 u = __ldg(reinterpret_cast<const uint2*>(W + k));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// y[r][o] = W[o] . x[r]. One warp per (row r, output o): lane j accumulates elements 128c+4j .. 128c+4j+3 for
+// c = 0, 1, .. with fused multiply-adds in ascending order, then a xor-butterfly (16, 8, 4, 2, 1) adds the 32 partial
+// sums. The CPU oracle follows the same order, so the logits - and with them the selected experts - agree bit for bit.
+// Stands behind gemv_f16_k (kernels.cuh:73-91). grid (ceil(O / WARPS), rows).
+template <typename WT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gemv_rows_k(const WT* __restrict__ W, const float* __restrict__ x,
+                                                          float* __restrict__ y, int I, int O) {
+    const int o = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (o >= O) return;
+    const float* xr = x + (size_t)blockIdx.y * I;
+    const WT* wr = W + (size_t)o * I;
+    float acc = 0.f;
+    for (int c = 0; c < I / 128; c++) {
+        const float4 w = ld_w4(wr, (size_t)128 * c + 4 * lane);
+        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + 128 * c + 4 * lane));
+        acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)blockIdx.y * O + o] = acc;
+}
+
+// The same result for many rows (a prefill chunk): a warp keeps TO outputs x TR rows of accumulators per lane, each
+// lane still owning elements 128c+4j..4j+3 of every dot product, so every (row, output) sum is formed in exactly the
+// order of gemv_rows_k and the two kernels are interchangeable bit for bit. grid (ceil(O / (WARPS*TO)), ceil(rows / TR)).
+template <typename WT, int WARPS, int TO, int TR>
+__global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__ W, const float* __restrict__ x,
+                                                          float* __restrict__ y, int I, int O, int rows) {
+    const int o0 = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * TO, r0 = blockIdx.y * TR, lane = threadIdx.x & 31;
+    if (o0 >= O) return;
+    float acc[TR][TO];
+#pragma unroll
+    for (int r = 0; r < TR; r++)
+#pragma unroll
+        for (int o = 0; o < TO; o++) acc[r][o] = 0.f;
+    for (int c = 0; c < I / 128; c++) {
+        float4 w[TO], v[TR];
+#pragma unroll
+        for (int o = 0; o < TO; o++) w[o] = ld_w4(W + (size_t)min(o0 + o, O - 1) * I, (size_t)128 * c + 4 * lane);
+#pragma unroll
+        for (int r = 0; r < TR; r++) v[r] = __ldg(reinterpret_cast<const float4*>(x + (size_t)min(r0 + r, rows - 1) * I + 128 * c + 4 * lane));
+#pragma unroll
+        for (int r = 0; r < TR; r++)
+#pragma unroll
+            for (int o = 0; o < TO; o++) {
+                float a = acc[r][o];
+                a = fmaf(w[o].x, v[r].x, a); a = fmaf(w[o].y, v[r].y, a); a = fmaf(w[o].z, v[r].z, a); a = fmaf(w[o].w, v[r].w, a);
+                acc[r][o] = a;
+            }
+    }
+#pragma unroll
+    for (int r = 0; r < TR; r++)
+#pragma unroll
+        for (int o = 0; o < TO; o++) {
+            const float s = warp_sum(acc[r][o]);
+            if (lane == 0 && r0 + r < rows && o0 + o < O) y[(size_t)(r0 + r) * O + o0 + o] = s;
+        }
+}
+
+// Softmax over E logits and the K largest, one warp per token (kernels.cuh:373-406 does it with a block per token).
+// Lane l holds logits l, l+32, ..; each round every lane offers its best remaining (value, index), a butterfly keeps
+// the larger value and on equal values the lower index, and the winner is struck from its owner's mask.
+// Selection compares logits (softmax is monotone). NaN logits count as -inf. Optional decode outputs: slots_out /
+// wts_out [K+1] = the selected experts' blob pointers and weights followed by the shared expert with weight
+// sigmoid(logits[E]).
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restrict__ logits, int E, int K, int norm, int ld,
+                                                            int* __restrict__ idx, float* __restrict__ w, int T,
+                                                            const uint8_t* const* __restrict__ slot_table,
+                                                            const uint8_t** __restrict__ slots_out, float* __restrict__ wts_out) {
+    const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* l = logits + (size_t)t * ld;
+    const int nj = E >> 5;
+    float v[32];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        v[j] = -INFINITY;
+        if (j < nj) { const float a = l[lane + 32 * j]; v[j] = a != a ? -INFINITY : a; }
+        m = fmaxf(m, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j++) if (j < nj) sum += expf(v[j] - m);
+    sum = warp_sum(sum);
+    unsigned taken = 0;
+    float mine = 0.f, total = 0.f;  // lane k keeps the k-th probability
+    int mine_i = 0;
+    for (int k = 0; k < K; k++) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < nj && !(taken >> j & 1) && (v[j] > bv || bi == 0x7fffffff)) { bv = v[j]; bi = lane + 32 * j; }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        const float p = expf(bv - m) / sum;
+        total += p;
+        if (lane == k) { mine = p; mine_i = bi; }
+    }
+    if (lane < K) {
+        const float wk = norm ? mine / total : mine;
+        idx[(size_t)t * K + lane] = mine_i;
+        w[(size_t)t * K + lane] = wk;
+        if (slots_out) { slots_out[(size_t)t * (K + 1) + lane] = slot_table[mine_i]; wts_out[(size_t)t * (K + 1) + lane] = wk; }
+    }
+    if (slots_out && lane == K) {
+        slots_out[(size_t)t * (K + 1) + K] = slot_table[E];
+        wts_out[(size_t)t * (K + 1) + K] = 1.f / (1.f + expf(-l[E]));
+    }
+}
+
+// ---- pair grouping: bucket the T*K (token, rank) pairs by expert (moex.cu:1466-1486; kernels.cuh:1030-1045) ----------
+
+// counts[e] = number of pairs that selected expert e. One warp per expert.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) group_count_k(const int* __restrict__ idx, int n, int E, int* __restrict__ counts) {
+    const int e = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (e >= E) return;
+    int c = 0;
+    for (int p = lane; p < n; p += 32) c += __ldg(idx + p) == e;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) counts[e] = c;
+}
+
+// Items in ascending expert id over the experts that are held (slot_table[e] != null) and selected; the pairs of an
+// expert in token order, p = t*K + rank. Every block rebuilds the (tiny) exclusive scan over experts, then one warp per
+// expert walks the pair list once and writes its matches in order. Optional shared expert: one more item holding every
+// token, p = T*K + t, w = sigmoid(gate logit of t). E <= 1024.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) group_scatter_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
+                                                              const uint8_t* const* __restrict__ slot_table, const int* __restrict__ counts,
+                                                              moexb_pair_item* __restrict__ items, moexb_pair* __restrict__ pairs,
+                                                              int* __restrict__ nitems, const float* __restrict__ gate_logits, int gl_stride) {
+    __shared__ int start[1024], item_of[1024];
+    __shared__ int s_ni, s_np;
+    if (threadIdx.x == 0) {
+        int ni = 0, np = 0;
+        for (int e = 0; e < E; e++) {
+            const int c = slot_table[e] ? counts[e] : 0;
+            start[e] = np; item_of[e] = c ? ni : -1;
+            np += c; ni += c != 0;
+        }
+        s_ni = ni; s_np = np;
+    }
+    __syncthreads();
+    const int n = T * K, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (e < E && item_of[e] >= 0) {
+        int at = start[e];
+        if (lane == 0) items[item_of[e]] = {slot_table[e], at, counts[e]};
+        for (int p0 = 0; p0 < n; p0 += 32) {
+            const int p = p0 + lane;
+            const bool hit = p < n && __ldg(idx + p) == e;
+            const unsigned b = __ballot_sync(0xffffffffu, hit);
+            if (hit) pairs[at + __popc(b & ((1u << lane) - 1))] = {p / K, p, __ldg(w + p)};
+            at += __popc(b);
+        }
+    }
+    if (blockIdx.x == 0) {
+        if (gate_logits && slot_table[E]) {
+            if (threadIdx.x == 0) { items[s_ni] = {slot_table[E], s_np, T}; *nitems = s_ni + 1; }
+            for (int t = threadIdx.x; t < T; t += blockDim.x)
+                pairs[s_np + t] = {t, n + t, 1.f / (1.f + expf(-gate_logits[(size_t)t * gl_stride]))};
+        } else if (threadIdx.x == 0) *nitems = s_ni;
+    }
+}
+
+}  // namespace moexb

@@ -1,0 +1,327 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs. Needs a B200.
+
+Bars: dequantised weights, router logits and selected expert ids bit-exact; routing weights to 1e-6; expert-FFN outputs
+within relative L2 error 1e-3 and max-abs error 2e-3 of the oracle's fp32 path (for the zero-point / Q4_K experts, whose
+synthetic outputs reach 1e6, the max-abs bar is scaled by max|ref| / 57, 57 being the largest symmetric-format output).
+"""
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+import moe_b200 as m
+from oracle import oracle as o
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("lib_built")]
+DEV = "cuda:0"
+ITEM_DT = np.dtype([("slot", "<u8"), ("start", "<i4"), ("count", "<i4")])
+PAIR_DT = np.dtype([("t", "<i4"), ("p", "<i4"), ("w", "<f4")])
+FMTS = [m.FMT_SYM_F32, m.FMT_SYM_F16, m.FMT_ZP]
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def check_ffn(got, ref, fmt, what=""):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    rel_l2 = np.linalg.norm(got - ref) / (np.linalg.norm(ref) + 1e-30)
+    max_abs = np.abs(got - ref).max()
+    bar = 2e-3 * (max(1.0, np.abs(ref).max() / 57.0) if fmt == m.FMT_ZP else 1.0)
+    assert rel_l2 <= 1e-3 and max_abs <= bar, f"{what}: rel-L2 {rel_l2:.3e} (bar 1e-3), max-abs {max_abs:.3e} (bar {bar:.3e})"
+    return rel_l2, max_abs
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = m.Context(0, max_tokens=64, max_experts=256, top_k=8)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def experts():
+    """Six synthetic experts per format: host blobs and their device copies."""
+    out = {}
+    for fmt in FMTS:
+        host = [m.synth_expert_host(fmt, 0, 0, e) for e in range(6)]
+        out[fmt] = (host, [dev(b) for b in host])
+    return out
+
+
+def test_device_generator_matches_host_generator(ctx):
+    for fmt in FMTS:
+        eb = m.expert_bytes(fmt)
+        dst = torch.zeros(3 * eb, device=DEV, dtype=torch.uint8)
+        ctx.synth_experts(fmt, 17, 5, 254, 3, dst)
+        got = dst.cpu().numpy()
+        for i in range(3):
+            assert np.array_equal(got[i * eb:(i + 1) * eb], m.synth_expert_host(fmt, 17, 5, 254 + i)), f"format {fmt} expert {254 + i}"
+
+
+def test_dequantised_weights_bit_exact(experts):
+    for fmt in FMTS:
+        host, devb = experts[fmt]
+        for e in (0, 3):
+            assert np.array_equal(m.dequant(fmt, devb[e]).cpu().numpy(), o.dequant(fmt, host[e])), f"format {fmt}"
+
+
+def test_q4k_blocks(golden_dir):
+    rec = open(os.path.join(golden_dir, "q4k_fixture.bin"), "rb").read()
+    _, n = struct.unpack_from("<II", rec, 0)
+    raw = np.frombuffer(rec, np.uint8, n // 256 * 144, 8).copy()
+    want = np.frombuffer(rec, np.float32, n, 8 + raw.size)
+    assert np.array_equal(m.q4k_dequant(dev(raw), n).cpu().numpy(), want)          # the reference's GGUF fixture
+    g, u, d = m.synth_q4k_host(4, 2, 9)
+    assert np.array_equal(m.q4k_dequant(dev(d), m.EH * m.EI).cpu().numpy(), o.q4k_dequant(d, m.EH * m.EI))
+    blob = m.q4k_to_zp(dev(g), dev(u), dev(d)).cpu().numpy()
+    assert np.array_equal(blob, o.q4k_to_zp(g, u, d))                                # bit-preserving conversion
+
+
+@pytest.mark.parametrize("rows,O", [(1, 257), (4, 257), (1, 5), (64, 257), (50, 256), (17, 33)])
+def test_router_logits_bit_exact(rows, O):
+    rng = np.random.default_rng(rows * 1000 + O)
+    W = (rng.standard_normal((O, 2048)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((rows, 2048)).astype(np.float32)
+    assert np.array_equal(m.gemv_f32(dev(W), dev(x), rows=rows).cpu().numpy(), o.router_logits(W, x, rows))
+    W16 = W.astype(np.float16)
+    assert np.array_equal(m.gemv_f16(dev(W16), dev(x), rows=rows).cpu().numpy(), o.router_logits(W16, x, rows))
+
+
+@pytest.mark.parametrize("T,E,K,ld", [(1, 256, 8, 257), (7, 256, 8, 256), (64, 256, 8, 257), (3, 32, 4, 40), (2, 1024, 15, 1024)])
+def test_router_topk(T, E, K, ld):
+    rng = np.random.default_rng(T + E)
+    lg = rng.standard_normal((T, ld)).astype(np.float32)
+    lg[0, 5] = lg[0, 3] = lg[0, 9] = 4.0            # ties go to the lower index
+    if T > 1:
+        lg[1, :E] = 0.25                            # all equal: experts 0..K-1 in order
+    for norm in (True, False):
+        idx, w = m.router_topk(dev(lg), E, K, norm, T, ld)
+        ri, rw = o.router_topk(lg, E, K, norm, T, ld)
+        assert np.array_equal(idx.cpu().numpy(), ri)
+        assert np.allclose(w.cpu().numpy(), rw, rtol=2e-6, atol=0)
+    assert list(ri[0, :3]) == [3, 5, 9]
+    if T > 1:
+        assert list(ri[1]) == list(range(K))
+
+
+def make_work(rng, blobs_dev, counts, T):
+    """Items with the given token counts; returns numpy item/pair records and the oracle's job list shape."""
+    items = np.zeros(len(counts), ITEM_DT); pairs = np.zeros(sum(counts), PAIR_DT)
+    jobs, p = [], 0
+    for i, c in enumerate(counts):
+        toks = sorted(rng.choice(T, size=c, replace=False).tolist())
+        ws = rng.uniform(0.05, 0.5, c).astype(np.float32)
+        items[i] = (blobs_dev[i].data_ptr(), p, c)
+        for j in range(c):
+            pairs[p + j] = (toks[j], p + j, ws[j])
+        jobs.append((i, toks, list(range(p, p + c)), ws))
+        p += c
+    return items, pairs, jobs, p
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_experts_forward_decode(experts, fmt):
+    host, devb = experts[fmt]
+    rng = np.random.default_rng(3)
+    K = 6
+    x = rng.standard_normal(2048).astype(np.float32)
+    w = rng.uniform(0.05, 0.3, K).astype(np.float32)
+    slots = torch.tensor([b.data_ptr() for b in devb], dtype=torch.int64, device=DEV)
+    ypair, act_ref = o.run_pairs(fmt, [(host[k], [0], [k], [w[k]]) for k in range(K)], x[None], K, want_act=True)
+    ref = o.pairs_reduce(ypair, K, 1)[0]
+    act = torch.zeros(K * 512, device=DEV)
+    out = m.experts_forward(fmt, slots, dev(w), K, dev(x), act=act)
+    check_ffn(out.cpu().numpy(), ref, fmt, "decode out")
+    check_ffn(act.cpu().numpy().reshape(K, 512), act_ref, fmt, "decode act")
+    # device-side count of valid experts: 3 of them, then none (kernels.cuh:660-661)
+    nh = torch.tensor([3], dtype=torch.int32, device=DEV)
+    out3 = m.experts_forward(fmt, slots, dev(w), K, dev(x), nh=nh)
+    check_ffn(out3.cpu().numpy(), o.pairs_reduce(ypair[:3], 3, 1)[0], fmt, "decode nh=3")
+    nh.zero_()
+    assert float(m.experts_forward(fmt, slots, dev(w), K, dev(x), nh=nh).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_pairs_forward_ragged(experts, fmt):
+    host, devb = experts[fmt]
+    rng = np.random.default_rng(11)
+    T = 12
+    X = rng.standard_normal((T, 2048)).astype(np.float32)
+    items, pairs, jobs, npairs = make_work(rng, devb, [1, 2, 5, 9, 12, 3], T)
+    ref, act_ref = o.run_pairs(fmt, [(host[i], t, p, w) for i, t, p, w in jobs], X, npairs, want_act=True)
+    act = torch.zeros(npairs * 512, device=DEV); yp = torch.zeros(npairs * 2048, device=DEV)
+    it_d, pr_d = dev(items.view(np.uint8)), dev(pairs.view(np.uint8))
+    m.pairs_forward(fmt, it_d, len(items), pr_d, dev(X), act, yp)
+    check_ffn(act.cpu().numpy().reshape(npairs, 512), act_ref, fmt, "pairs act")
+    check_ffn(yp.cpu().numpy().reshape(npairs, 2048), ref, fmt, "pairs ypair")
+    # device-side item count: only the first 4 items run (kernels.cuh:755-766)
+    yp2 = torch.zeros_like(yp)
+    m.pairs_forward_dev(fmt, it_d, torch.tensor([4], dtype=torch.int32, device=DEV), len(items), pr_d, dev(X), act, yp2)
+    n4 = int(items["start"][4])
+    got = yp2.cpu().numpy().reshape(npairs, 2048)
+    check_ffn(got[:n4], ref[:n4], fmt, "pairs_dev")
+    assert not got[n4:].any()
+    assert m.lib().moexb_pairs_forward(fmt, None, 0, None, None, None, None, None) == 0   # empty work list: nothing to do
+
+
+def test_pairs_reduce_and_gated_add():
+    rng = np.random.default_rng(2)
+    T, K, D = 5, 8, 2048
+    yp = rng.standard_normal((T * K, D)).astype(np.float32); extra = rng.standard_normal((T, D)).astype(np.float32)
+    moe = torch.empty(T, D, device=DEV)
+    m.pairs_reduce(dev(yp), None, moe, K, D, T)
+    assert np.array_equal(moe.cpu().numpy(), o.pairs_reduce(yp, K, T))                   # fixed rank order: bit-exact
+    m.pairs_reduce(dev(yp), dev(extra), moe, K, D, T)
+    assert np.array_equal(moe.cpu().numpy(), o.pairs_reduce(yp, K, T) + extra)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m.pairs_reduce(dev(yp), dev(extra), moe, K, D, T, use_cpu=flag)
+    assert np.array_equal(moe.cpu().numpy(), o.pairs_reduce(yp, K, T))
+    gl = rng.standard_normal((T, 3)).astype(np.float32)
+    out = dev(extra.copy())
+    m.gated_add_rows(out, dev(yp[:T]), dev(gl), 3, D, T)
+    ref = extra + yp[:T] / (1 + np.exp(-gl[:, :1].astype(np.float64)))
+    assert np.allclose(out.cpu().numpy(), ref, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("fmt", [m.FMT_SYM_F16, m.FMT_ZP])
+def test_shared_expert_add(experts, fmt):
+    host, devb = experts[fmt]
+    rng = np.random.default_rng(8)
+    T = 5
+    X = rng.standard_normal((T, 2048)).astype(np.float32); gl = rng.standard_normal(T).astype(np.float32)
+    base = rng.standard_normal((T, 2048)).astype(np.float32)
+    out = dev(base.copy())
+    m.shared_expert_add(fmt, devb[2], dev(gl), 1, dev(X), T, out)
+    sh = o.run_pairs(fmt, [(host[2], list(range(T)), list(range(T)), [1.0] * T)], X, T)
+    ref = base + sh / (1 + np.exp(-gl[:, None]))
+    check_ffn(out.cpu().numpy(), ref, fmt, "shared expert")
+
+
+@pytest.mark.parametrize("T,E,K,holes", [(1, 256, 8, False), (4, 256, 8, False), (64, 256, 8, True), (33, 64, 4, True)])
+def test_group_pairs(T, E, K, holes):
+    rng = np.random.default_rng(T * E)
+    idx = np.stack([rng.choice(E, size=K, replace=False) for _ in range(T)]).astype(np.int32)
+    w = rng.uniform(0, 1, (T, K)).astype(np.float32)
+    table = np.arange(1, E + 2, dtype=np.int64) * 4096        # fake non-null blob addresses
+    held = np.ones(E, np.uint8)
+    if holes:
+        held[E // 4: E // 2] = 0
+        table[E // 4: E // 2] = 0
+    items, pairs, nitems = m.group_pairs(dev(idx), dev(w), T, K, E, dev(table))
+    ri, pt, pp, pw = o.group_pairs(idx, w, E, held)
+    ni = int(nitems.item())
+    assert ni == len(ri)
+    gi = items.cpu().numpy().view(ITEM_DT)[:ni]; gp = pairs.cpu().numpy().view(PAIR_DT)[:len(pt)]
+    assert [(int(table[e]), s, c) for e, s, c in ri] == [(int(a), int(b), int(c)) for a, b, c in gi]
+    assert np.array_equal(gp["t"], pt) and np.array_equal(gp["p"], pp) and np.array_equal(gp["w"], pw)
+
+
+@pytest.fixture(scope="module")
+def layer_sym(ctx):
+    """A full-size layer (256 routed + shared, fp16 scales) with seeded router weights, and its host twin."""
+    rng = np.random.default_rng(0)
+    L = m.Layer(ctx, m.FMT_SYM_F16, 256)
+    L.fill_synth(0, 0)
+    W = (rng.standard_normal((257, 2048)) * 0.02).astype(np.float32)
+    L.set_router(W)
+    host = [m.synth_expert_host(m.FMT_SYM_F16, 0, 0, e) for e in range(257)]
+    yield L, W, host
+    L.close()
+
+
+@pytest.mark.parametrize("T", [1, 4, 64])
+def test_layer_forward_symmetric(layer_sym, T):
+    L, W, host = layer_sym
+    rng = np.random.default_rng(100 + T)
+    X = rng.standard_normal((T, 2048)).astype(np.float32)
+    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV); w = torch.empty(T, 8, device=DEV)
+    out = L.forward(dev(X), T, 8, idx=idx, w=w)
+    ref, ri, rw, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X, 8)
+    assert np.array_equal(idx.cpu().numpy(), ri)                      # selected experts: identical
+    assert np.allclose(w.cpu().numpy(), rw, rtol=2e-6, atol=0)
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"layer T={T}")
+
+
+def test_layer_forward_bf16_input_and_no_shared(layer_sym):
+    L, W, host = layer_sym
+    T = 16
+    X = torch.randn(T, 2048, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    out = L.forward(X.to(DEV), T, 8)
+    ref, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X.float().numpy(), 8)
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, "bf16 input")
+    out = L.forward(X.to(DEV), T, 8, flags=1)
+    ref, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X.float().numpy(), 8, flags=1)
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, "no shared expert")
+
+
+def test_layer_forward_zero_point(ctx):
+    rng = np.random.default_rng(1)
+    E = 32
+    L = m.Layer(ctx, m.FMT_ZP, E, router_dtype=m.F16)
+    L.fill_synth(1, 0)
+    W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float16)
+    L.set_router(W)
+    host = [m.synth_expert_host(m.FMT_ZP, 1, 0, e) for e in range(E + 1)]
+    for T in (1, 5):
+        X = rng.standard_normal((T, 2048)).astype(np.float32)
+        idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+        out = L.forward(dev(X), T, 8, idx=idx)
+        ref, ri, _, _ = o.layer_forward(m.FMT_ZP, host, W, X, 8)
+        assert np.array_equal(idx.cpu().numpy(), ri)
+        check_ffn(out.cpu().numpy(), ref, m.FMT_ZP, f"zero-point layer T={T}")
+    L.close()
+
+
+def test_expert_parallel_partial_layers_sum_to_the_whole(ctx, layer_sym):
+    """Two layers holding experts [0,128) and [128,256) of the same weights: their partial outputs add up to the full
+    layer's routed part (pairs of experts that a rank does not hold are dropped)."""
+    Lfull, W, host = layer_sym
+    T = 8
+    X = np.random.default_rng(9).standard_normal((T, 2048)).astype(np.float32)
+    parts = []
+    for r in range(2):
+        L = m.Layer(ctx, m.FMT_SYM_F16, 256, first_local=128 * r, n_local=128)
+        L.fill_synth(0, 0); L.set_router(W)
+        parts.append(L.forward(dev(X), T, 8, flags=1).cpu().numpy())
+        L.close()
+    ref, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X, 8, flags=1)
+    check_ffn(parts[0] + parts[1], ref, m.FMT_SYM_F16, "expert-parallel halves")
+
+
+def test_residual_block_chain(ctx):
+    """x_{l+1} = x_l + moe_l(rmsnorm(x_l)) over 3 layers of 32 experts: every layer checked with the oracle's own input
+    (teacher forcing), and the chained result end to end."""
+    rng = np.random.default_rng(4)
+    E, T, NL = 32, 4, 3
+    layers, hosts, Ws = [], [], []
+    for l in range(NL):
+        L = m.Layer(ctx, m.FMT_SYM_F16, E)
+        L.fill_synth(2, l)
+        W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
+        L.set_router(W)
+        layers.append(L); Ws.append(W); hosts.append([m.synth_expert_host(m.FMT_SYM_F16, 2, l, e) for e in range(E + 1)])
+    x_ref = rng.standard_normal((T, 2048)).astype(np.float32)
+    x_gpu = dev(x_ref.copy())
+    for l in range(NL):
+        idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+        forced = layers[l].forward(dev(x_ref), T, 8, idx=idx, flags=2).cpu().numpy()
+        x_gpu = layers[l].forward(x_gpu, T, 8, flags=2)
+        moe, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, hosts[l], Ws[l], o.rmsnorm(x_ref), 8)
+        x_ref = x_ref + moe
+        assert np.array_equal(idx.cpu().numpy(), ri)
+        check_ffn(forced, x_ref, m.FMT_SYM_F16, f"block {l}")
+    check_ffn(x_gpu.cpu().numpy(), x_ref, m.FMT_SYM_F16, "chained")
+    for L in layers:
+        L.close()
+
+
+def test_layer_forward_rejects_oversize_requests(ctx, layer_sym):
+    L, _, _ = layer_sym
+    X = torch.zeros(65, 2048, device=DEV)
+    with pytest.raises(m.MoexbError, match="max_tokens"):
+        L.forward(X, 65, 8)
+    with pytest.raises(m.MoexbError, match="top_k"):
+        L.forward(X, 4, 9)
