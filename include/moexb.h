@@ -176,6 +176,38 @@ int moexb_layer_fill_synth(moexb_layer* layer, unsigned seed, int layer_index, v
 int moexb_layer_forward(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x_dtype, int T, int K, float* out,
                         int* idx_out, float* w_out, int flags, void* stream);
 
+/* ---- a stack of layers as one replayable unit ---------------------------------------------------------------------- */
+
+typedef struct moexb_stack moexb_stack;
+
+/* Chains n_layers residual blocks x_{l+1} = x_l + moe_l(rmsnorm(x_l)) (unit norm weight, eps 1e-6; the structure of
+ * the reference's decoder block around its MoE, moex.cu:1082, 1092) for a fixed token count T and captures the whole
+ * sequence of launches in one CUDA graph, as the reference captures its per-step graph (moex.cu:1165-1181).
+ * Input [T][H] of x_dtype, output x_{n_layers} [T][H] f32. The layers must outlive the stack. */
+int moexb_stack_create(moexb_ctx* ctx, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype,
+                       moexb_stack** out);
+int moexb_stack_destroy(moexb_stack* stack);
+/* Device buffers: copies X in, replays the graph, copies the result to out; all on `stream`, no synchronisation. */
+int moexb_stack_run(moexb_stack* stack, const void* X, float* out, void* stream);
+/* Host buffers (pinned memory recommended): host->device copy of X, the graph, device->host copy of the result, then
+ * waits for the stream. This is the call an engine that keeps activations on the host makes once per step. */
+int moexb_stack_run_host(moexb_stack* stack, const void* X_host, float* out_host, void* stream);
+/* Kernel launches of one replay. */
+int moexb_stack_kernel_count(moexb_stack* stack);
+
+/* ---- instrumentation ------------------------------------------------------------------------------------------------ */
+
+/* Kernels launched by this library in this process so far (graph replays count their kernel nodes). */
+long long moexb_launch_count(void);
+
+enum { MOEXB_PROF_ROUTER = 0, MOEXB_PROF_TOPK = 1, MOEXB_PROF_GROUP = 2, MOEXB_PROF_GATE_UP = 3, MOEXB_PROF_DOWN = 4,
+       MOEXB_PROF_COMBINE = 5, MOEXB_PROF_OTHER = 6, MOEXB_PROF_TAGS = 7 };
+/* While on, moexb_layer_forward brackets each of its kernels with CUDA events on the launching stream (not valid during
+ * graph capture). moexb_ctx_profile_read waits for the device, then returns per tag the summed kernel time in ms and
+ * the number of launches since the last read (arrays of MOEXB_PROF_TAGS), and clears the records. */
+int moexb_ctx_profile(moexb_ctx* ctx, int on);
+int moexb_ctx_profile_read(moexb_ctx* ctx, float* ms, int* launches);
+
 #ifdef __cplusplus
 }
 #endif

@@ -145,6 +145,15 @@ class Context:
     def synth_experts(self, fmt, seed, layer, e0, n, dst):
         check(lib().moexb_synth_experts(self.h, fmt, seed, layer, e0, n, _ptr(dst), _stream()))
 
+    def profile(self, on):
+        check(lib().moexb_ctx_profile(self.h, int(on)))
+
+    def profile_read(self):
+        """(ms per tag, launches per tag) since the last read; tags as MOEXB_PROF_* in include/moexb.h."""
+        ms = np.zeros(7, np.float32); n = np.zeros(7, np.int32)
+        check(lib().moexb_ctx_profile_read(self.h, ms.ctypes.data, n.ctypes.data))
+        return ms, n
+
     def close(self):
         if self.h:
             lib().moexb_ctx_destroy(self.h)
@@ -194,3 +203,37 @@ class Layer:
         if self.h:
             lib().moexb_layer_destroy(self.h)
             self.h = None
+
+
+class Stack:
+    """moexb_stack: n layers chained as residual blocks for a fixed token count, replayed as one CUDA graph."""
+
+    def __init__(self, ctx, layers, T, K=8, x_dtype=F32):
+        arr = (C.c_void_p * len(layers))(*[l.h for l in layers])
+        h = C.c_void_p()
+        check(lib().moexb_stack_create(ctx.h, arr, len(layers), T, K, x_dtype, C.byref(h)))
+        self.h, self.T, self.layers, self.x_dtype = h, T, layers, x_dtype
+
+    @property
+    def kernel_count(self):
+        return lib().moexb_stack_kernel_count(self.h)
+
+    def run(self, X, out=None):
+        out = torch.empty(self.T, EH, device=X.device, dtype=torch.float32) if out is None else out
+        check(lib().moexb_stack_run(self.h, _ptr(X), _ptr(out), _stream()))
+        return out
+
+    def run_host(self, X_host, out_host):
+        """X_host / out_host: CPU tensors (pinned for full speed). Returns after the result has landed."""
+        assert not X_host.is_cuda and not out_host.is_cuda and X_host.is_contiguous() and out_host.is_contiguous()
+        check(lib().moexb_stack_run_host(self.h, X_host.data_ptr(), out_host.data_ptr(), _stream()))
+        return out_host
+
+    def close(self):
+        if self.h:
+            lib().moexb_stack_destroy(self.h)
+            self.h = None
+
+
+def launch_count():
+    return lib().moexb_launch_count()

@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -30,7 +31,9 @@ int fail(int code, const char* fmt, ...) {
 
 #define REQUIRE(cond, ...) do { if (!(cond)) return fail(MOEXB_ERR_ARG, __VA_ARGS__); } while (0)
 #define CUDA_TRY(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) return fail(MOEXB_ERR_CUDA, "%s: %s", #x, cudaGetErrorString(e_)); } while (0)
-#define LAUNCHED(name) do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return fail(MOEXB_ERR_CUDA, "launch of %s: %s", name, cudaGetErrorString(e_)); } while (0)
+#define LAUNCHED(name) do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return fail(MOEXB_ERR_CUDA, "launch of %s: %s", name, cudaGetErrorString(e_)); \
+    g_launches.fetch_add(1, std::memory_order_relaxed); } while (0)
+std::atomic<long long> g_launches{0};
 
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool fmt_ok(int fmt) { return fmt == FMT_SYM_F32 || fmt == FMT_SYM_F16 || fmt == FMT_ZP; }
@@ -83,7 +86,30 @@ struct moexb_ctx {
     const uint8_t** slots = nullptr;  // decode: K+1 blob pointers
     float* wts = nullptr;             // decode: K+1 weights
     std::vector<void*> owned;
+    // optional per-kernel timing of the layer-level calls
+    bool profiling = false;
+    struct Rec { int tag; cudaEvent_t a, b; };
+    std::vector<Rec> recs;
+    std::vector<cudaEvent_t> spare;
 };
+
+namespace {
+// Brackets the launches made inside its scope with two events on the stream when the context is profiling.
+struct ProfScope {
+    moexb_ctx* c; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; int tag;
+    ProfScope(moexb_ctx* c_, int tag_, cudaStream_t st_) : c(c_), st(st_), tag(tag_) {
+        if (!c || !c->profiling) return;
+        auto get = [&] { cudaEvent_t e; if (c->spare.empty()) cudaEventCreate(&e); else { e = c->spare.back(); c->spare.pop_back(); } return e; };
+        a = get(); b = get();
+        cudaEventRecord(a, st);
+    }
+    ~ProfScope() { if (a) { cudaEventRecord(b, st); c->recs.push_back({tag, a, b}); } }
+};
+}  // namespace
+
+#define PROF_CAT2(a, b) a##b
+#define PROF_CAT(a, b) PROF_CAT2(a, b)
+#define PROF(ctx, tag, stream) ProfScope PROF_CAT(prof_scope_, __LINE__)(ctx, tag, S(stream))
 
 struct moexb_layer {
     moexb_ctx* ctx = nullptr;
@@ -142,28 +168,40 @@ int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, flo
 
 // ---- routed experts ------------------------------------------------------------------------------------------------
 
-int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
-                          float* out, void* stream, const int* nh) {
+static int decode_launch(moexb_ctx* prof, int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
+                         float* out, void* stream, const int* nh) {
     REQUIRE(slots && w && x && act && out, "experts_forward: null pointer");
     REQUIRE(K > 0 && K <= 16, "experts_forward: K=%d out of range 1..16", K);
     return by_fmt(fmt, [&]<int FMT>() {
         constexpr int WARPS = 8;
-        decode_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, K), WARPS * 32, 0, S(stream)>>>(slots, K, nh, x, act);
-        LAUNCHED("decode_gate_up");
+        {
+            PROF(prof, MOEXB_PROF_GATE_UP, stream);
+            decode_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, K), WARPS * 32, 0, S(stream)>>>(slots, K, nh, x, act);
+            LAUNCHED("decode_gate_up");
+        }
+        PROF(prof, MOEXB_PROF_DOWN, stream);
         decode_down_k<FMT, WARPS, 16><<<EH / WARPS, WARPS * 32, K * pad32_size(EI) * sizeof(float), S(stream)>>>(slots, w, K, nh, act, out);
         LAUNCHED("decode_down");
         return (int)MOEXB_OK;
     });
 }
+int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
+                          float* out, void* stream, const int* nh) {
+    return decode_launch(nullptr, fmt, slots, w, K, x, act, out, stream, nh);
+}
 
-static int pairs_launch(int fmt, const moexb_pair_item* items, const int* nitems, int grid_items, const moexb_pair* pairs,
+static int pairs_launch(moexb_ctx* prof, int fmt, const moexb_pair_item* items, const int* nitems, int grid_items, const moexb_pair* pairs,
                         const float* X, float* act, float* ypair, void* stream) {
     REQUIRE(items && pairs && X && act && ypair, "pairs_forward: null pointer");
     REQUIRE(grid_items > 0 && grid_items <= 65535, "pairs_forward: %d items", grid_items);
     return by_fmt(fmt, [&]<int FMT>() {
         constexpr int WARPS = 8;
-        pairs_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, grid_items), WARPS * 32, 0, S(stream)>>>(items, pairs, X, act, nitems);
-        LAUNCHED("pairs_gate_up");
+        {
+            PROF(prof, MOEXB_PROF_GATE_UP, stream);
+            pairs_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, grid_items), WARPS * 32, 0, S(stream)>>>(items, pairs, X, act, nitems);
+            LAUNCHED("pairs_gate_up");
+        }
+        PROF(prof, MOEXB_PROF_DOWN, stream);
         pairs_down_k<FMT, WARPS><<<dim3(EH / WARPS, grid_items), WARPS * 32, 0, S(stream)>>>(items, pairs, act, ypair, nitems);
         LAUNCHED("pairs_down");
         return (int)MOEXB_OK;
@@ -172,12 +210,12 @@ static int pairs_launch(int fmt, const moexb_pair_item* items, const int* nitems
 int moexb_pairs_forward(int fmt, const moexb_pair_item* items, int n_items, const moexb_pair* pairs, const float* X,
                         float* act, float* ypair, void* stream) {
     if (n_items == 0) return fmt_ok(fmt) ? MOEXB_OK : fail(MOEXB_ERR_ARG, "unknown expert format %d", fmt);
-    return pairs_launch(fmt, items, nullptr, n_items, pairs, X, act, ypair, stream);
+    return pairs_launch(nullptr, fmt, items, nullptr, n_items, pairs, X, act, ypair, stream);
 }
 int moexb_pairs_forward_dev(int fmt, const moexb_pair_item* items, const int* nitems, int max_items,
                             const moexb_pair* pairs, const float* X, float* act, float* ypair, void* stream) {
     REQUIRE(nitems, "pairs_forward_dev: null item count");
-    return pairs_launch(fmt, items, nitems, max_items, pairs, X, act, ypair, stream);
+    return pairs_launch(nullptr, fmt, items, nitems, max_items, pairs, X, act, ypair, stream);
 }
 
 int moexb_pairs_reduce(const float* ypair, const float* ycpu, float* moe, int K, int D, int T, const int* use_cpu, void* stream) {
@@ -219,7 +257,7 @@ int moexb_shared_expert_add(int fmt, const uint8_t* blob, const float* gl, int g
     moexb_pair* pairs = reinterpret_cast<moexb_pair*>(item + 1);
     identity_pairs_k<<<(T + 255) / 256, 256, 0, S(stream)>>>(blob, T, item, pairs);
     LAUNCHED("identity_pairs");
-    int rc = pairs_launch(fmt, item, nullptr, 1, pairs, X, act, sh, stream);
+    int rc = pairs_launch(nullptr, fmt, item, nullptr, 1, pairs, X, act, sh, stream);
     if (rc != MOEXB_OK) return rc;
     gated_add_rows_k<<<dim3((EH + 255) / 256, T), 256, 0, S(stream)>>>(out, sh, gl, gl_stride, EH);
     LAUNCHED("gated_add_rows");
@@ -343,6 +381,8 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
 int moexb_ctx_destroy(moexb_ctx* ctx) {
     if (!ctx) return MOEXB_OK;
     for (void* p : ctx->owned) cudaFree(p);
+    for (auto& r : ctx->recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (auto e : ctx->spare) cudaEventDestroy(e);
     delete ctx;
     return MOEXB_OK;
 }
@@ -417,9 +457,14 @@ int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void*
 // Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
 static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode_slots) {
     const int E = L->n_routed, ld = E + 1;
-    int rc = L->router_dtype == MOEXB_F32 ? gemv_any(static_cast<const float*>(L->router), xf, c->logits, EH, ld, stream, T)
+    int rc;
+    {
+        PROF(c, MOEXB_PROF_ROUTER, stream);
+        rc = L->router_dtype == MOEXB_F32 ? gemv_any(static_cast<const float*>(L->router), xf, c->logits, EH, ld, stream, T)
                                           : gemv_any(static_cast<const __half*>(L->router), xf, c->logits, EH, ld, stream, T);
+    }
     if (rc != MOEXB_OK) return rc;
+    PROF(c, MOEXB_PROF_TOPK, stream);
     return topk_launch(c->logits, E, K, 1, c->idx, c->w, stream, T, ld, L->slot_table, decode_slots ? c->slots : nullptr, decode_slots ? c->wts : nullptr);
 }
 
@@ -437,12 +482,14 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     const size_t n = (size_t)T * EH;
     const float* xin;  // the layer input as f32
     if (x_dtype == MOEXB_BF16) {
+        PROF(c, MOEXB_PROF_OTHER, stream);
         bf16_to_f32_k<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), c->xf, n);
         LAUNCHED("bf16_to_f32");
         xin = c->xf;
     } else xin = static_cast<const float*>(X);
     const float* xf = xin;  // what the router and the experts see
     if (block) {
+        PROF(c, MOEXB_PROF_OTHER, stream);
         rmsnorm_rows_k<<<T, 256, 0, st>>>(xin, c->xn, EH, 1e-6f);
         LAUNCHED("rmsnorm");
         xf = c->xn;
@@ -453,28 +500,136 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     if (rc != MOEXB_OK) return rc;
     if (decode) {
         // one token: the K routed experts and the shared expert (weight sigmoid(gate logit)) as K+1 decode experts
-        rc = moexb_experts_forward(L->fmt, c->slots, c->wts, K + 1, xf, c->act, moe, stream, nullptr);
+        rc = decode_launch(c, L->fmt, c->slots, c->wts, K + 1, xf, c->act, moe, stream, nullptr);
         if (rc != MOEXB_OK) return rc;
     } else {
         constexpr int WARPS = 8;
-        group_count_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, T * K, E, c->counts);
-        LAUNCHED("group_count");
-        group_scatter_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->counts, c->items, c->pairs,
-                                                                                 c->nitems, shared ? c->logits + E : nullptr, ld);
-        LAUNCHED("group_scatter");
-        // pairs of experts that are not held here are never written: their ypair rows must read as zero
-        if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
-        rc = pairs_launch(L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
+        {
+            PROF(c, MOEXB_PROF_GROUP, stream);
+            group_count_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, T * K, E, c->counts);
+            LAUNCHED("group_count");
+            group_scatter_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->counts, c->items, c->pairs,
+                                                                                     c->nitems, shared ? c->logits + E : nullptr, ld);
+            LAUNCHED("group_scatter");
+            // pairs of experts that are not held here are never written: their ypair rows must read as zero
+            if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
+        }
+        rc = pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;
+        PROF(c, MOEXB_PROF_COMBINE, stream);
         rc = moexb_pairs_reduce(c->ypair, shared ? c->ypair + (size_t)T * K * EH : nullptr, moe, K, EH, T, nullptr, stream);
         if (rc != MOEXB_OK) return rc;
     }
     if (block) {
+        PROF(c, MOEXB_PROF_COMBINE, stream);
         residual_add_k<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(xin, c->moe, out, n);
         LAUNCHED("residual_add");
     }
     if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
     if (w_out) CUDA_TRY(cudaMemcpyAsync(w_out, c->w, (size_t)T * K * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return MOEXB_OK;
+}
+
+// ---- stack of layers as one CUDA graph ----------------------------------------------------------------------------------
+
+struct moexb_stack {
+    moexb_ctx* ctx = nullptr;
+    int T = 0, K = 0, x_dtype = 0, n_layers = 0, kernels = 0;
+    void* x_in = nullptr;        // [T][H] of x_dtype
+    float* buf[2] = {nullptr, nullptr};
+    float* result = nullptr;     // = buf[(n_layers - 1) & 1]
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaStream_t cap = nullptr;
+};
+
+int moexb_stack_destroy(moexb_stack* s) {
+    if (!s) return MOEXB_OK;
+    if (s->exec) cudaGraphExecDestroy(s->exec);
+    if (s->graph) cudaGraphDestroy(s->graph);
+    if (s->cap) cudaStreamDestroy(s->cap);
+    cudaFree(s->x_in); cudaFree(s->buf[0]); cudaFree(s->buf[1]);
+    delete s;
+    return MOEXB_OK;
+}
+
+int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, moexb_stack** out) {
+    REQUIRE(c && layers && out, "stack_create: null pointer");
+    REQUIRE(n_layers > 0 && T > 0 && T <= c->max_tokens && K > 0 && K <= c->top_k, "stack_create: n_layers=%d T=%d K=%d", n_layers, T, K);
+    REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "stack_create: x_dtype=%d", x_dtype);
+    REQUIRE(!c->profiling, "stack_create: switch profiling off before capturing a graph");
+    CUDA_TRY(cudaSetDevice(c->device));
+    moexb_stack* s = new (std::nothrow) moexb_stack;
+    if (!s) return fail(MOEXB_ERR_NOMEM, "out of host memory");
+    s->ctx = c; s->T = T; s->K = K; s->x_dtype = x_dtype; s->n_layers = n_layers;
+    const size_t n = (size_t)T * EH;
+    cudaError_t e = cudaMalloc(&s->x_in, n * (x_dtype == MOEXB_BF16 ? 2 : 4));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&s->buf[0], n * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&s->buf[1], n * 4);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->cap, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_NOMEM, "stack_create: %s", cudaGetErrorString(e)); }
+    const long long before = g_launches.load();
+    e = cudaStreamBeginCapture(s->cap, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "stack_create: begin capture: %s", cudaGetErrorString(e)); }
+    int rc = MOEXB_OK;
+    for (int l = 0; l < n_layers && rc == MOEXB_OK; l++)
+        rc = moexb_layer_forward(c, layers[l], l == 0 ? s->x_in : (const void*)s->buf[(l - 1) & 1], l == 0 ? x_dtype : MOEXB_F32, T, K,
+                                 s->buf[l & 1], nullptr, nullptr, 2, s->cap);
+    e = cudaStreamEndCapture(s->cap, &s->graph);
+    s->kernels = (int)(g_launches.load() - before);
+    g_launches.store(before);  // captured, not yet run
+    if (rc != MOEXB_OK) { moexb_stack_destroy(s); return rc; }
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&s->exec, s->graph, 0);
+    if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "stack_create: graph: %s", cudaGetErrorString(e)); }
+    s->result = s->buf[(n_layers - 1) & 1];
+    *out = s;
+    return MOEXB_OK;
+}
+
+int moexb_stack_kernel_count(moexb_stack* s) { return s ? s->kernels : 0; }
+
+int moexb_stack_run(moexb_stack* s, const void* X, float* out, void* stream) {
+    REQUIRE(s && X && out, "stack_run: null pointer");
+    const size_t n = (size_t)s->T * EH;
+    CUDA_TRY(cudaMemcpyAsync(s->x_in, X, n * (s->x_dtype == MOEXB_BF16 ? 2 : 4), cudaMemcpyDeviceToDevice, S(stream)));
+    CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
+    g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    CUDA_TRY(cudaMemcpyAsync(out, s->result, n * 4, cudaMemcpyDeviceToDevice, S(stream)));
+    return MOEXB_OK;
+}
+
+int moexb_stack_run_host(moexb_stack* s, const void* X_host, float* out_host, void* stream) {
+    REQUIRE(s && X_host && out_host, "stack_run_host: null pointer");
+    const size_t n = (size_t)s->T * EH;
+    CUDA_TRY(cudaMemcpyAsync(s->x_in, X_host, n * (s->x_dtype == MOEXB_BF16 ? 2 : 4), cudaMemcpyHostToDevice, S(stream)));
+    CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
+    g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    CUDA_TRY(cudaMemcpyAsync(out_host, s->result, n * 4, cudaMemcpyDeviceToHost, S(stream)));
+    CUDA_TRY(cudaStreamSynchronize(S(stream)));
+    return MOEXB_OK;
+}
+
+// ---- instrumentation ------------------------------------------------------------------------------------------------------
+
+long long moexb_launch_count(void) { return g_launches.load(); }
+
+int moexb_ctx_profile(moexb_ctx* c, int on) {
+    REQUIRE(c, "ctx_profile: null context");
+    c->profiling = on != 0;
+    return MOEXB_OK;
+}
+
+int moexb_ctx_profile_read(moexb_ctx* c, float* ms, int* launches) {
+    REQUIRE(c && ms && launches, "ctx_profile_read: null pointer");
+    CUDA_TRY(cudaDeviceSynchronize());
+    for (int i = 0; i < MOEXB_PROF_TAGS; i++) { ms[i] = 0.f; launches[i] = 0; }
+    for (auto& r : c->recs) {
+        float t = 0.f;
+        CUDA_TRY(cudaEventElapsedTime(&t, r.a, r.b));
+        ms[r.tag] += t; launches[r.tag]++;
+        c->spare.push_back(r.a); c->spare.push_back(r.b);
+    }
+    c->recs.clear();
     return MOEXB_OK;
 }
 
