@@ -83,6 +83,18 @@ int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, flo
 int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
                           float* out, void* stream, const int* nh);
 
+/* The same computation for callers that cannot allocate device memory (an engine that gave all free memory to its
+ * expert cache at load time, or a decode thread that must never block in cudaMalloc). It has no counterpart in the
+ * reference, which always receives `act` from its caller. The intermediate activations live in a fixed 32 KB array
+ * inside the library image, which every GPU that loads the library keeps until the process exits, so there is no
+ * `act` argument and K is limited to 16 experts per call (larger K is rejected with MOEXB_ERR_ARG). The function calls
+ * no allocator. The first call on each device looks up the array's device address; make that first call outside any
+ * stream capture. All calls on a device share the array, which keeps the previous call's values: nothing in it needs
+ * clearing between calls, but two calls whose kernels overlap on the GPU (different streams) race on it - keep them
+ * on one stream or order them with events. */
+int moexb_experts_forward_static(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* out,
+                                 void* stream, const int* nh);
+
 /* ---- routed experts, T tokens grouped by expert -------------------------------------------------------------------- */
 
 /* For every pair of every item: act[p][I] = silu(gate x_t) * (up x_t), ypair[p][H] = w * (down act[p]).

@@ -39,6 +39,7 @@ SIGNATURES = {
     "moexb_gemv_f32": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i]),
     "moexb_router_topk": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i]),
     "moexb_experts_forward": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "moexb_experts_forward_static": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward_dev": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "moexb_pairs_reduce": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),

@@ -634,3 +634,51 @@ int moexb_ctx_profile_read(moexb_ctx* c, float* ms, int* launches) {
 }
 
 }  // extern "C"
+
+// ---- one-token experts with built-in scratch ------------------------------------------------------------------------------
+//
+// moexb_experts_forward_static is for callers that cannot allocate device memory: an engine that sizes its expert cache
+// from whatever memory is free at load time has no bytes left to ask for afterwards, and code on a latency-critical
+// decode thread must not call cudaMalloc at all, because an allocation can block on the whole device.
+// moexb_experts_forward asks such a caller for an `act` buffer; this variant brings its own.
+
+namespace {
+constexpr int STATIC_MAX_K = 16;  // experts per call: the scratch holds STATIC_MAX_K x I floats = 32 KB
+constexpr int STATIC_MAX_DEVICES = 64;
+// act[k][I] of the call in flight. Every GPU that loads the library holds these 32 KB until the process exits.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address to hand to a kernel.
+static __device__ __align__(256) float g_static_act[STATIC_MAX_K * EI];
+std::mutex g_static_lock;
+float* g_static_ptr[STATIC_MAX_DEVICES];  // device address of g_static_act per device, resolved on first use
+}  // namespace
+
+extern "C" int moexb_experts_forward_static(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* out,
+                                            void* stream, const int* nh) {
+    REQUIRE(slots && w && x && out, "experts_forward_static: null pointer");
+    REQUIRE(K >= 1 && K <= STATIC_MAX_K, "experts_forward_static: K=%d exceeds the built-in scratch (at most %d experts per call)", K, STATIC_MAX_K);
+    REQUIRE(fmt_ok(fmt), "experts_forward_static: unknown expert format %d", fmt);
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "experts_forward_static: device %d out of range", dev);
+    float* act;
+    {
+        // Set-up, once per device and with that device current: ask the runtime where the array lives on this GPU.
+        std::lock_guard<std::mutex> lock(g_static_lock);
+        if (!g_static_ptr[dev]) {
+            void* p = nullptr;
+            CUDA_TRY(cudaGetSymbolAddress(&p, g_static_act));
+            REQUIRE(p, "experts_forward_static: the scratch array has no address on device %d", dev);
+            g_static_ptr[dev] = static_cast<float*>(p);
+        }
+        act = g_static_ptr[dev];
+    }
+    // Nothing in the array has to start at zero: the first kernel writes rows k < K (or < *nh), the second reads only those.
+    return by_fmt(fmt, [&]<int FMT>() {
+        constexpr int WARPS = 8;
+        decode_gate_up_k<FMT, WARPS><<<dim3(EI / WARPS, K), WARPS * 32, 0, S(stream)>>>(slots, K, nh, x, act);
+        LAUNCHED("decode_gate_up (static scratch)");
+        decode_down_k<FMT, WARPS, STATIC_MAX_K><<<EH / WARPS, WARPS * 32, K * pad32_size(EI) * sizeof(float), S(stream)>>>(slots, w, K, nh, act, out);
+        LAUNCHED("decode_down (static scratch)");
+        return (int)MOEXB_OK;
+    });
+}
