@@ -51,6 +51,9 @@ enum {
 /* Activation element types accepted by the layer-level calls. */
 enum { MOEXB_F32 = 0, MOEXB_BF16 = 1 };
 
+typedef struct moexb_ctx moexb_ctx;     /* one per process and device: stream-ordered workspace, synthetic tables */
+typedef struct moexb_layer moexb_layer; /* one MoE layer resident in HBM: E routed experts + 1 shared + router */
+
 /* Work list of the multi-token path, identical to kernels.cuh:688-689. */
 typedef struct { const uint8_t* slot; int start, count; } moexb_pair_item; /* pairs[start, start+count) use this expert */
 typedef struct { int t, p; float w; } moexb_pair;                          /* token row, output row of ypair, routing weight */
@@ -105,6 +108,12 @@ int moexb_pairs_forward(int fmt, const moexb_pair_item* items, int n_items, cons
 int moexb_pairs_forward_dev(int fmt, const moexb_pair_item* items, const int* nitems, int max_items,
                             const moexb_pair* pairs, const float* X, float* act, float* ypair, void* stream);
 
+/* The same work list on the tensor-core streaming kernels (bf16 mma.sync, weights exact, activations as bf16 hi + lo,
+ * fp32 accumulation and group scales). Stands behind pairs_forward_tc (kernels.cuh:780-965). Needs the context's
+ * workspace: T <= max_tokens rows in X, npairs <= max_tokens * (top_k + 1); act (fp32 [npairs][I]) may be null. */
+int moexb_pairs_forward_tc(moexb_ctx* ctx, int fmt, const moexb_pair_item* items, int n_items, const moexb_pair* pairs,
+                           const float* X, int T, int npairs, float* act, float* ypair, void* stream);
+
 /* moe[t][d] = sum_{r<K} ypair[t*K+r][d] (rank order) + (ycpu ? ycpu[t][d] : 0). Replaces pairs_reduce_k
  * (kernels.cuh:744-753). use_cpu: optional device flag, ycpu is added only if *use_cpu != 0. */
 int moexb_pairs_reduce(const float* ypair, const float* ycpu, float* moe, int K, int D, int T, const int* use_cpu,
@@ -142,9 +151,6 @@ int moexb_q4k_to_zp(const uint8_t* gate, const uint8_t* up, const uint8_t* down,
 
 /* ---- synthetic experts (seeded, identical bytes on host and device) ----------------------------------------------- */
 
-typedef struct moexb_ctx moexb_ctx;     /* one per process and device: stream-ordered workspace, synthetic tables */
-typedef struct moexb_layer moexb_layer; /* one MoE layer resident in HBM: E routed experts + 1 shared + router */
-
 /* Fill dst (device) with n consecutive experts e0..e0+n-1 of `layer` in format fmt (blob stride =
  * moexb_expert_bytes(fmt)); MOEXB_FMT_ZP experts are synthetic Q4_K super-blocks converted as moexb_q4k_to_zp does. */
 int moexb_synth_experts(moexb_ctx* ctx, int fmt, unsigned seed, int layer, int e0, int n, uint8_t* dst, void* stream);
@@ -159,6 +165,12 @@ int moexb_synth_q4k_host(unsigned seed, int layer, int expert, uint8_t* gate, ui
  * layer-level calls; their workspace (about max_tokens * (top_k + 1) * 10 KB) is allocated here, once. */
 int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moexb_ctx** out);
 int moexb_ctx_destroy(moexb_ctx* ctx);
+/* Which expert kernels the layer-level calls use: 0 = the streaming tensor-core kernels (default), 1 = the fp32 SIMT
+ * kernels (the restatement of the reference's pairs_forward / experts_forward, kept for cross-checks). */
+int moexb_ctx_set_path(moexb_ctx* ctx, int path);
+/* Waits for the device and reads the error word of the streaming kernels: 0 = none; 1 / 2 = a consumer warp / the producer
+ * warp gave up waiting on a pipeline barrier (every device-side wait is bounded). The word is cleared. */
+int moexb_ctx_status(moexb_ctx* ctx, int* status);
 
 /* Allocates the image of one layer: n_routed experts (ids 0..n_routed-1) and the shared expert (id n_routed), each a
  * blob of format fmt, plus the router [n_routed+1][H] (row n_routed = the shared expert's gate vector).

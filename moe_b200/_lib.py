@@ -42,6 +42,9 @@ SIGNATURES = {
     "moexb_experts_forward_static": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward_dev": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "moexb_pairs_forward_tc": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp]),
+    "moexb_ctx_set_path": (_i, [_vp, _i]),
+    "moexb_ctx_status": (_i, [_vp, C.POINTER(_i)]),
     "moexb_pairs_reduce": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "moexb_gated_add_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "moexb_shared_expert_add": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),

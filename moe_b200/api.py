@@ -145,6 +145,21 @@ class Context:
     def synth_experts(self, fmt, seed, layer, e0, n, dst):
         check(lib().moexb_synth_experts(self.h, fmt, seed, layer, e0, n, _ptr(dst), _stream()))
 
+    def set_path(self, path):
+        """0 = streaming tensor-core kernels (default), 1 = fp32 SIMT kernels."""
+        check(lib().moexb_ctx_set_path(self.h, path))
+
+    def status(self):
+        """Synchronises and returns the streaming kernels' error word (0 = fine)."""
+        st = C.c_int(0)
+        check(lib().moexb_ctx_status(self.h, C.byref(st)))
+        return st.value
+
+    def pairs_forward_tc(self, fmt, items, n_items, pairs, X, T, npairs, act, ypair):
+        """reference pairs_forward_tc (kernels.cuh:955) on the streaming kernels."""
+        check(lib().moexb_pairs_forward_tc(self.h, fmt, _ptr(items), n_items, _ptr(pairs), _ptr(X), T, npairs, _ptr(act), _ptr(ypair), _stream()))
+        return ypair
+
     def profile(self, on):
         check(lib().moexb_ctx_profile(self.h, int(on)))
 

@@ -4,6 +4,7 @@
 #include "router.cuh"
 #include "experts_simt.cuh"
 #include "formats.cuh"
+#include "stream.cuh"
 
 #include <cmath>
 #include <cstdarg>
@@ -85,6 +86,11 @@ struct moexb_ctx {
     moexb_pair* pairs = nullptr;
     const uint8_t** slots = nullptr;  // decode: K+1 blob pointers
     float* wts = nullptr;             // decode: K+1 weights
+    // streaming (tensor-core) path
+    __nv_bfloat16 *xs = nullptr, *act_split = nullptr;  // activations / act as bf16 hi+lo, permuted
+    moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
+    int *nsub = nullptr, *counters = nullptr, *err = nullptr;
+    int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
     std::vector<void*> owned;
     // optional per-kernel timing of the layer-level calls
     bool profiling = false;
@@ -369,6 +375,10 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->act, P * EI); A(&c->ypair, P * EH); A(&c->moe, T * EH);
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
+    A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
+    A(&c->nsub, 1); A(&c->counters, 2); A(&c->err, 1);
+    if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
+    if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
     if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
     const Tables& t = host_tables();
     cudaError_t e = cudaMemcpy(c->table_s, t.s, sizeof t.s, cudaMemcpyHostToDevice);
@@ -454,6 +464,78 @@ int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void*
     return synth_launch(L->fmt, seed, layer_index, L->n_routed, 1, L->image + (size_t)L->n_local * eb, L->ctx->table_s, L->ctx->table_d, stream);
 }
 
+}  // extern "C"
+
+// ---- streaming (tensor-core) expert path ------------------------------------------------------------------------------------
+
+template <int FMT, bool DOWN>
+static int stream_launch_one(moexb_ctx* c, const StreamArgs& a, void* stream) {
+    constexpr int NW = 4, STAGES = 5;
+    constexpr int SMEM = st_smem_bytes<FMT, NW, STAGES>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_k<FMT, DOWN, NW, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "stream kernel shared memory: %s", cudaGetErrorString(attr_err));
+    PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
+    stream_k<FMT, DOWN, NW, STAGES><<<2 * c->sms, (NW + 1) * 32, SMEM, S(stream)>>>(a);
+    LAUNCHED(DOWN ? "stream_down" : "stream_gate_up");
+    return MOEXB_OK;
+}
+
+// gate/up then down over the sub-items already planned in the context (subs, nsub, zeroed counters);
+// xs = the split activations [token][2][H]; act32 optional.
+static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream) {
+    StreamArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->counters, c->err};
+    return by_fmt(fmt, [&]<int FMT>() {
+        int rc = stream_launch_one<FMT, false>(c, a, stream);
+        if (rc != MOEXB_OK) return rc;
+        StreamArgs d = a;
+        d.xs = c->act_split; d.counter = c->counters + 1;
+        return stream_launch_one<FMT, true>(c, d, stream);
+    });
+}
+
+static int split_launch(moexb_ctx* c, const float* x, int rows, void* stream) {
+    PROF(c, MOEXB_PROF_OTHER, stream);
+    const size_t n = (size_t)rows * EH;
+    split_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(x, c->xs, EH, n);
+    LAUNCHED("split_rows");
+    return MOEXB_OK;
+}
+
+extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_item* items, int n_items, const moexb_pair* pairs,
+                                      const float* X, int T, int npairs, float* act, float* ypair, void* stream) {
+    REQUIRE(c && items && pairs && X && ypair, "pairs_forward_tc: null pointer");
+    REQUIRE(fmt_ok(fmt), "pairs_forward_tc: unknown expert format %d", fmt);
+    REQUIRE(T > 0 && T <= c->max_tokens, "pairs_forward_tc: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
+    REQUIRE(npairs > 0 && npairs <= c->max_tokens * (c->top_k + 1), "pairs_forward_tc: npairs=%d exceeds the context's capacity %d", npairs, c->max_tokens * (c->top_k + 1));
+    REQUIRE(n_items >= 0 && n_items <= c->max_experts + 1, "pairs_forward_tc: n_items=%d exceeds the context's capacity %d", n_items, c->max_experts + 1);
+    if (n_items == 0) return MOEXB_OK;
+    int rc = split_launch(c, X, T, stream);
+    if (rc != MOEXB_OK) return rc;
+    plan_subitems_k<<<1, 32, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub, c->counters);
+    LAUNCHED("plan_subitems");
+    return stream_experts(c, fmt, pairs, act, ypair, stream);
+}
+
+extern "C" int moexb_ctx_set_path(moexb_ctx* c, int path) {
+    REQUIRE(c && (path == 0 || path == 1), "ctx_set_path: path must be 0 (streaming) or 1 (fp32 SIMT)");
+    c->path = path;
+    return MOEXB_OK;
+}
+
+// Waits for the device and returns the error word of the streaming kernels (0 = none; 1 / 2 = a consumer / the producer
+// gave up waiting on a pipeline barrier), clearing it.
+extern "C" int moexb_ctx_status(moexb_ctx* c, int* status) {
+    REQUIRE(c && status, "ctx_status: null pointer");
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpy(status, c->err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status) CUDA_TRY(cudaMemset(c->err, 0, sizeof(int)));
+    return MOEXB_OK;
+}
+
+extern "C" {
+
 // Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
 static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode_slots) {
     const int E = L->n_routed, ld = E + 1;
@@ -498,9 +580,25 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     const bool decode = T == 1 && all_local && shared;
     int rc = layer_route(c, L, xf, T, K, stream, decode);
     if (rc != MOEXB_OK) return rc;
-    if (decode) {
+    const bool streaming = c->path == 0;
+    if (streaming) {
+        rc = split_launch(c, xf, T, stream);
+        if (rc != MOEXB_OK) return rc;
+    }
+    if (decode && !streaming) {
         // one token: the K routed experts and the shared expert (weight sigmoid(gate logit)) as K+1 decode experts
         rc = decode_launch(c, L->fmt, c->slots, c->wts, K + 1, xf, c->act, moe, stream, nullptr);
+        if (rc != MOEXB_OK) return rc;
+    } else if (decode) {
+        {
+            PROF(c, MOEXB_PROF_GROUP, stream);
+            plan_decode_k<<<1, 32, 0, st>>>(c->slots, c->wts, K + 1, nullptr, c->subs, c->pairs, c->nsub, c->counters);
+            LAUNCHED("plan_decode");
+        }
+        rc = stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
+        if (rc != MOEXB_OK) return rc;
+        PROF(c, MOEXB_PROF_COMBINE, stream);
+        rc = moexb_pairs_reduce(c->ypair, nullptr, moe, K + 1, EH, 1, nullptr, stream);
         if (rc != MOEXB_OK) return rc;
     } else {
         constexpr int WARPS = 8;
@@ -513,8 +611,13 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
             LAUNCHED("group_scatter");
             // pairs of experts that are not held here are never written: their ypair rows must read as zero
             if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
+            if (streaming) {
+                plan_subitems_k<<<1, 32, 0, st>>>(c->items, c->nitems, 0, c->subs, c->nsub, c->counters);
+                LAUNCHED("plan_subitems");
+            }
         }
-        rc = pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
+        rc = streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
+                       : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;
         PROF(c, MOEXB_PROF_COMBINE, stream);
         rc = moexb_pairs_reduce(c->ypair, shared ? c->ypair + (size_t)T * K * EH : nullptr, moe, K, EH, T, nullptr, stream);

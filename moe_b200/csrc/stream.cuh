@@ -1,0 +1,336 @@
+// Streaming expert kernels for 1..64 tokens: the bandwidth-bound skinny GEMM of the decode-size path.
+//
+// One kernel template serves both projections (gate/up with the SwiGLU epilogue, down with the routing-weight epilogue).
+// A persistent CTA has one producer warp and NW consumer warps. The producer pulls tiles from a global queue and streams
+// packed int4 rows through a ring of shared-memory stages with cp.async.bulk (the TMA bulk-copy engine), one 256-byte
+// row piece (512 weights = 8 scale groups) per copy, 64 pieces per stage, completion counted on an mbarrier; the scale
+// bytes of the same pieces follow with 16-byte cp.async copies on the same barrier. Consumer warps read 16 nibbles per
+// lane and row with 8-byte shared loads (the piece stride of 288 bytes keeps them conflict-free), turn them into exact
+// bf16 integers in registers (one lop3 + one bf16x2 subtract per two weights) and feed mma.sync.m16n8k16 with the
+// activations as the 8-wide operand. Activations arrive as bf16 hi + lo halves (16 significand bits) in adjacent
+// columns, so a lane adds its two accumulator columns to get one token's value; the fp32 scale of each 64-weight group
+// is applied to the group's partial sum on the accumulators, so weights stay exact. Sub-items hold at most 8
+// (token, expert) pairs = 16 columns = two n8 tiles; experts with more tokens are split and re-stream their weights
+// from L2.
+//
+// k-slot permutation: within a 64-weight group lane t of a quad owns nibbles 16t..16t+15 (two 32-bit words w = 0, 1);
+// the bf16x2 register P[i] of word w holds nibbles (8w+i, 8w+i+4). MMA (w, h) uses P[2h] for k-slots (2t, 2t+1) and
+// P[2h+1] for k-slots (2t+8, 2t+9). The activation rows are stored in the matching order: position
+// G*64 + w*32 + t*8 + e' holds input k = G*64 + 16t + 8w + e with e' = ((e & 3) << 1) | (e >> 2), so the four k-values
+// of both MMAs of a word are one 16-byte load per lane (see split_pos).
+#pragma once
+#include "common.cuh"
+
+namespace moexb {
+
+constexpr int ST_PIECE = 256;    // bytes of one row piece: 512 int4 weights
+constexpr int ST_STRIDE = 288;   // piece stride in shared memory (rows g..g+3 of a half-warp land on distinct banks)
+constexpr int ST_SC_PER_PIECE = 48;  // scale bytes per piece: zero point needs 16 x [sc, mn] + 2 x (d, dm) = 40, kept 16-byte aligned
+constexpr int ST_MAXP = 8;       // pairs per sub-item
+constexpr int ST_WAIT_LIMIT = 1 << 22;
+
+enum : int { ST_ERR_NONE = 0, ST_ERR_FULL_WAIT = 1, ST_ERR_EMPTY_WAIT = 2 };
+
+template <int FMT> constexpr int st_scale_bytes() { return FMT == FMT_SYM_F16 ? 16 : FMT == FMT_SYM_F32 ? 32 : 40; }
+template <int NW> constexpr int st_pieces() { return 16 * NW; }
+template <int FMT, int NW> constexpr int st_slot_bytes() { return st_pieces<NW>() * (ST_STRIDE + ST_SC_PER_PIECE); }
+template <int FMT, int NW, int STAGES> constexpr int st_smem_bytes() { return STAGES * st_slot_bytes<FMT, NW>() + 256; }
+
+// Position of input k inside a permuted activation row (see the header comment).
+__host__ __device__ constexpr int split_pos(int k) {
+    const int G = k >> 6, kl = k & 63, t = kl >> 4, w = (kl >> 3) & 1, e = kl & 7;
+    return G * 64 + w * 32 + t * 8 + (((e & 3) << 1) | (e >> 2));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ST_WAIT_LIMIT polls, records why, and lets the caller leave the kernel.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+    for (int i = 0; i < ST_WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Eight nibbles of q -> four bf16x2 registers P[i] = (nibble i, nibble i+4) as exact integers: (x & 0x000F000F) ^ C
+// puts each nibble into the mantissa of 128.0 (C also flips bit 3 of two's-complement nibbles, turning v into v + 8),
+// and subtracting 128 (or 136) leaves the integer.
+template <bool SIGNED>
+__device__ __forceinline__ void dq_word(uint32_t q, uint32_t (&P)[4]) {
+    constexpr uint32_t C = SIGNED ? 0x43084308u : 0x43004300u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t r;
+        asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6A;" : "=r"(r) : "r"(q >> (4 * i)), "r"(C));
+        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(P[i]) : "r"(r), "r"(C));
+    }
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct StreamArgs {
+    const moexb_pair_item* subs;  // sub-items: at most ST_MAXP pairs each
+    const int* nsub;              // device count of sub-items
+    const moexb_pair* pairs;
+    const __nv_bfloat16* xs;      // gate/up: activations [token][2][H] (hi, lo), permuted; down: act [pair p][2][I]
+    float* act32;                 // gate/up: optional fp32 copy of act [p][I]
+    __nv_bfloat16* act_split;     // gate/up output [p][2][I], permuted
+    float* ypair;                 // down output [p][H]
+    int* counter;                 // tile queue head, zero before launch
+    int* err;                     // error word: first failed wait
+};
+
+struct StageInfo { int sub, tin, ks, first; };
+
+// DOWN = false: tile = 8*NW gate rows + the same up rows, 4 stages (K slices of 512); act = silu(gate) * up.
+// DOWN = true : tile = 16*NW down rows, 1 stage (K = 512); ypair = w * (down . act).
+template <int FMT, bool DOWN, int NW, int STAGES>
+__global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
+    constexpr int PIECES = st_pieces<NW>();
+    constexpr int SLOT = st_slot_bytes<FMT, NW>();
+    constexpr int SCB = st_scale_bytes<FMT>();
+    constexpr int KS = DOWN ? 1 : 4;                                  // stages per tile
+    constexpr int TILES = DOWN ? EH / (16 * NW) : EI / (8 * NW);      // tiles per sub-item
+    constexpr bool Z = FMT == FMT_ZP;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * SLOT);  // full[STAGES], empty[STAGES]
+    StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(bars + s), 33); mbar_init(smem_u32(bars + STAGES + s), NW); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int ntiles = *a.nsub * TILES;
+
+    if (warp == NW) {
+        // ---- producer ----
+        int s = 0; uint32_t ph = 0;
+        while (true) {
+            int tile = 0;
+            if (lane == 0) tile = atomicAdd(a.counter, 1);
+            tile = __shfl_sync(0xffffffffu, tile, 0);
+            const bool done = tile >= ntiles;
+            const int sub = done ? -1 : tile / TILES, tin = done ? 0 : tile % TILES;
+            const uint8_t* slot = done ? nullptr : a.subs[sub].slot;
+            for (int ks = 0; ks < (done ? 1 : KS); ks++) {
+                const uint32_t full = smem_u32(bars + s), empty = smem_u32(bars + STAGES + s);
+                if (!mbar_wait(empty, ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) return;
+                if (lane == 0) {
+                    info[s] = {sub, tin, ks, ks == 0};
+                    mbar_arrive_expect_tx(full, done ? 0 : PIECES * ST_PIECE);
+                }
+                __syncwarp();
+                if (!done) {
+                    const uint32_t base = smem_u32(smem + s * SLOT);
+#pragma unroll
+                    for (int i = 0; i < PIECES / 32; i++) {
+                        const int pi = lane + 32 * i;
+                        size_t row = 0, c0;  // the piece's row in the blob's merged [gate | up | down] row space; its first 32-chunk
+                        const uint8_t* src;
+                        if (DOWN) {
+                            const int d = tin * (16 * NW) + pi;
+                            src = slot + DOWN_Q_OFF + (size_t)d * (EI / 2);
+                            c0 = DOWN_C_OFF + (size_t)d * (EI / 32);
+                        } else {
+                            const int wq = pi >> 4, m = pi & 15;
+                            row = (size_t)(m < 8 ? 0 : EI) + tin * (8 * NW) + wq * 8 + (m & 7);
+                            src = slot + row * (EH / 2) + ks * ST_PIECE;
+                            c0 = row * (EH / 32) + ks * 16;
+                        }
+                        bulk_g2s(base + pi * ST_STRIDE, src, ST_PIECE, full);
+                        const uint32_t sdst = base + PIECES * ST_STRIDE + pi * ST_SC_PER_PIECE;
+                        const uint8_t* sp = slot + Q_BYTES;
+                        if constexpr (FMT == FMT_SYM_F16) cp_async16(sdst, sp + (c0 / 2) * 2);
+                        else if constexpr (FMT == FMT_SYM_F32) { cp_async16(sdst, sp + (c0 / 2) * 4); cp_async16(sdst + 16, sp + (c0 / 2) * 4 + 16); }
+                        else { cp_async16(sdst, sp + c0 * 2); cp_async16(sdst + 16, sp + c0 * 2 + 16); cp_async8(sdst + 32, sp + CHUNKS * 2 + (c0 / 8) * 4); }
+                    }
+                }
+                cp_async_arrive_noinc(full);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            if (done) break;
+        }
+        // drain: wait until the consumers have released every slot, so no copy is in flight when the CTA exits
+        for (int i = 0; i < STAGES; i++) {
+            if (!mbar_wait(smem_u32(bars + STAGES + s), ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) return;
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        return;
+    }
+
+    // ---- consumers ----
+    const int g = lane >> 2, t = lane & 3, wq = warp;
+    float acc[2][4];
+    const uint4* xrow[2] = {nullptr, nullptr};
+    int cur_sub = -1, n = 0, nct = 0, start = 0;
+    int s = 0; uint32_t ph = 0;
+    while (true) {
+        const uint32_t full = smem_u32(bars + s), empty = smem_u32(bars + STAGES + s);
+        if (!mbar_wait(full, ph, a.err, ST_ERR_FULL_WAIT)) return;
+        const StageInfo inf = info[s];
+        if (inf.sub < 0) { __syncwarp(); if (lane == 0) mbar_arrive(empty); break; }
+        if (inf.sub != cur_sub) {
+            cur_sub = inf.sub;
+            const moexb_pair_item it = a.subs[cur_sub];
+            n = it.count; start = it.start; nct = (n + 3) >> 2;
+#pragma unroll
+            for (int ct = 0; ct < 2; ct++) {
+                const int j = 4 * ct + (g >> 1);
+                const moexb_pair pr = a.pairs[start + (j < n ? j : 0)];
+                const size_t r = DOWN ? (size_t)pr.p : (size_t)pr.t;
+                xrow[ct] = reinterpret_cast<const uint4*>(a.xs + (r * 2 + (g & 1)) * (DOWN ? EI : EH));
+            }
+        }
+        if (inf.first) {
+#pragma unroll
+            for (int ct = 0; ct < 2; ct++) acc[ct][0] = acc[ct][1] = acc[ct][2] = acc[ct][3] = 0.f;
+        }
+        const uint8_t* st = smem + s * SLOT;
+        const int pa = wq * 16 + g, pb = pa + 8;  // the lane's two row pieces: A rows g and g + 8
+        const uint8_t *sca = st + PIECES * ST_STRIDE + pa * ST_SC_PER_PIECE, *scb = st + PIECES * ST_STRIDE + pb * ST_SC_PER_PIECE;
+#pragma unroll 2
+        for (int G = 0; G < 8; G++) {
+            const uint2 qa = *reinterpret_cast<const uint2*>(st + pa * ST_STRIDE + G * 32 + t * 8);
+            const uint2 qb = *reinterpret_cast<const uint2*>(st + pb * ST_STRIDE + G * 32 + t * 8);
+            uint32_t Pa[2][4], Pb[2][4];
+            dq_word<!Z>(qa.x, Pa[0]); dq_word<!Z>(qa.y, Pa[1]);
+            dq_word<!Z>(qb.x, Pb[0]); dq_word<!Z>(qb.y, Pb[1]);
+            float sa, sb;
+            if constexpr (FMT == FMT_SYM_F16) { sa = __half2float(reinterpret_cast<const __half*>(sca)[G]); sb = __half2float(reinterpret_cast<const __half*>(scb)[G]); }
+            else if constexpr (FMT == FMT_SYM_F32) { sa = reinterpret_cast<const float*>(sca)[G]; sb = reinterpret_cast<const float*>(scb)[G]; }
+            const int Gg = inf.ks * 8 + G;  // group index along the row
+#pragma unroll
+            for (int ct = 0; ct < 2; ct++) {
+                if (ct < nct) {
+                    const uint4 B0 = __ldg(xrow[ct] + Gg * 8 + t), B1 = __ldg(xrow[ct] + Gg * 8 + 4 + t);
+                    if constexpr (!Z) {
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_bf16(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
+                        mma_bf16(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
+                        mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
+                        mma_bf16(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
+                        acc[ct][0] = fmaf(c[0], sa, acc[ct][0]); acc[ct][1] = fmaf(c[1], sa, acc[ct][1]);
+                        acc[ct][2] = fmaf(c[2], sb, acc[ct][2]); acc[ct][3] = fmaf(c[3], sb, acc[ct][3]);
+                    } else {
+                        // zero point: each 32-weight chunk has its own (s, m): w = s*u + m, so a group is two partial sums
+                        // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 2G, lanes t = 2,3 chunk 2G+1, and an
+                        // MMA mixes the quad's k-slots, so the two chunks are separated by zeroing the other half's
+                        // nibbles; sum(x) comes from an all-ones A fragment.
+                        const float2 dda = __half22float2(*reinterpret_cast<const __half2*>(sca + 32 + (G >> 2) * 4));
+                        const float2 ddb = __half22float2(*reinterpret_cast<const __half2*>(scb + 32 + (G >> 2) * 4));
+#pragma unroll
+                        for (int hc = 0; hc < 2; hc++) {
+                            const bool mine = (t >> 1) == hc;
+                            float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                            const uint32_t one = mine ? 0x3F803F80u : 0u;
+                            mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
+                            mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
+                            mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
+                            mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
+                            mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
+                            mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                            const int ch = 2 * G + hc;
+                            const float s_a = dda.x * (float)sca[2 * ch], m_a = dda.y * (float)(int8_t)sca[2 * ch + 1];
+                            const float s_b = ddb.x * (float)scb[2 * ch], m_b = ddb.y * (float)(int8_t)scb[2 * ch + 1];
+                            acc[ct][0] += fmaf(s_a, c[0], m_a * c1[0]); acc[ct][1] += fmaf(s_a, c[1], m_a * c1[1]);
+                            acc[ct][2] += fmaf(s_b, c[2], m_b * c1[2]); acc[ct][3] += fmaf(s_b, c[3], m_b * c1[3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty);
+        if (inf.ks == KS - 1) {
+            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) of tile ct belong to pair slot 4*ct + t
+#pragma unroll
+            for (int ct = 0; ct < 2; ct++) {
+                const int j = 4 * ct + t;
+                if (ct < nct && j < n) {
+                    const moexb_pair pr = a.pairs[start + j];
+                    const float va = acc[ct][0] + acc[ct][1], vb = acc[ct][2] + acc[ct][3];
+                    if (DOWN) {
+                        const int d = inf.tin * (16 * NW) + wq * 16 + g;
+                        a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
+                        a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
+                    } else {
+                        const int r = inf.tin * (8 * NW) + wq * 8 + g;
+                        const float v = va / (1.f + expf(-va)) * vb;
+                        if (a.act32) a.act32[(size_t)pr.p * EI + r] = v;
+                        const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                        __nv_bfloat16* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(r);
+                        dst[0] = hi; dst[EI] = lo;
+                    }
+                }
+            }
+        }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+}
+
+// x [rows][K] fp32 -> xs [rows][2][K] bf16: hi = bf16(x), lo = bf16(x - hi), both in the permuted order of split_pos.
+__global__ void split_rows_k(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, int K, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t r = i / K; const int k = (int)(i % K);
+    const float v = x[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    __nv_bfloat16* dst = xs + r * 2 * K + split_pos(k);
+    dst[0] = hi; dst[K] = lo;
+}
+
+// Sub-items of at most ST_MAXP pairs from the items of a work list; zeroes the two tile-queue heads. One block.
+__global__ void plan_subitems_k(const moexb_pair_item* __restrict__ items, const int* __restrict__ nitems_dev, int nitems_host,
+                                moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int* __restrict__ counters) {
+    if (threadIdx.x == 0) {
+        const int ni = nitems_dev ? *nitems_dev : nitems_host;
+        int ns = 0;
+        for (int i = 0; i < ni; i++) {
+            const moexb_pair_item it = items[i];
+            for (int c = 0; c < it.count; c += ST_MAXP) subs[ns++] = {it.slot, it.start + c, min(ST_MAXP, it.count - c)};
+        }
+        *nsub = ns;
+        counters[0] = 0; counters[1] = 0;
+    }
+}
+
+// One token: the K (or *nh) decode experts as sub-items of one pair each, pair k = (token 0, row k, weight w[k]).
+__global__ void plan_decode_k(const uint8_t* const* __restrict__ slots, const float* __restrict__ w, int K, const int* __restrict__ nh,
+                              moexb_pair_item* __restrict__ subs, moexb_pair* __restrict__ pairs, int* __restrict__ nsub, int* __restrict__ counters) {
+    const int k = threadIdx.x, n = nh ? *nh : K;
+    if (k < n) { subs[k] = {slots[k], k, 1}; pairs[k] = {0, k, w[k]}; }
+    if (k == 0) { *nsub = n; counters[0] = 0; counters[1] = 0; }
+}
+
+}  // namespace moexb

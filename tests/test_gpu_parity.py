@@ -1,8 +1,10 @@
 """Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs. Needs a B200.
 
 Bars: dequantised weights, router logits and selected expert ids bit-exact; routing weights to 1e-6; expert-FFN outputs
-within relative L2 error 1e-3 and max-abs error 2e-3 of the oracle's fp32 path (for the zero-point / Q4_K experts, whose
-synthetic outputs reach 1e6, the max-abs bar is scaled by max|ref| / 57, 57 being the largest symmetric-format output).
+within relative L2 error 1e-3 and max-abs error 2e-3 of the oracle's fp32 path. The absolute bar is stated for one
+layer's output on BASELINE's distributions (largest value about 57); where the reference values are larger than that - the
+zero-point / Q4_K experts, whose synthetic outputs reach 1e6, and the residual stream of a chained stack - it is scaled by
+max|ref| / 57, i.e. kept at the same 3.5e-5 of the largest value (one fp32 ulp at 1e6 is already 0.06).
 """
 import os
 import struct
@@ -29,7 +31,7 @@ def check_ffn(got, ref, fmt, what=""):
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
     rel_l2 = np.linalg.norm(got - ref) / (np.linalg.norm(ref) + 1e-30)
     max_abs = np.abs(got - ref).max()
-    bar = 2e-3 * (max(1.0, np.abs(ref).max() / 57.0) if fmt == m.FMT_ZP else 1.0)
+    bar = 2e-3 * max(1.0, np.abs(ref).max() / 57.0)
     assert rel_l2 <= 1e-3 and max_abs <= bar, f"{what}: rel-L2 {rel_l2:.3e} (bar 1e-3), max-abs {max_abs:.3e} (bar {bar:.3e})"
     return rel_l2, max_abs
 
@@ -167,6 +169,28 @@ def test_pairs_forward_ragged(experts, fmt):
     assert m.lib().moexb_pairs_forward(fmt, None, 0, None, None, None, None, None) == 0   # empty work list: nothing to do
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+def test_pairs_forward_tc_streaming(ctx, experts, fmt):
+    """The tensor-core streaming kernels on the same ragged work list (the reference checks its tensor-core path
+    against its GEMV pairs at 5e-3 of max, test_kernels.cu:540-542; the bar here is the FFN bar of this file)."""
+    host, devb = experts[fmt]
+    rng = np.random.default_rng(12)
+    T = 12
+    X = rng.standard_normal((T, 2048)).astype(np.float32)
+    items, pairs, jobs, npairs = make_work(rng, devb, [1, 2, 5, 9, 12, 3], T)
+    ref, act_ref = o.run_pairs(fmt, [(host[i], t, p, w) for i, t, p, w in jobs], X, npairs, want_act=True)
+    act = torch.zeros(npairs * 512, device=DEV); yp = torch.zeros(npairs * 2048, device=DEV)
+    ctx.pairs_forward_tc(fmt, dev(items.view(np.uint8)), len(items), dev(pairs.view(np.uint8)), dev(X), T, npairs, act, yp)
+    assert ctx.status() == 0
+    check_ffn(act.cpu().numpy().reshape(npairs, 512), act_ref, fmt, "streaming act")
+    check_ffn(yp.cpu().numpy().reshape(npairs, 2048), ref, fmt, "streaming ypair")
+    # and against the fp32 SIMT kernels, as the reference's PF1 test does
+    yp_simt = torch.zeros_like(yp); act2 = torch.zeros_like(act)
+    m.pairs_forward(fmt, dev(items.view(np.uint8)), len(items), dev(pairs.view(np.uint8)), dev(X), act2, yp_simt)
+    a, b = yp.cpu().numpy(), yp_simt.cpu().numpy()
+    assert np.abs(a - b).max() <= 5e-3 * np.abs(b).max()
+
+
 def test_pairs_reduce_and_gated_add():
     rng = np.random.default_rng(2)
     T, K, D = 5, 8, 2048
@@ -232,9 +256,11 @@ def layer_sym(ctx):
     L.close()
 
 
+@pytest.mark.parametrize("path", [0, 1])
 @pytest.mark.parametrize("T", [1, 4, 64])
-def test_layer_forward_symmetric(layer_sym, T):
+def test_layer_forward_symmetric(ctx, layer_sym, T, path):
     L, W, host = layer_sym
+    ctx.set_path(path)
     rng = np.random.default_rng(100 + T)
     X = rng.standard_normal((T, 2048)).astype(np.float32)
     idx = torch.empty(T, 8, dtype=torch.int32, device=DEV); w = torch.empty(T, 8, device=DEV)
@@ -242,7 +268,9 @@ def test_layer_forward_symmetric(layer_sym, T):
     ref, ri, rw, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X, 8)
     assert np.array_equal(idx.cpu().numpy(), ri)                      # selected experts: identical
     assert np.allclose(w.cpu().numpy(), rw, rtol=2e-6, atol=0)
-    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"layer T={T}")
+    ctx.set_path(0)
+    assert ctx.status() == 0
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"layer T={T} path={path}")
 
 
 def test_layer_forward_bf16_input_and_no_shared(layer_sym):
@@ -265,10 +293,13 @@ def test_layer_forward_zero_point(ctx):
     W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float16)
     L.set_router(W)
     host = [m.synth_expert_host(m.FMT_ZP, 1, 0, e) for e in range(E + 1)]
-    for T in (1, 5):
+    for T, path in ((1, 0), (5, 0), (1, 1), (5, 1)):
+        ctx.set_path(path)
         X = rng.standard_normal((T, 2048)).astype(np.float32)
         idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
         out = L.forward(dev(X), T, 8, idx=idx)
+        ctx.set_path(0)
+        assert ctx.status() == 0
         ref, ri, _, _ = o.layer_forward(m.FMT_ZP, host, W, X, 8)
         assert np.array_equal(idx.cpu().numpy(), ri)
         check_ffn(out.cpu().numpy(), ref, m.FMT_ZP, f"zero-point layer T={T}")
