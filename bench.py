@@ -178,8 +178,12 @@ def main():
     ap.add_argument("--workload", default="serve64", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.layers > 0:
+        T_, _, f_, x_ = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (T_, args.layers, f_, x_)
     if args.impl == "reference":
         return run_reference(args)
 

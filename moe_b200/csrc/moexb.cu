@@ -89,7 +89,7 @@ struct moexb_ctx {
     // streaming (tensor-core) path
     __nv_bfloat16 *xs = nullptr, *act_split = nullptr;  // activations / act as bf16 hi+lo, permuted
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
-    int *nsub = nullptr, *counters = nullptr, *err = nullptr;
+    int *nsub = nullptr, *err = nullptr;
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
     std::vector<void*> owned;
     // optional per-kernel timing of the layer-level calls
@@ -376,7 +376,7 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
     A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
-    A(&c->nsub, 1); A(&c->counters, 2); A(&c->err, 1);
+    A(&c->nsub, 1); A(&c->err, 1);
     if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
     if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
@@ -470,8 +470,8 @@ int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void*
 
 template <int FMT, bool DOWN>
 static int stream_launch_one(moexb_ctx* c, const StreamArgs& a, void* stream) {
-    constexpr int NW = 4, STAGES = 5;
-    constexpr int SMEM = st_smem_bytes<FMT, NW, STAGES>();
+    constexpr int NW = 4, STAGES = FMT == FMT_SYM_F16 ? 4 : 3;
+    constexpr int SMEM = st_smem_bytes<FMT, DOWN, NW, STAGES>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_k<FMT, DOWN, NW, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
@@ -482,15 +482,15 @@ static int stream_launch_one(moexb_ctx* c, const StreamArgs& a, void* stream) {
     return MOEXB_OK;
 }
 
-// gate/up then down over the sub-items already planned in the context (subs, nsub, zeroed counters);
+// gate/up then down over the sub-items already planned in the context (subs, nsub);
 // xs = the split activations [token][2][H]; act32 optional.
 static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream) {
-    StreamArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->counters, c->err};
+    StreamArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->err};
     return by_fmt(fmt, [&]<int FMT>() {
         int rc = stream_launch_one<FMT, false>(c, a, stream);
         if (rc != MOEXB_OK) return rc;
         StreamArgs d = a;
-        d.xs = c->act_split; d.counter = c->counters + 1;
+        d.xs = c->act_split;
         return stream_launch_one<FMT, true>(c, d, stream);
     });
 }
@@ -513,7 +513,7 @@ extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_it
     if (n_items == 0) return MOEXB_OK;
     int rc = split_launch(c, X, T, stream);
     if (rc != MOEXB_OK) return rc;
-    plan_subitems_k<<<1, 32, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub, c->counters);
+    plan_subitems_k<<<1, 1024, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub);
     LAUNCHED("plan_subitems");
     return stream_experts(c, fmt, pairs, act, ypair, stream);
 }
@@ -592,7 +592,7 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     } else if (decode) {
         {
             PROF(c, MOEXB_PROF_GROUP, stream);
-            plan_decode_k<<<1, 32, 0, st>>>(c->slots, c->wts, K + 1, nullptr, c->subs, c->pairs, c->nsub, c->counters);
+            plan_decode_k<<<1, 32, 0, st>>>(c->slots, c->wts, K + 1, nullptr, c->subs, c->pairs, c->nsub);
             LAUNCHED("plan_decode");
         }
         rc = stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
@@ -612,7 +612,7 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
             // pairs of experts that are not held here are never written: their ypair rows must read as zero
             if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
             if (streaming) {
-                plan_subitems_k<<<1, 32, 0, st>>>(c->items, c->nitems, 0, c->subs, c->nsub, c->counters);
+                plan_subitems_k<<<1, 1024, 0, st>>>(c->items, c->nitems, 0, c->subs, c->nsub);
                 LAUNCHED("plan_subitems");
             }
         }

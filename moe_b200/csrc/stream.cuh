@@ -9,9 +9,10 @@
 // bf16 integers in registers (one lop3 + one bf16x2 subtract per two weights) and feed mma.sync.m16n8k16 with the
 // activations as the 8-wide operand. Activations arrive as bf16 hi + lo halves (16 significand bits) in adjacent
 // columns, so a lane adds its two accumulator columns to get one token's value; the fp32 scale of each 64-weight group
-// is applied to the group's partial sum on the accumulators, so weights stay exact. Sub-items hold at most 8
-// (token, expert) pairs = 16 columns = two n8 tiles; experts with more tokens are split and re-stream their weights
-// from L2.
+// is applied to the group's partial sum on the accumulators, so weights stay exact. Sub-items hold at most 4
+// (token, expert) pairs = 8 columns = one n8 tile; experts with more tokens are split and re-stream their weights
+// from L2. The 8 activation columns of the current sub-item sit in shared memory (the consumer warps copy them in when
+// the sub-item changes); every CTA works on a contiguous range of tiles, so that happens once or twice per launch.
 //
 // k-slot permutation: within a 64-weight group lane t of a quad owns nibbles 16t..16t+15 (two 32-bit words w = 0, 1);
 // the bf16x2 register P[i] of word w holds nibbles (8w+i, 8w+i+4). MMA (w, h) uses P[2h] for k-slots (2t, 2t+1) and
@@ -25,16 +26,18 @@ namespace moexb {
 
 constexpr int ST_PIECE = 256;    // bytes of one row piece: 512 int4 weights
 constexpr int ST_STRIDE = 288;   // piece stride in shared memory (rows g..g+3 of a half-warp land on distinct banks)
-constexpr int ST_SC_PER_PIECE = 48;  // scale bytes per piece: zero point needs 16 x [sc, mn] + 2 x (d, dm) = 40, kept 16-byte aligned
-constexpr int ST_MAXP = 8;       // pairs per sub-item
+constexpr int ST_SC_PER_PIECE = 48;  // zero point: 16 x [sc, mn] + 2 x (d, dm) = 40 scale bytes per piece, kept 16-byte aligned
+constexpr int ST_MAXP = 4;       // pairs per sub-item: 4 x (hi, lo) = the 8 columns of one MMA tile
 constexpr int ST_WAIT_LIMIT = 1 << 22;
 
 enum : int { ST_ERR_NONE = 0, ST_ERR_FULL_WAIT = 1, ST_ERR_EMPTY_WAIT = 2 };
 
-template <int FMT> constexpr int st_scale_bytes() { return FMT == FMT_SYM_F16 ? 16 : FMT == FMT_SYM_F32 ? 32 : 40; }
+template <int FMT> constexpr int st_scale_bytes() { return FMT == FMT_SYM_F16 ? 16 : FMT == FMT_SYM_F32 ? 32 : ST_SC_PER_PIECE; }
 template <int NW> constexpr int st_pieces() { return 16 * NW; }
-template <int FMT, int NW> constexpr int st_slot_bytes() { return st_pieces<NW>() * (ST_STRIDE + ST_SC_PER_PIECE); }
-template <int FMT, int NW, int STAGES> constexpr int st_smem_bytes() { return STAGES * st_slot_bytes<FMT, NW>() + 256; }
+template <int FMT, int NW> constexpr int st_slot_bytes() { return st_pieces<NW>() * (ST_STRIDE + st_scale_bytes<FMT>()); }
+// activation columns in shared memory: 8 columns of K bf16, column stride K*2 + 64 bytes (conflict-free 16-byte reads)
+template <bool DOWN> constexpr int st_bcol_bytes() { return (DOWN ? EI : EH) * 2 + 64; }
+template <int FMT, bool DOWN, int NW, int STAGES> constexpr int st_smem_bytes() { return STAGES * st_slot_bytes<FMT, NW>() + 8 * st_bcol_bytes<DOWN>() + 256; }
 
 // Position of input k inside a permuted activation row (see the header comment).
 __host__ __device__ constexpr int split_pos(int k) {
@@ -106,7 +109,6 @@ struct StreamArgs {
     float* act32;                 // gate/up: optional fp32 copy of act [p][I]
     __nv_bfloat16* act_split;     // gate/up output [p][2][I], permuted
     float* ypair;                 // down output [p][H]
-    int* counter;                 // tile queue head, zero before launch
     int* err;                     // error word: first failed wait
 };
 
@@ -114,16 +116,20 @@ struct StageInfo { int sub, tin, ks, first; };
 
 // DOWN = false: tile = 8*NW gate rows + the same up rows, 4 stages (K slices of 512); act = silu(gate) * up.
 // DOWN = true : tile = 16*NW down rows, 1 stage (K = 512); ypair = w * (down . act).
+// CTA c of G works on tiles [c*U/G, (c+1)*U/G) of the U = nsub * TILES tiles, in order.
 template <int FMT, bool DOWN, int NW, int STAGES>
 __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
     constexpr int PIECES = st_pieces<NW>();
-    constexpr int SLOT = st_slot_bytes<FMT, NW>();
     constexpr int SCB = st_scale_bytes<FMT>();
+    constexpr int SLOT = st_slot_bytes<FMT, NW>();
     constexpr int KS = DOWN ? 1 : 4;                                  // stages per tile
     constexpr int TILES = DOWN ? EH / (16 * NW) : EI / (8 * NW);      // tiles per sub-item
+    constexpr int KB = DOWN ? EI : EH;                                // inputs per activation row
+    constexpr int BCOL = st_bcol_bytes<DOWN>();
     constexpr bool Z = FMT == FMT_ZP;
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * SLOT);  // full[STAGES], empty[STAGES]
+    uint8_t* bsm = smem + STAGES * SLOT;                                     // 8 activation columns
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);            // full[STAGES], empty[STAGES]
     StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * STAGES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -131,16 +137,14 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    const int ntiles = *a.nsub * TILES;
+    const long long U = (long long)*a.nsub * TILES;
+    const int tile0 = (int)(U * blockIdx.x / gridDim.x), tile1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
 
     if (warp == NW) {
-        // ---- producer ----
+        // ---- producer: one warp streams the tiles' row pieces and scale bytes into the ring ----
         int s = 0; uint32_t ph = 0;
-        while (true) {
-            int tile = 0;
-            if (lane == 0) tile = atomicAdd(a.counter, 1);
-            tile = __shfl_sync(0xffffffffu, tile, 0);
-            const bool done = tile >= ntiles;
+        for (int tile = tile0; tile <= tile1; tile++) {
+            const bool done = tile == tile1;  // one empty stage after the last tile tells the consumers to stop
             const int sub = done ? -1 : tile / TILES, tin = done ? 0 : tile % TILES;
             const uint8_t* slot = done ? nullptr : a.subs[sub].slot;
             for (int ks = 0; ks < (done ? 1 : KS); ks++) {
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
 #pragma unroll
                     for (int i = 0; i < PIECES / 32; i++) {
                         const int pi = lane + 32 * i;
-                        size_t row = 0, c0;  // the piece's row in the blob's merged [gate | up | down] row space; its first 32-chunk
+                        size_t c0;  // first 32-weight chunk of the piece inside the blob
                         const uint8_t* src;
                         if (DOWN) {
                             const int d = tin * (16 * NW) + pi;
@@ -164,12 +168,12 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
                             c0 = DOWN_C_OFF + (size_t)d * (EI / 32);
                         } else {
                             const int wq = pi >> 4, m = pi & 15;
-                            row = (size_t)(m < 8 ? 0 : EI) + tin * (8 * NW) + wq * 8 + (m & 7);
+                            const size_t row = (size_t)(m < 8 ? 0 : EI) + tin * (8 * NW) + wq * 8 + (m & 7);  // row in [gate | up]
                             src = slot + row * (EH / 2) + ks * ST_PIECE;
                             c0 = row * (EH / 32) + ks * 16;
                         }
                         bulk_g2s(base + pi * ST_STRIDE, src, ST_PIECE, full);
-                        const uint32_t sdst = base + PIECES * ST_STRIDE + pi * ST_SC_PER_PIECE;
+                        const uint32_t sdst = base + PIECES * ST_STRIDE + pi * SCB;
                         const uint8_t* sp = slot + Q_BYTES;
                         if constexpr (FMT == FMT_SYM_F16) cp_async16(sdst, sp + (c0 / 2) * 2);
                         else if constexpr (FMT == FMT_SYM_F32) { cp_async16(sdst, sp + (c0 / 2) * 4); cp_async16(sdst + 16, sp + (c0 / 2) * 4 + 16); }
@@ -179,9 +183,8 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
                 cp_async_arrive_noinc(full);
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
-            if (done) break;
         }
-        // drain: wait until the consumers have released every slot, so no copy is in flight when the CTA exits
+        // drain: every slot released, so no copy is in flight when the CTA exits
         for (int i = 0; i < STAGES; i++) {
             if (!mbar_wait(smem_u32(bars + STAGES + s), ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) return;
             if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -191,108 +194,100 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
 
     // ---- consumers ----
     const int g = lane >> 2, t = lane & 3, wq = warp;
-    float acc[2][4];
-    const uint4* xrow[2] = {nullptr, nullptr};
-    int cur_sub = -1, n = 0, nct = 0, start = 0;
+    const int ctid = threadIdx.x;  // 0 .. NW*32-1
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int cur_sub = -1, n = 0, start = 0;
     int s = 0; uint32_t ph = 0;
+    const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
     while (true) {
         const uint32_t full = smem_u32(bars + s), empty = smem_u32(bars + STAGES + s);
         if (!mbar_wait(full, ph, a.err, ST_ERR_FULL_WAIT)) return;
         const StageInfo inf = info[s];
         if (inf.sub < 0) { __syncwarp(); if (lane == 0) mbar_arrive(empty); break; }
         if (inf.sub != cur_sub) {
+            // new sub-item: all consumer warps swap the activation columns (the weights keep streaming meanwhile)
             cur_sub = inf.sub;
             const moexb_pair_item it = a.subs[cur_sub];
-            n = it.count; start = it.start; nct = (n + 3) >> 2;
-#pragma unroll
-            for (int ct = 0; ct < 2; ct++) {
-                const int j = 4 * ct + (g >> 1);
-                const moexb_pair pr = a.pairs[start + (j < n ? j : 0)];
+            n = it.count; start = it.start;
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");  // everyone is done with the old columns
+            constexpr int CHUNKS16 = KB * 2 / 16;                        // 16-byte chunks per column
+            for (int i = ctid; i < 2 * n * CHUNKS16; i += NW * 32) {
+                const int col = i / CHUNKS16, ch = i % CHUNKS16;
+                const moexb_pair pr = a.pairs[start + (col >> 1)];
                 const size_t r = DOWN ? (size_t)pr.p : (size_t)pr.t;
-                xrow[ct] = reinterpret_cast<const uint4*>(a.xs + (r * 2 + (g & 1)) * (DOWN ? EI : EH));
+                cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (r * 2 + (col & 1)) * KB + ch * 8);
             }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
         }
-        if (inf.first) {
-#pragma unroll
-            for (int ct = 0; ct < 2; ct++) acc[ct][0] = acc[ct][1] = acc[ct][2] = acc[ct][3] = 0.f;
-        }
+        if (inf.first) acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
         const uint8_t* st = smem + s * SLOT;
         const int pa = wq * 16 + g, pb = pa + 8;  // the lane's two row pieces: A rows g and g + 8
-        const uint8_t *sca = st + PIECES * ST_STRIDE + pa * ST_SC_PER_PIECE, *scb = st + PIECES * ST_STRIDE + pb * ST_SC_PER_PIECE;
-#pragma unroll 2
+        const uint8_t *sca = st + PIECES * ST_STRIDE + pa * SCB, *scb = st + PIECES * ST_STRIDE + pb * SCB;
+        const uint8_t *qpa = st + pa * ST_STRIDE + t * 8, *qpb = st + pb * ST_STRIDE + t * 8;
+        const uint8_t* bp = bcol + inf.ks * 1024;  // 8 groups of 128 bytes per stage
+#pragma unroll 4
         for (int G = 0; G < 8; G++) {
-            const uint2 qa = *reinterpret_cast<const uint2*>(st + pa * ST_STRIDE + G * 32 + t * 8);
-            const uint2 qb = *reinterpret_cast<const uint2*>(st + pb * ST_STRIDE + G * 32 + t * 8);
+            const uint2 qa = *reinterpret_cast<const uint2*>(qpa + G * 32);
+            const uint2 qb = *reinterpret_cast<const uint2*>(qpb + G * 32);
+            const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
             uint32_t Pa[2][4], Pb[2][4];
             dq_word<!Z>(qa.x, Pa[0]); dq_word<!Z>(qa.y, Pa[1]);
             dq_word<!Z>(qb.x, Pb[0]); dq_word<!Z>(qb.y, Pb[1]);
-            float sa, sb;
-            if constexpr (FMT == FMT_SYM_F16) { sa = __half2float(reinterpret_cast<const __half*>(sca)[G]); sb = __half2float(reinterpret_cast<const __half*>(scb)[G]); }
-            else if constexpr (FMT == FMT_SYM_F32) { sa = reinterpret_cast<const float*>(sca)[G]; sb = reinterpret_cast<const float*>(scb)[G]; }
-            const int Gg = inf.ks * 8 + G;  // group index along the row
+            if constexpr (!Z) {
+                float sa, sb;
+                if constexpr (FMT == FMT_SYM_F16) { sa = __half2float(reinterpret_cast<const __half*>(sca)[G]); sb = __half2float(reinterpret_cast<const __half*>(scb)[G]); }
+                else { sa = reinterpret_cast<const float*>(sca)[G]; sb = reinterpret_cast<const float*>(scb)[G]; }
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};  // two chains, so consecutive MMAs do not wait on each other
+                mma_bf16(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
+                mma_bf16(e, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
+                mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
+                mma_bf16(e, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
+                acc[0] = fmaf(c[0] + e[0], sa, acc[0]); acc[1] = fmaf(c[1] + e[1], sa, acc[1]);
+                acc[2] = fmaf(c[2] + e[2], sb, acc[2]); acc[3] = fmaf(c[3] + e[3], sb, acc[3]);
+            } else {
+                // zero point: each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial sums
+                // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 2G, lanes t = 2,3 chunk 2G+1, and an MMA mixes
+                // the quad's k-slots, so the chunks are separated by zeroing the other half's nibbles; sum(x) comes
+                // from an all-ones A fragment.
+                const float2 dda = __half22float2(*reinterpret_cast<const __half2*>(sca + 32 + (G >> 2) * 4));
+                const float2 ddb = __half22float2(*reinterpret_cast<const __half2*>(scb + 32 + (G >> 2) * 4));
 #pragma unroll
-            for (int ct = 0; ct < 2; ct++) {
-                if (ct < nct) {
-                    const uint4 B0 = __ldg(xrow[ct] + Gg * 8 + t), B1 = __ldg(xrow[ct] + Gg * 8 + 4 + t);
-                    if constexpr (!Z) {
-                        float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_bf16(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
-                        mma_bf16(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
-                        mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
-                        mma_bf16(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
-                        acc[ct][0] = fmaf(c[0], sa, acc[ct][0]); acc[ct][1] = fmaf(c[1], sa, acc[ct][1]);
-                        acc[ct][2] = fmaf(c[2], sb, acc[ct][2]); acc[ct][3] = fmaf(c[3], sb, acc[ct][3]);
-                    } else {
-                        // zero point: each 32-weight chunk has its own (s, m): w = s*u + m, so a group is two partial sums
-                        // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 2G, lanes t = 2,3 chunk 2G+1, and an
-                        // MMA mixes the quad's k-slots, so the two chunks are separated by zeroing the other half's
-                        // nibbles; sum(x) comes from an all-ones A fragment.
-                        const float2 dda = __half22float2(*reinterpret_cast<const __half2*>(sca + 32 + (G >> 2) * 4));
-                        const float2 ddb = __half22float2(*reinterpret_cast<const __half2*>(scb + 32 + (G >> 2) * 4));
-#pragma unroll
-                        for (int hc = 0; hc < 2; hc++) {
-                            const bool mine = (t >> 1) == hc;
-                            float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-                            const uint32_t one = mine ? 0x3F803F80u : 0u;
-                            mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
-                            mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
-                            mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
-                            mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
-                            mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
-                            mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
-                            const int ch = 2 * G + hc;
-                            const float s_a = dda.x * (float)sca[2 * ch], m_a = dda.y * (float)(int8_t)sca[2 * ch + 1];
-                            const float s_b = ddb.x * (float)scb[2 * ch], m_b = ddb.y * (float)(int8_t)scb[2 * ch + 1];
-                            acc[ct][0] += fmaf(s_a, c[0], m_a * c1[0]); acc[ct][1] += fmaf(s_a, c[1], m_a * c1[1]);
-                            acc[ct][2] += fmaf(s_b, c[2], m_b * c1[2]); acc[ct][3] += fmaf(s_b, c[3], m_b * c1[3]);
-                        }
-                    }
+                for (int hc = 0; hc < 2; hc++) {
+                    const bool mine = (t >> 1) == hc;
+                    float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint32_t one = mine ? 0x3F803F80u : 0u;
+                    mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
+                    mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
+                    mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
+                    mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
+                    mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
+                    mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                    const int ch = 2 * G + hc;
+                    const float s_a = dda.x * (float)sca[2 * ch], m_a = dda.y * (float)(int8_t)sca[2 * ch + 1];
+                    const float s_b = ddb.x * (float)scb[2 * ch], m_b = ddb.y * (float)(int8_t)scb[2 * ch + 1];
+                    acc[0] += fmaf(s_a, c[0], m_a * c1[0]); acc[1] += fmaf(s_a, c[1], m_a * c1[1]);
+                    acc[2] += fmaf(s_b, c[2], m_b * c1[2]); acc[3] += fmaf(s_b, c[3], m_b * c1[3]);
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty);
-        if (inf.ks == KS - 1) {
-            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) of tile ct belong to pair slot 4*ct + t
-#pragma unroll
-            for (int ct = 0; ct < 2; ct++) {
-                const int j = 4 * ct + t;
-                if (ct < nct && j < n) {
-                    const moexb_pair pr = a.pairs[start + j];
-                    const float va = acc[ct][0] + acc[ct][1], vb = acc[ct][2] + acc[ct][3];
-                    if (DOWN) {
-                        const int d = inf.tin * (16 * NW) + wq * 16 + g;
-                        a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
-                        a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
-                    } else {
-                        const int r = inf.tin * (8 * NW) + wq * 8 + g;
-                        const float v = va / (1.f + expf(-va)) * vb;
-                        if (a.act32) a.act32[(size_t)pr.p * EI + r] = v;
-                        const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-                        __nv_bfloat16* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(r);
-                        dst[0] = hi; dst[EI] = lo;
-                    }
-                }
+        if (inf.ks == KS - 1 && t < n) {
+            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) belong to pair slot t
+            const moexb_pair pr = a.pairs[start + t];
+            const float va = acc[0] + acc[1], vb = acc[2] + acc[3];
+            if (DOWN) {
+                const int d = inf.tin * (16 * NW) + wq * 16 + g;
+                a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
+                a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
+            } else {
+                const int r = inf.tin * (8 * NW) + wq * 8 + g;
+                const float v = va / (1.f + expf(-va)) * vb;
+                if (a.act32) a.act32[(size_t)pr.p * EI + r] = v;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                __nv_bfloat16* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(r);
+                dst[0] = hi; dst[EI] = lo;
             }
         }
         if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -310,27 +305,49 @@ __global__ void split_rows_k(const float* __restrict__ x, __nv_bfloat16* __restr
     dst[0] = hi; dst[K] = lo;
 }
 
-// Sub-items of at most ST_MAXP pairs from the items of a work list; zeroes the two tile-queue heads. One block.
-__global__ void plan_subitems_k(const moexb_pair_item* __restrict__ items, const int* __restrict__ nitems_dev, int nitems_host,
-                                moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int* __restrict__ counters) {
-    if (threadIdx.x == 0) {
-        const int ni = nitems_dev ? *nitems_dev : nitems_host;
-        int ns = 0;
-        for (int i = 0; i < ni; i++) {
-            const moexb_pair_item it = items[i];
-            for (int c = 0; c < it.count; c += ST_MAXP) subs[ns++] = {it.slot, it.start + c, min(ST_MAXP, it.count - c)};
-        }
-        *nsub = ns;
-        counters[0] = 0; counters[1] = 0;
+// Exclusive prefix sum over the 1024 threads of a block; every thread also gets the total.
+__device__ __forceinline__ int block_scan_1024(int v, int& total) {
+    __shared__ int wsum[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += u; }
+    __syncthreads();  // wsum may still be read by a previous scan
+    if (lane == 31) wsum[w] = inc;
+    __syncthreads();
+    int ws = wsum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, ws, o); if (lane >= o) ws += u; }
+    total = __shfl_sync(0xffffffffu, ws, 31);
+    const int before = __shfl_sync(0xffffffffu, ws, (w + 31) & 31);
+    return inc - v + (w ? before : 0);
+}
+
+// Sub-items of at most ST_MAXP pairs from the items of a work list. One block of 1024 threads, one item per thread
+// and pass.
+__global__ void __launch_bounds__(1024) plan_subitems_k(const moexb_pair_item* __restrict__ items, const int* __restrict__ nitems_dev, int nitems_host,
+                                                        moexb_pair_item* __restrict__ subs, int* __restrict__ nsub) {
+    const int ni = nitems_dev ? *nitems_dev : nitems_host;
+    int done = 0;
+    for (int base = 0; base < ni; base += 1024) {
+        const int i = base + threadIdx.x;
+        moexb_pair_item it = {nullptr, 0, 0};
+        if (i < ni) it = items[i];
+        const int mine = (it.count + ST_MAXP - 1) / ST_MAXP;
+        int total;
+        const int at = done + block_scan_1024(mine, total);
+        for (int j = 0; j < mine; j++) subs[at + j] = {it.slot, it.start + j * ST_MAXP, min(ST_MAXP, it.count - j * ST_MAXP)};
+        done += total;
     }
+    if (threadIdx.x == 0) *nsub = done;
 }
 
 // One token: the K (or *nh) decode experts as sub-items of one pair each, pair k = (token 0, row k, weight w[k]).
 __global__ void plan_decode_k(const uint8_t* const* __restrict__ slots, const float* __restrict__ w, int K, const int* __restrict__ nh,
-                              moexb_pair_item* __restrict__ subs, moexb_pair* __restrict__ pairs, int* __restrict__ nsub, int* __restrict__ counters) {
+                              moexb_pair_item* __restrict__ subs, moexb_pair* __restrict__ pairs, int* __restrict__ nsub) {
     const int k = threadIdx.x, n = nh ? *nh : K;
     if (k < n) { subs[k] = {slots[k], k, 1}; pairs[k] = {0, k, w[k]}; }
-    if (k == 0) { *nsub = n; counters[0] = 0; counters[1] = 0; }
+    if (k == 0) *nsub = n;
 }
 
 }  // namespace moexb
