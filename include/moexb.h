@@ -48,6 +48,12 @@ enum {
                               EXPERT_BYTES_ZP = 1,818,624) */
 };
 
+/* How a resident layer keeps its expert blobs. TILED is the streaming layout of the B200 kernels: the same bytes as the
+ * reference blob, re-ordered into contiguous 4-5 KB slices in tensor-core lane order (see moe_b200/csrc/tiled.cuh), so a
+ * slice is one bulk copy; only the layer-level calls read it. REFERENCE keeps the reference blob as it is, which the
+ * pointer-level entry points (moexb_experts_forward, moexb_pairs_forward, moexb_pairs_forward_tc) require. */
+enum { MOEXB_LAYOUT_TILED = 0, MOEXB_LAYOUT_REFERENCE = 1 };
+
 /* Activation element types accepted by the layer-level calls. */
 enum { MOEXB_F32 = 0, MOEXB_BF16 = 1 };
 
@@ -165,8 +171,9 @@ int moexb_synth_q4k_host(unsigned seed, int layer, int expert, uint8_t* gate, ui
  * layer-level calls; their workspace (about max_tokens * (top_k + 1) * 10 KB) is allocated here, once. */
 int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moexb_ctx** out);
 int moexb_ctx_destroy(moexb_ctx* ctx);
-/* Which expert kernels the layer-level calls use: 0 = the streaming tensor-core kernels (default), 1 = the fp32 SIMT
- * kernels (the restatement of the reference's pairs_forward / experts_forward, kept for cross-checks). */
+/* Which expert kernels the layer-level calls use on a REFERENCE-layout layer: 0 = the streaming tensor-core kernels on
+ * 256-byte row pieces (default), 1 = the fp32 SIMT kernels (the restatement of the reference's pairs_forward /
+ * experts_forward, kept for cross-checks). TILED layers always use the tiled streaming kernels. */
 int moexb_ctx_set_path(moexb_ctx* ctx, int path);
 /* Waits for the device and reads the error word of the streaming kernels: 0 = none; 1 / 2 = a consumer warp / the producer
  * warp gave up waiting on a pipeline barrier (every device-side wait is bounded). The word is cleared. */
@@ -176,16 +183,19 @@ int moexb_ctx_status(moexb_ctx* ctx, int* status);
  * blob of format fmt, plus the router [n_routed+1][H] (row n_routed = the shared expert's gate vector).
  * first_local/n_local select the routed experts this process holds (expert parallelism); the others take no memory and
  * their pairs are dropped by moexb_group_pairs. router_dtype: MOEXB_F32, or 2 for F16 as the reference stores it. */
-int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype,
+int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype, int layout,
                        moexb_layer** out);
 int moexb_layer_destroy(moexb_layer* layer);
-/* Device pointer of expert e's blob (e == n_routed: shared expert); null if not held. */
+/* Device pointer of expert e's blob in the layer's layout (e == n_routed: shared expert); null if not held. */
 uint8_t* moexb_layer_blob(moexb_layer* layer, int e);
 /* Device array of n_routed+1 blob pointers (null = not held), usable as `slot_table`. */
 const uint8_t* const* moexb_layer_slot_table(moexb_layer* layer);
 /* Copies one expert blob (format of the layer, moexb_expert_bytes(fmt) bytes, host memory) into expert e's place; the
- * role of the reference's slot admission copy (moex.cu:257) with every expert resident. */
+ * role of the reference's slot admission copy (moex.cu:257) with every expert resident. The blob is given in the
+ * reference layout and converted on the device when the layer is TILED. Synchronous. */
 int moexb_layer_upload_expert(moexb_layer* layer, int e, const uint8_t* blob_host);
+/* The inverse: expert e's blob back in the reference layout, to host memory. Synchronous. */
+int moexb_layer_export_expert(moexb_layer* layer, int e, uint8_t* blob_host);
 /* Copies router weights from the host: W [n_routed+1][H] in the layer's router dtype. */
 int moexb_layer_set_router(moexb_layer* layer, const void* W_host);
 void* moexb_layer_router(moexb_layer* layer);

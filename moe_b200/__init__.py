@@ -4,7 +4,7 @@ The product is libmoexb.so (CUDA kernels behind the C ABI of include/moexb.h). T
 mirror of the reference's expert-layer entry points (same names and argument meaning as src/kernels.cuh of the
 reference) on torch tensors, used by the tests and the benchmark.
 """
-from ._lib import (FMT_SYM_F32, FMT_SYM_F16, FMT_ZP, F32, BF16, F16, EH, EI, EGS, Q_BYTES, CHUNKS, MoexbError,
+from ._lib import (FMT_SYM_F32, FMT_SYM_F16, FMT_ZP, F32, BF16, F16, LAYOUT_TILED, LAYOUT_REFERENCE, EH, EI, EGS, Q_BYTES, CHUNKS, MoexbError,
                    PairItem, Pair, lib)
 from .api import (expert_bytes, gemv_f16, gemv_f32, router_topk, experts_forward, pairs_forward, pairs_forward_dev,
                   pairs_reduce, gated_add_rows, shared_expert_add, group_pairs, dequant, q4k_dequant, q4k_to_zp,

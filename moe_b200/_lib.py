@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "libmoexb.so")
 
 FMT_SYM_F32, FMT_SYM_F16, FMT_ZP = 0, 1, 2
 F32, BF16, F16 = 0, 1, 2
+LAYOUT_TILED, LAYOUT_REFERENCE = 0, 1
 EH, EI, EGS = 2048, 512, 64
 Q_BYTES = 3 * EH * EI // 2
 CHUNKS = 3 * EH * EI // 32
@@ -57,11 +58,12 @@ SIGNATURES = {
     "moexb_synth_q4k_host": (_i, [_u, _i, _i, _vp, _vp, _vp]),
     "moexb_ctx_create": (_i, [_i, _i, _i, _i, C.POINTER(_vp)]),
     "moexb_ctx_destroy": (_i, [_vp]),
-    "moexb_layer_create": (_i, [_vp, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "moexb_layer_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "moexb_layer_destroy": (_i, [_vp]),
     "moexb_layer_blob": (_vp, [_vp, _i]),
     "moexb_layer_slot_table": (_vp, [_vp]),
     "moexb_layer_upload_expert": (_i, [_vp, _i, _vp]),
+    "moexb_layer_export_expert": (_i, [_vp, _i, _vp]),
     "moexb_layer_set_router": (_i, [_vp, _vp]),
     "moexb_layer_router": (_vp, [_vp]),
     "moexb_layer_fill_synth": (_i, [_vp, _u, _i, _vp]),

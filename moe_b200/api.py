@@ -179,10 +179,11 @@ class Layer:
     """moexb_layer: one MoE layer resident in HBM (routed experts [first_local, first_local+n_local), shared expert,
     router with the shared gate vector as its last row)."""
 
-    def __init__(self, ctx, fmt, n_routed=256, first_local=0, n_local=None, router_dtype=F32):
+    def __init__(self, ctx, fmt, n_routed=256, first_local=0, n_local=None, router_dtype=F32, layout=_lib.LAYOUT_TILED):
         n_local = n_routed - first_local if n_local is None else n_local
         h = C.c_void_p()
-        check(lib().moexb_layer_create(ctx.h, fmt, n_routed, first_local, n_local, router_dtype, C.byref(h)))
+        check(lib().moexb_layer_create(ctx.h, fmt, n_routed, first_local, n_local, router_dtype, layout, C.byref(h)))
+        self.layout = layout
         self.h, self.ctx, self.fmt, self.n_routed, self.router_dtype = h, ctx, fmt, n_routed, router_dtype
         self.first_local, self.n_local = first_local, n_local
 
@@ -206,6 +207,12 @@ class Layer:
         blob = np.ascontiguousarray(blob, dtype=np.uint8)
         assert blob.size == expert_bytes(self.fmt)
         check(lib().moexb_layer_upload_expert(self.h, e, blob.ctypes.data))
+
+    def export_blob(self, e):
+        """Expert e's blob in the reference layout, as numpy uint8."""
+        out = np.empty(expert_bytes(self.fmt), dtype=np.uint8)
+        check(lib().moexb_layer_export_expert(self.h, e, out.ctypes.data))
+        return out
 
     def forward(self, X, T, K=8, out=None, idx=None, w=None, flags=0):
         """moexb_layer_forward. X: [T][H] float32 or bfloat16 device tensor."""

@@ -5,6 +5,7 @@
 #include "experts_simt.cuh"
 #include "formats.cuh"
 #include "stream.cuh"
+#include "tiled.cuh"
 
 #include <cmath>
 #include <cstdarg>
@@ -76,6 +77,8 @@ const Tables& host_tables() {
 
 }  // namespace
 
+constexpr int STAGING_BLOBS = 8;
+
 struct moexb_ctx {
     int device = 0, max_tokens = 0, max_experts = 0, top_k = 0;
     uint16_t *table_s = nullptr, *table_d = nullptr;  // device copies of the synthetic tables
@@ -91,6 +94,7 @@ struct moexb_ctx {
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
+    uint8_t* staging = nullptr;                         // reference-layout blobs on their way into a tiled image
     std::vector<void*> owned;
     // optional per-kernel timing of the layer-level calls
     bool profiling = false;
@@ -119,7 +123,7 @@ struct ProfScope {
 
 struct moexb_layer {
     moexb_ctx* ctx = nullptr;
-    int fmt = 0, n_routed = 0, first_local = 0, n_local = 0, router_dtype = 0;
+    int fmt = 0, n_routed = 0, first_local = 0, n_local = 0, router_dtype = 0, layout = 0;
     uint8_t* image = nullptr;               // n_local + 1 blobs: the held routed experts, then the shared expert
     void* router = nullptr;                 // [n_routed + 1][H]
     const uint8_t** slot_table = nullptr;   // device, n_routed + 1 pointers
@@ -139,9 +143,15 @@ template <typename WT>
 static int gemv_any(const WT* W, const float* x, float* y, int I, int O, void* stream, int rows) {
     REQUIRE(W && x && y, "gemv: null pointer");
     REQUIRE(I > 0 && I % 128 == 0 && O > 0 && rows > 0, "gemv: I=%d must be a positive multiple of 128, O=%d, rows=%d", I, O, rows);
-    if (rows >= 16) {
-        constexpr int WARPS = 4, TO = 4, TR = 8;
-        gemm_rows_k<WT, WARPS, TO, TR><<<dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, 0, S(stream)>>>(W, x, y, I, O, rows);
+    if (rows >= 8) {
+        constexpr int WARPS = 8, TO = 4, TR = 8;
+        const int smem = TR * I * (int)sizeof(float);
+        REQUIRE(smem <= 200 * 1024, "gemv: I=%d is too large for the batched kernel", I);
+        static std::once_flag once;
+        static cudaError_t attr_err = cudaSuccess;
+        std::call_once(once, [] { attr_err = cudaFuncSetAttribute(gemm_rows_k<WT, WARPS, TO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+        if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "gemv: shared memory attribute: %s", cudaGetErrorString(attr_err));
+        gemm_rows_k<WT, WARPS, TO, TR><<<dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, smem, S(stream)>>>(W, x, y, I, O, rows);
     } else {
         constexpr int WARPS = 8;
         gemv_rows_k<WT, WARPS><<<dim3((O + WARPS - 1) / WARPS, rows), WARPS * 32, 0, S(stream)>>>(W, x, y, I, O);
@@ -158,13 +168,14 @@ int moexb_gemv_f32(const float* W, const float* x, float* y, int I, int O, void*
 }
 
 static int topk_launch(const float* logits, int E, int K, int norm, int* idx, float* w, void* stream, int T, int ld,
-                       const uint8_t* const* slot_table, const uint8_t** slots_out, float* wts_out) {
+                       const uint8_t* const* slot_table, const uint8_t** slots_out, float* wts_out,
+                       moexb_pair_item* dsubs = nullptr, moexb_pair* dpairs = nullptr, int* dnsub = nullptr) {
     REQUIRE(logits && idx && w, "router_topk: null pointer");
     REQUIRE(E > 0 && E % 32 == 0 && E <= 1024, "router_topk: E=%d must be a multiple of 32 up to 1024", E);
     REQUIRE(K > 0 && K < 32 && K <= E, "router_topk: K=%d out of range", K);
     REQUIRE(T > 0 && ld >= E, "router_topk: T=%d, ld=%d", T, ld);
     constexpr int WARPS = 4;
-    router_topk_k<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out);
+    router_topk_k<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
     LAUNCHED("router_topk");
     return MOEXB_OK;
 }
@@ -376,7 +387,7 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
     A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
-    A(&c->nsub, 1); A(&c->err, 1);
+    A(&c->nsub, 1); A(&c->err, 1); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
     if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
     if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
@@ -402,16 +413,17 @@ int moexb_synth_experts(moexb_ctx* ctx, int fmt, unsigned seed, int layer, int e
     return synth_launch(fmt, seed, layer, e0, n, dst, ctx->table_s, ctx->table_d, stream);
 }
 
-int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype, moexb_layer** out) {
+int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, int n_local, int router_dtype, int layout, moexb_layer** out) {
     REQUIRE(ctx && out, "layer_create: null pointer");
     REQUIRE(fmt_ok(fmt), "layer_create: unknown expert format %d", fmt);
     REQUIRE(n_routed > 0 && n_routed % 32 == 0 && n_routed <= ctx->max_experts, "layer_create: n_routed=%d (context allows %d)", n_routed, ctx->max_experts);
     REQUIRE(first_local >= 0 && n_local >= 0 && first_local + n_local <= n_routed, "layer_create: local experts [%d, %d) outside 0..%d", first_local, first_local + n_local, n_routed);
     REQUIRE(router_dtype == MOEXB_F32 || router_dtype == 2, "layer_create: router dtype %d", router_dtype);
+    REQUIRE(layout == MOEXB_LAYOUT_TILED || layout == MOEXB_LAYOUT_REFERENCE, "layer_create: layout %d", layout);
     CUDA_TRY(cudaSetDevice(ctx->device));
     moexb_layer* L = new (std::nothrow) moexb_layer;
     if (!L) return fail(MOEXB_ERR_NOMEM, "out of host memory");
-    L->ctx = ctx; L->fmt = fmt; L->n_routed = n_routed; L->first_local = first_local; L->n_local = n_local; L->router_dtype = router_dtype;
+    L->ctx = ctx; L->fmt = fmt; L->n_routed = n_routed; L->first_local = first_local; L->n_local = n_local; L->router_dtype = router_dtype; L->layout = layout;
     const size_t eb = expert_bytes(fmt);
     cudaError_t e = cudaMalloc((void**)&L->image, (size_t)(n_local + 1) * eb);
     if (e == cudaSuccess) e = cudaMalloc(&L->router, (size_t)(n_routed + 1) * EH * (router_dtype == MOEXB_F32 ? 4 : 2));
@@ -441,10 +453,50 @@ uint8_t* moexb_layer_blob(moexb_layer* L, int e) {
 const uint8_t* const* moexb_layer_slot_table(moexb_layer* L) { return L ? L->slot_table : nullptr; }
 void* moexb_layer_router(moexb_layer* L) { return L ? L->router : nullptr; }
 
+}  // extern "C"
+
+// Reference-layout blobs at src (device) -> the layer's layout at dst, n experts.
+static int to_layer_layout(moexb_layer* L, const uint8_t* src, uint8_t* dst, int n, cudaStream_t st) {
+    const size_t eb = expert_bytes(L->fmt);
+    if (L->layout == MOEXB_LAYOUT_REFERENCE) {
+        CUDA_TRY(cudaMemcpyAsync(dst, src, n * eb, cudaMemcpyDeviceToDevice, st));
+        return MOEXB_OK;
+    }
+    return by_fmt(L->fmt, [&]<int FMT>() {
+        for (int i = 0; i < n; i++) {
+            tile_expert_k<FMT, true><<<TL_SLICES, 256, 0, st>>>(src + i * eb, dst + i * eb);
+            LAUNCHED("tile_expert");
+        }
+        return (int)MOEXB_OK;
+    });
+}
+
+extern "C" {
+
 int moexb_layer_upload_expert(moexb_layer* L, int e, const uint8_t* blob_host) {
     REQUIRE(L && blob_host, "layer_upload_expert: null pointer");
     REQUIRE(e >= 0 && e <= L->n_routed && L->slot_host[e], "layer_upload_expert: expert %d is not held by this layer", e);
-    CUDA_TRY(cudaMemcpy(const_cast<uint8_t*>(L->slot_host[e]), blob_host, expert_bytes(L->fmt), cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(L->ctx->staging, blob_host, expert_bytes(L->fmt), cudaMemcpyHostToDevice));
+    const int rc = to_layer_layout(L, L->ctx->staging, const_cast<uint8_t*>(L->slot_host[e]), 1, nullptr);
+    if (rc != MOEXB_OK) return rc;
+    CUDA_TRY(cudaStreamSynchronize(nullptr));
+    return MOEXB_OK;
+}
+
+int moexb_layer_export_expert(moexb_layer* L, int e, uint8_t* blob_host) {
+    REQUIRE(L && blob_host, "layer_export_expert: null pointer");
+    REQUIRE(e >= 0 && e <= L->n_routed && L->slot_host[e], "layer_export_expert: expert %d is not held by this layer", e);
+    const uint8_t* src = L->slot_host[e];
+    if (L->layout == MOEXB_LAYOUT_TILED) {
+        const int rc = by_fmt(L->fmt, [&]<int FMT>() {
+            tile_expert_k<FMT, false><<<TL_SLICES, 256>>>(src, L->ctx->staging);
+            LAUNCHED("untile_expert");
+            return (int)MOEXB_OK;
+        });
+        if (rc != MOEXB_OK) return rc;
+        src = L->ctx->staging;
+    }
+    CUDA_TRY(cudaMemcpy(blob_host, src, expert_bytes(L->fmt), cudaMemcpyDeviceToHost));
     return MOEXB_OK;
 }
 
@@ -457,11 +509,18 @@ int moexb_layer_set_router(moexb_layer* L, const void* W_host) {
 int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void* stream) {
     REQUIRE(L, "layer_fill_synth: null layer");
     const size_t eb = expert_bytes(L->fmt);
-    if (L->n_local) {
-        const int rc = synth_launch(L->fmt, seed, layer_index, L->first_local, L->n_local, L->image, L->ctx->table_s, L->ctx->table_d, stream);
+    moexb_ctx* c = L->ctx;
+    // held routed experts, then the shared expert (id n_routed), through the staging buffer in batches
+    for (int i = 0; i < L->n_local + 1; i += STAGING_BLOBS) {
+        const int n = min(STAGING_BLOBS, L->n_local + 1 - i);
+        const int routed = min(n, max(0, L->n_local - i));
+        int rc = MOEXB_OK;
+        if (routed) rc = synth_launch(L->fmt, seed, layer_index, L->first_local + i, routed, c->staging, c->table_s, c->table_d, stream);
+        if (rc == MOEXB_OK && routed < n) rc = synth_launch(L->fmt, seed, layer_index, L->n_routed, 1, c->staging + routed * eb, c->table_s, c->table_d, stream);
+        if (rc == MOEXB_OK) rc = to_layer_layout(L, c->staging, L->image + (size_t)i * eb, n, S(stream));
         if (rc != MOEXB_OK) return rc;
     }
-    return synth_launch(L->fmt, seed, layer_index, L->n_routed, 1, L->image + (size_t)L->n_local * eb, L->ctx->table_s, L->ctx->table_d, stream);
+    return MOEXB_OK;
 }
 
 }  // extern "C"
@@ -492,6 +551,32 @@ static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float*
         StreamArgs d = a;
         d.xs = c->act_split;
         return stream_launch_one<FMT, true>(c, d, stream);
+    });
+}
+
+template <int FMT, bool DOWN>
+static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, void* stream) {
+    constexpr int NW = 4, D = 4;
+    constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "tiled stream kernel shared memory: %s", cudaGetErrorString(attr_err));
+    PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
+    stream_tiled_k<FMT, DOWN, NW, D><<<2 * c->sms, NW * 32, SMEM, S(stream)>>>(a);
+    LAUNCHED(DOWN ? "stream_tiled_down" : "stream_tiled_gate_up");
+    return MOEXB_OK;
+}
+
+// The same on blobs in the tiled layout (sub-item slots point into a tiled layer image).
+static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream) {
+    TiledArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->err};
+    return by_fmt(fmt, [&]<int FMT>() {
+        int rc = tiled_launch_one<FMT, false>(c, a, stream);
+        if (rc != MOEXB_OK) return rc;
+        TiledArgs d = a;
+        d.xs = c->act_split;
+        return tiled_launch_one<FMT, true>(c, d, stream);
     });
 }
 
@@ -537,7 +622,8 @@ extern "C" int moexb_ctx_status(moexb_ctx* c, int* status) {
 extern "C" {
 
 // Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
-static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode_slots) {
+// decode: also emit the K+1 one-pair sub-items of a single token (slots, weights, sub-items, pairs).
+static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode) {
     const int E = L->n_routed, ld = E + 1;
     int rc;
     {
@@ -547,7 +633,88 @@ static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int
     }
     if (rc != MOEXB_OK) return rc;
     PROF(c, MOEXB_PROF_TOPK, stream);
-    return topk_launch(c->logits, E, K, 1, c->idx, c->w, stream, T, ld, L->slot_table, decode_slots ? c->slots : nullptr, decode_slots ? c->wts : nullptr);
+    return topk_launch(c->logits, E, K, 1, c->idx, c->w, stream, T, ld, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
+                       decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr);
+}
+
+// One layer. xin: the layer input as f32 [T][H]. flags as moexb_layer_forward. pre_normed: the context already holds
+// rmsnorm(xin) and its bf16 split (left there by the previous layer of a stack); next_norm: leave rmsnorm(out) and its
+// split in the context for the next layer.
+static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int K, float* out, int* idx_out, float* w_out, int flags,
+                      void* stream, bool pre_normed, bool next_norm) {
+    const bool shared = !(flags & 1), block = flags & 2;
+    const bool all_local = L->n_local == L->n_routed;
+    const int E = L->n_routed, ld = E + 1;
+    cudaStream_t st = S(stream);
+    const bool tiled = L->layout == MOEXB_LAYOUT_TILED;
+    const bool streaming = tiled || c->path == 0;
+    const float* xf = xin;  // what the router and the experts see
+    if (block) {
+        xf = c->xn;
+        if (!pre_normed) {
+            PROF(c, MOEXB_PROF_OTHER, stream);
+            rmsnorm_split_k<<<T, 256, 0, st>>>(xin, c->xn, c->xs, 1e-6f);
+            LAUNCHED("rmsnorm_split");
+        }
+    } else if (streaming) {
+        const int rc = split_launch(c, xf, T, stream);
+        if (rc != MOEXB_OK) return rc;
+    }
+    const bool decode = T == 1 && all_local && shared;
+    int rc = layer_route(c, L, xf, T, K, stream, decode);
+    if (rc != MOEXB_OK) return rc;
+    int ranks = K;                  // rows of ypair per token that the final reduction adds
+    const float* extra = nullptr;   // + the shared expert's rows
+    if (decode && !streaming) {
+        // one token on the fp32 SIMT kernels: the K routed experts and the shared expert as K+1 decode experts
+        rc = decode_launch(c, L->fmt, c->slots, c->wts, K + 1, xf, c->act, block ? c->moe : out, stream, nullptr);
+        if (rc != MOEXB_OK) return rc;
+        if (block) {
+            PROF(c, MOEXB_PROF_COMBINE, stream);
+            residual_add_k<<<(unsigned)((EH / 4 + 255) / 256), 256, 0, st>>>(xin, c->moe, out, EH);
+            LAUNCHED("residual_add");
+            if (next_norm) { rmsnorm_split_k<<<1, 256, 0, st>>>(out, c->xn, c->xs, 1e-6f); LAUNCHED("rmsnorm_split"); }
+        }
+        ranks = 0;
+    } else if (decode) {
+        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream) : stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
+        if (rc != MOEXB_OK) return rc;
+        ranks = K + 1;
+    } else {
+        {
+            PROF(c, MOEXB_PROF_GROUP, stream);
+            group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
+                                                                 shared ? c->logits + E : nullptr, ld);
+            LAUNCHED("group_plan");
+            // pairs of experts that are not held here are never written: their ypair rows must read as zero
+            if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
+        }
+        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
+           : streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
+                       : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
+        if (rc != MOEXB_OK) return rc;
+        if (shared) extra = c->ypair + (size_t)T * K * EH;
+    }
+    if (ranks) {
+        PROF(c, MOEXB_PROF_COMBINE, stream);
+        reduce_residual_norm_k<<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
+        LAUNCHED("reduce_residual_norm");
+    }
+    if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    if (w_out) CUDA_TRY(cudaMemcpyAsync(w_out, c->w, (size_t)T * K * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return MOEXB_OK;
+}
+
+// The layer input as f32: bf16 inputs are widened (exactly) into the context.
+static int layer_input(moexb_ctx* c, const void* X, int x_dtype, int T, void* stream, const float** xin) {
+    if (x_dtype == MOEXB_BF16) {
+        PROF(c, MOEXB_PROF_OTHER, stream);
+        const size_t n = (size_t)T * EH;
+        bf16_to_f32_k<<<(unsigned)((n / 2 + 255) / 256), 256, 0, S(stream)>>>(static_cast<const __nv_bfloat16*>(X), c->xf, n);
+        LAUNCHED("bf16_to_f32");
+        *xin = c->xf;
+    } else *xin = static_cast<const float*>(X);
+    return MOEXB_OK;
 }
 
 int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype, int T, int K, float* out, int* idx_out,
@@ -557,80 +724,10 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     REQUIRE(T > 0 && T <= c->max_tokens, "layer_forward: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
     REQUIRE(K > 0 && K <= c->top_k, "layer_forward: K=%d exceeds the context's top_k=%d", K, c->top_k);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "layer_forward: x_dtype=%d", x_dtype);
-    const bool shared = !(flags & 1), block = flags & 2;
-    const bool all_local = L->n_local == L->n_routed;
-    const int E = L->n_routed, ld = E + 1;
-    cudaStream_t st = S(stream);
-    const size_t n = (size_t)T * EH;
-    const float* xin;  // the layer input as f32
-    if (x_dtype == MOEXB_BF16) {
-        PROF(c, MOEXB_PROF_OTHER, stream);
-        bf16_to_f32_k<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), c->xf, n);
-        LAUNCHED("bf16_to_f32");
-        xin = c->xf;
-    } else xin = static_cast<const float*>(X);
-    const float* xf = xin;  // what the router and the experts see
-    if (block) {
-        PROF(c, MOEXB_PROF_OTHER, stream);
-        rmsnorm_rows_k<<<T, 256, 0, st>>>(xin, c->xn, EH, 1e-6f);
-        LAUNCHED("rmsnorm");
-        xf = c->xn;
-    }
-    float* moe = block ? c->moe : out;
-    const bool decode = T == 1 && all_local && shared;
-    int rc = layer_route(c, L, xf, T, K, stream, decode);
+    const float* xin;
+    int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
-    const bool streaming = c->path == 0;
-    if (streaming) {
-        rc = split_launch(c, xf, T, stream);
-        if (rc != MOEXB_OK) return rc;
-    }
-    if (decode && !streaming) {
-        // one token: the K routed experts and the shared expert (weight sigmoid(gate logit)) as K+1 decode experts
-        rc = decode_launch(c, L->fmt, c->slots, c->wts, K + 1, xf, c->act, moe, stream, nullptr);
-        if (rc != MOEXB_OK) return rc;
-    } else if (decode) {
-        {
-            PROF(c, MOEXB_PROF_GROUP, stream);
-            plan_decode_k<<<1, 32, 0, st>>>(c->slots, c->wts, K + 1, nullptr, c->subs, c->pairs, c->nsub);
-            LAUNCHED("plan_decode");
-        }
-        rc = stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
-        if (rc != MOEXB_OK) return rc;
-        PROF(c, MOEXB_PROF_COMBINE, stream);
-        rc = moexb_pairs_reduce(c->ypair, nullptr, moe, K + 1, EH, 1, nullptr, stream);
-        if (rc != MOEXB_OK) return rc;
-    } else {
-        constexpr int WARPS = 8;
-        {
-            PROF(c, MOEXB_PROF_GROUP, stream);
-            group_count_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, T * K, E, c->counts);
-            LAUNCHED("group_count");
-            group_scatter_k<WARPS><<<(E + WARPS - 1) / WARPS, WARPS * 32, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->counts, c->items, c->pairs,
-                                                                                     c->nitems, shared ? c->logits + E : nullptr, ld);
-            LAUNCHED("group_scatter");
-            // pairs of experts that are not held here are never written: their ypair rows must read as zero
-            if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
-            if (streaming) {
-                plan_subitems_k<<<1, 1024, 0, st>>>(c->items, c->nitems, 0, c->subs, c->nsub);
-                LAUNCHED("plan_subitems");
-            }
-        }
-        rc = streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
-                       : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
-        if (rc != MOEXB_OK) return rc;
-        PROF(c, MOEXB_PROF_COMBINE, stream);
-        rc = moexb_pairs_reduce(c->ypair, shared ? c->ypair + (size_t)T * K * EH : nullptr, moe, K, EH, T, nullptr, stream);
-        if (rc != MOEXB_OK) return rc;
-    }
-    if (block) {
-        PROF(c, MOEXB_PROF_COMBINE, stream);
-        residual_add_k<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(xin, c->moe, out, n);
-        LAUNCHED("residual_add");
-    }
-    if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
-    if (w_out) CUDA_TRY(cudaMemcpyAsync(w_out, c->w, (size_t)T * K * sizeof(float), cudaMemcpyDeviceToDevice, st));
-    return MOEXB_OK;
+    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, flags, stream, false, false);
 }
 
 // ---- stack of layers as one CUDA graph ----------------------------------------------------------------------------------
@@ -661,6 +758,7 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     REQUIRE(n_layers > 0 && T > 0 && T <= c->max_tokens && K > 0 && K <= c->top_k, "stack_create: n_layers=%d T=%d K=%d", n_layers, T, K);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "stack_create: x_dtype=%d", x_dtype);
     REQUIRE(!c->profiling, "stack_create: switch profiling off before capturing a graph");
+    for (int l = 0; l < n_layers; l++) REQUIRE(layers[l] && layers[l]->ctx == c, "stack_create: layer %d is null or belongs to another context", l);
     CUDA_TRY(cudaSetDevice(c->device));
     moexb_stack* s = new (std::nothrow) moexb_stack;
     if (!s) return fail(MOEXB_ERR_NOMEM, "out of host memory");
@@ -674,10 +772,13 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     const long long before = g_launches.load();
     e = cudaStreamBeginCapture(s->cap, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "stack_create: begin capture: %s", cudaGetErrorString(e)); }
-    int rc = MOEXB_OK;
-    for (int l = 0; l < n_layers && rc == MOEXB_OK; l++)
-        rc = moexb_layer_forward(c, layers[l], l == 0 ? s->x_in : (const void*)s->buf[(l - 1) & 1], l == 0 ? x_dtype : MOEXB_F32, T, K,
-                                 s->buf[l & 1], nullptr, nullptr, 2, s->cap);
+    const float* xin = nullptr;
+    int rc = layer_input(c, s->x_in, x_dtype, T, s->cap, &xin);
+    for (int l = 0; l < n_layers && rc == MOEXB_OK; l++) {
+        // layer l leaves rmsnorm(x_{l+1}) and its split in the context, so layer l+1 starts at its router
+        rc = layer_impl(c, layers[l], xin, T, K, s->buf[l & 1], nullptr, nullptr, 2, s->cap, l > 0, l + 1 < n_layers);
+        xin = s->buf[l & 1];
+    }
     e = cudaStreamEndCapture(s->cap, &s->graph);
     s->kernels = (int)(g_launches.load() - before);
     g_launches.store(before);  // captured, not yet run

@@ -32,13 +32,21 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_rows_k(const WT* __restrict__
     if (lane == 0) y[(size_t)blockIdx.y * O + o] = acc;
 }
 
-// The same result for many rows (a prefill chunk): a warp keeps TO outputs x TR rows of accumulators per lane, each
-// lane still owning elements 128c+4j..4j+3 of every dot product, so every (row, output) sum is formed in exactly the
-// order of gemv_rows_k and the two kernels are interchangeable bit for bit. grid (ceil(O / (WARPS*TO)), ceil(rows / TR)).
+// The same result for many rows (a batch or a prefill chunk). A block stages TR activation rows in shared memory and its
+// WARPS warps each own TO outputs; a lane still holds elements 128c+4j..4j+3 of every dot product, so every
+// (row, output) sum is formed in exactly the order of gemv_rows_k and the two kernels agree bit for bit.
+// grid (ceil(O / (WARPS*TO)), ceil(rows / TR)); dynamic shared memory TR * I floats.
 template <typename WT, int WARPS, int TO, int TR>
 __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__ W, const float* __restrict__ x,
                                                           float* __restrict__ y, int I, int O, int rows) {
-    const int o0 = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * TO, r0 = blockIdx.y * TR, lane = threadIdx.x & 31;
+    extern __shared__ __align__(16) float xsm[];  // [TR][I]
+    const int r0 = blockIdx.y * TR, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x * 4; i < TR * I; i += WARPS * 128) {
+        const int r = min(r0 + i / I, rows - 1);
+        *reinterpret_cast<float4*>(xsm + i) = __ldg(reinterpret_cast<const float4*>(x + (size_t)r * I + i % I));
+    }
+    __syncthreads();
+    const int o0 = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * TO;
     if (o0 >= O) return;
     float acc[TR][TO];
 #pragma unroll
@@ -46,26 +54,26 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
 #pragma unroll
         for (int o = 0; o < TO; o++) acc[r][o] = 0.f;
     for (int c = 0; c < I / 128; c++) {
-        float4 w[TO], v[TR];
+        float4 w[TO];
 #pragma unroll
         for (int o = 0; o < TO; o++) w[o] = ld_w4(W + (size_t)min(o0 + o, O - 1) * I, (size_t)128 * c + 4 * lane);
 #pragma unroll
-        for (int r = 0; r < TR; r++) v[r] = __ldg(reinterpret_cast<const float4*>(x + (size_t)min(r0 + r, rows - 1) * I + 128 * c + 4 * lane));
-#pragma unroll
-        for (int r = 0; r < TR; r++)
+        for (int r = 0; r < TR; r++) {
+            const float4 v = *reinterpret_cast<const float4*>(xsm + r * I + 128 * c + 4 * lane);
 #pragma unroll
             for (int o = 0; o < TO; o++) {
                 float a = acc[r][o];
-                a = fmaf(w[o].x, v[r].x, a); a = fmaf(w[o].y, v[r].y, a); a = fmaf(w[o].z, v[r].z, a); a = fmaf(w[o].w, v[r].w, a);
+                a = fmaf(w[o].x, v.x, a); a = fmaf(w[o].y, v.y, a); a = fmaf(w[o].z, v.z, a); a = fmaf(w[o].w, v.w, a);
                 acc[r][o] = a;
             }
+        }
     }
 #pragma unroll
     for (int r = 0; r < TR; r++)
 #pragma unroll
         for (int o = 0; o < TO; o++) {
-            const float s = warp_sum(acc[r][o]);
-            if (lane == 0 && r0 + r < rows && o0 + o < O) y[(size_t)(r0 + r) * O + o0 + o] = s;
+            const float sum = warp_sum(acc[r][o]);
+            if (lane == 0 && r0 + r < rows && o0 + o < O) y[(size_t)(r0 + r) * O + o0 + o] = sum;
         }
 }
 
@@ -74,12 +82,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
 // the larger value and on equal values the lower index, and the winner is struck from its owner's mask.
 // Selection compares logits (softmax is monotone). NaN logits count as -inf. Optional decode outputs: slots_out /
 // wts_out [K+1] = the selected experts' blob pointers and weights followed by the shared expert with weight
-// sigmoid(logits[E]).
+// sigmoid(logits[E]); dsubs / dpairs / dnsub = the same K+1 experts as one-pair sub-items for the streaming kernels (T = 1).
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restrict__ logits, int E, int K, int norm, int ld,
                                                             int* __restrict__ idx, float* __restrict__ w, int T,
                                                             const uint8_t* const* __restrict__ slot_table,
-                                                            const uint8_t** __restrict__ slots_out, float* __restrict__ wts_out) {
+                                                            const uint8_t** __restrict__ slots_out, float* __restrict__ wts_out,
+                                                            moexb_pair_item* __restrict__ dsubs, moexb_pair* __restrict__ dpairs,
+                                                            int* __restrict__ dnsub) {
     const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float* l = logits + (size_t)t * ld;
@@ -121,10 +131,13 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
         idx[(size_t)t * K + lane] = mine_i;
         w[(size_t)t * K + lane] = wk;
         if (slots_out) { slots_out[(size_t)t * (K + 1) + lane] = slot_table[mine_i]; wts_out[(size_t)t * (K + 1) + lane] = wk; }
+        if (dsubs) { dsubs[lane] = {slot_table[mine_i], lane, 1}; dpairs[lane] = {0, lane, wk}; }  // one token: expert k = sub-item k
     }
     if (slots_out && lane == K) {
+        const float gate = 1.f / (1.f + expf(-l[E]));
         slots_out[(size_t)t * (K + 1) + K] = slot_table[E];
-        wts_out[(size_t)t * (K + 1) + K] = 1.f / (1.f + expf(-l[E]));
+        wts_out[(size_t)t * (K + 1) + K] = gate;
+        if (dsubs) { dsubs[K] = {slot_table[E], K, 1}; dpairs[K] = {0, K, gate}; *dnsub = K + 1; }
     }
 }
 
@@ -182,6 +195,91 @@ __global__ void __launch_bounds__(WARPS * 32) group_scatter_k(const int* __restr
             for (int t = threadIdx.x; t < T; t += blockDim.x)
                 pairs[s_np + t] = {t, n + t, 1.f / (1.f + expf(-gate_logits[(size_t)t * gl_stride]))};
         } else if (threadIdx.x == 0) *nitems = s_ni;
+    }
+}
+
+// Exclusive prefix sums of three per-thread values over a block of 256 threads; totals returned through tot[].
+__device__ __forceinline__ void block_scan3_256(int (&v)[3], int (&tot)[3]) {
+    __shared__ int ws[3][8];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int inc[3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        inc[i] = v[i];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, inc[i], o); if (lane >= o) inc[i] += u; }
+        if (lane == 31) ws[i][w] = inc[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        int before = 0, all = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { const int x = ws[i][j]; all += x; if (j < w) before += x; }
+        v[i] = inc[i] - v[i] + before;
+        tot[i] = all;
+    }
+}
+
+// Grouping and planning in one launch (the work of group_count_k + group_scatter_k, plus the sub-items of at most MAXP
+// pairs that the streaming kernels walk). Every block builds the per-expert histogram of the T*K pairs in shared memory
+// and scans it; then one warp per expert writes that expert's item, its sub-items and its pairs in token order.
+// Optional shared expert as in group_scatter_k. E <= 1024; 256 threads; grid ceil(E / 8).
+template <int MAXP>
+__global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
+                                                    const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
+                                                    moexb_pair* __restrict__ pairs, int* __restrict__ nitems, moexb_pair_item* __restrict__ subs,
+                                                    int* __restrict__ nsub, const float* __restrict__ gate_logits, int gl_stride) {
+    __shared__ int cnt[1024], start[1024], item_of[1024], sub_at[1024];
+    __shared__ int s_tot[3];
+    const int n = T * K, tid = threadIdx.x, lane = tid & 31;
+    for (int e = tid; e < E; e += 256) cnt[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < n; p += 256) atomicAdd(&cnt[__ldg(idx + p)], 1);
+    __syncthreads();
+    {
+        const int per = (E + 255) / 256, e0 = tid * per;
+        int c[4], v[3] = {0, 0, 0}, tot[3];
+        for (int i = 0; i < per; i++) {
+            const int e = e0 + i;
+            c[i] = (e < E && slot_table[e]) ? cnt[e] : 0;
+            v[0] += c[i]; v[1] += c[i] != 0; v[2] += (c[i] + MAXP - 1) / MAXP;
+        }
+        block_scan3_256(v, tot);
+        for (int i = 0; i < per; i++) {
+            const int e = e0 + i;
+            if (e < E) {
+                start[e] = v[0]; item_of[e] = c[i] ? v[1] : -1; sub_at[e] = v[2];
+                cnt[e] = c[i];
+            }
+            v[0] += c[i]; v[1] += c[i] != 0; v[2] += (c[i] + MAXP - 1) / MAXP;
+        }
+        if (tid == 0) { s_tot[0] = tot[0]; s_tot[1] = tot[1]; s_tot[2] = tot[2]; }
+    }
+    __syncthreads();
+    const int e = blockIdx.x * 8 + (tid >> 5);
+    if (e < E && item_of[e] >= 0) {
+        const uint8_t* slot = slot_table[e];
+        int at = start[e];
+        const int c = cnt[e];
+        if (lane == 0) items[item_of[e]] = {slot, at, c};
+        for (int j = lane; j * MAXP < c; j += 32) subs[sub_at[e] + j] = {slot, at + j * MAXP, min(MAXP, c - j * MAXP)};
+        for (int p0 = 0; p0 < n; p0 += 32) {
+            const int p = p0 + lane;
+            const bool hit = p < n && __ldg(idx + p) == e;
+            const unsigned b = __ballot_sync(0xffffffffu, hit);
+            if (hit) pairs[at + __popc(b & ((1u << lane) - 1))] = {p / K, p, __ldg(w + p)};
+            at += __popc(b);
+        }
+    }
+    if (blockIdx.x == 0) {
+        const int np = s_tot[0], ni = s_tot[1], ns = s_tot[2];
+        if (gate_logits && slot_table[E]) {
+            const uint8_t* slot = slot_table[E];
+            if (tid == 0) { items[ni] = {slot, np, T}; *nitems = ni + 1; *nsub = ns + (T + MAXP - 1) / MAXP; }
+            for (int t = tid; t < T; t += 256) pairs[np + t] = {t, n + t, 1.f / (1.f + expf(-gate_logits[(size_t)t * gl_stride]))};
+            for (int j = tid; j * MAXP < T; j += 256) subs[ns + j] = {slot, np + j * MAXP, min(MAXP, T - j * MAXP)};
+        } else if (tid == 0) { *nitems = ni; *nsub = ns; }
     }
 }
 

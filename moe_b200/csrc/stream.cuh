@@ -305,6 +305,75 @@ __global__ void split_rows_k(const float* __restrict__ x, __nv_bfloat16* __restr
     dst[0] = hi; dst[K] = lo;
 }
 
+// One row of D = 2048 floats held 8 per thread (thread i: elements 4i..4i+3 and 1024+4i..1024+4i+3): the sum of squares
+// in the pinned order of rmsnorm_rows_k, then the normalised row as fp32 (for the router) and as bf16 hi + lo in the
+// permuted order (for the streaming kernels).
+__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, __nv_bfloat16* __restrict__ xs, float eps) {
+    __shared__ float part[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += part[i];
+    const float r = 1.f / sqrtf(tot / (float)EH + eps);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int k0 = 1024 * h + 4 * threadIdx.x;
+        float4 o = make_float4(v[4 * h] * r, v[4 * h + 1] * r, v[4 * h + 2] * r, v[4 * h + 3] * r);
+        *reinterpret_cast<float4*>(xn + k0) = o;
+        const float f[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(f[i]), lo = __float2bfloat16_rn(f[i] - __bfloat162float(hi));
+            const int pos = split_pos(k0 + i);
+            xs[pos] = hi; xs[EH + pos] = lo;
+        }
+    }
+}
+
+// xn[t] = rmsnorm(x[t]) and its bf16 split, one block of 256 per row (H = 2048).
+__global__ void __launch_bounds__(256) rmsnorm_split_k(const float* __restrict__ x, float* __restrict__ xn, __nv_bfloat16* __restrict__ xs, float eps) {
+    const size_t t = blockIdx.x;
+    float v[8];
+    const float4 a = *reinterpret_cast<const float4*>(x + t * EH + 4 * threadIdx.x), b = *reinterpret_cast<const float4*>(x + t * EH + 1024 + 4 * threadIdx.x);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    norm_split_row(v, xn + t * EH, xs + t * 2 * EH, eps);
+}
+
+// The end of a layer in one pass over the token's row: moe[t] = sum_{r<K} ypair[t*K+r] in rank order (+ extra[t]: the
+// shared expert's row), out[t] = x[t] + moe[t] when x is given (the residual block) else moe[t]; and, when xn_next is
+// given, the next layer's normalised input and its bf16 split straight from the registers. One block of 256 per token.
+__global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __restrict__ ypair, const float* __restrict__ extra, const float* __restrict__ x,
+                                                              float* __restrict__ out, int K, float* __restrict__ xn_next,
+                                                              __nv_bfloat16* __restrict__ xs_next, float eps) {
+    const size_t t = blockIdx.x;
+    float v[8];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int k0 = 1024 * h + 4 * threadIdx.x;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < K; r++) {
+            const float4 y = *reinterpret_cast<const float4*>(ypair + (t * K + r) * EH + k0);
+            acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+        }
+        if (extra) {
+            const float4 y = *reinterpret_cast<const float4*>(extra + t * EH + k0);
+            acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+        }
+        if (x) {
+            const float4 y = *reinterpret_cast<const float4*>(x + t * EH + k0);
+            acc.x = y.x + acc.x; acc.y = y.y + acc.y; acc.z = y.z + acc.z; acc.w = y.w + acc.w;
+        }
+        *reinterpret_cast<float4*>(out + t * EH + k0) = acc;
+        v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
+    }
+    if (xn_next) norm_split_row(v, xn_next + t * EH, xs_next + t * 2 * EH, eps);
+}
+
 // Exclusive prefix sum over the 1024 threads of a block; every thread also gets the total.
 __device__ __forceinline__ int block_scan_1024(int v, int& total) {
     __shared__ int wsum[32];

@@ -1,0 +1,236 @@
+// The resident ("tiled") expert layout and the streaming kernels that read it.
+//
+// Why a second layout: cp.async.bulk has a per-instruction cost. Streaming the reference layout needs one copy per row
+// piece (256 bytes, because rows must be padded apart in shared memory to avoid bank conflicts), and 256-byte copies top
+// out near 2 TB/s on a B200; 1 KB copies reach 4 TB/s, 4 KB copies 5.7 TB/s, 16 KB copies 6.4 TB/s (measured with the
+// math switched off). So the resident image stores every expert as a sequence of self-contained 4-5 KB slices, each one
+// contiguous copy, already in the order the tensor-core lanes consume it. The bytes are the same as in the reference
+// blob (sizes are identical); only their order changes, and tile_expert_k / untile_expert_k convert in both directions.
+//
+// A slice is the weights of one MMA row tile (16 rows) over 512 inputs = 8 scale groups:
+//   gate/up: rows 8*wt..8*wt+7 of gate (MMA rows 0-7) and of up (MMA rows 8-15), inputs 512*ks..512*ks+511; slice index
+//            wt*4 + ks, wt < 64, ks < 4.
+//   down   : rows 16*wt..16*wt+15, all 512 inputs; slice index 256 + wt, wt < 128.
+// Inside a slice, for each group G: 512 bytes of nibbles, 16 bytes per lane l = 4*g + t: bytes 0-7 = row A(g)'s
+// 16 nibbles for inputs 64*G + 16*t .. +15, bytes 8-15 = row B(g)'s (A = MMA row g, B = MMA row g + 8); then the group's
+// scale bytes: fp16 (sA, sB) per g (32 bytes), or f32 (64 bytes), or zero point [scA0 mnA0 scA1 mnA1 | scB0 mnB0 scB1 mnB1]
+// per g (64 bytes). Zero-point slices end with 128 bytes of half2 (d, dm): per g [A block 0, A block 1, B block 0,
+// B block 1] for the two 256-input super-blocks of the slice.
+#pragma once
+#include "common.cuh"
+#include "stream.cuh"
+
+namespace moexb {
+
+constexpr int TL_SLICES = 384;  // 256 gate/up + 128 down
+template <int FMT> constexpr int tl_scale_group() { return FMT == FMT_SYM_F16 ? 32 : 64; }
+template <int FMT> constexpr int tl_group_bytes() { return 512 + tl_scale_group<FMT>(); }
+template <int FMT> constexpr int tl_slice_bytes() { return 8 * tl_group_bytes<FMT>() + (FMT == FMT_ZP ? 128 : 0); }
+static_assert(TL_SLICES * tl_slice_bytes<FMT_SYM_F16>() == expert_bytes(FMT_SYM_F16), "tiled size");
+static_assert(TL_SLICES * tl_slice_bytes<FMT_SYM_F32>() == expert_bytes(FMT_SYM_F32), "tiled size");
+static_assert(TL_SLICES * tl_slice_bytes<FMT_ZP>() == expert_bytes(FMT_ZP), "tiled size");
+
+// Rows (in the blob's merged [gate | up | down] row space) and first input of slice si, MMA row m (0..15).
+__device__ __forceinline__ void tl_row_of(int si, int m, size_t& qoff, size_t& c0) {
+    if (si < 256) {
+        const int wt = si >> 2, ks = si & 3;
+        const size_t row = (size_t)(m < 8 ? 0 : EI) + 8 * wt + (m & 7);
+        qoff = row * (EH / 2) + ks * 256;     // byte offset of the row's 512 inputs in the nibble area
+        c0 = row * (EH / 32) + ks * 16;       // their first 32-weight chunk
+    } else {
+        const int d = 16 * (si - 256) + m;
+        qoff = DOWN_Q_OFF + (size_t)d * (EI / 2);
+        c0 = DOWN_C_OFF + (size_t)d * (EI / 32);
+    }
+}
+
+// One block per slice: reference-layout blob <-> tiled blob (TO_TILED = direction). 256 threads.
+template <int FMT, bool TO_TILED>
+__global__ void __launch_bounds__(256) tile_expert_k(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst) {
+    constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
+    const int si = blockIdx.x, tid = threadIdx.x;
+    const uint8_t* ref = TO_TILED ? src : dst;   // the reference-layout side
+    uint8_t* til = const_cast<uint8_t*>(TO_TILED ? dst : src) + (size_t)si * SB;
+    uint8_t* refw = const_cast<uint8_t*>(ref);
+    auto move = [&](uint8_t* t, size_t roff, int n) {  // n bytes between tiled address t and reference offset roff
+        for (int i = 0; i < n; i++) { if (TO_TILED) t[i] = ref[roff + i]; else refw[roff + i] = t[i]; }
+    };
+    {   // nibbles: thread = (group G, lane l)
+        const int G = tid >> 5, l = tid & 31, g = l >> 2, t = l & 3;
+        size_t qa, qb, ca, cb;
+        tl_row_of(si, g, qa, ca); tl_row_of(si, g + 8, qb, cb);
+        move(til + G * GB + 16 * l, qa + G * 32 + 8 * t, 8);
+        move(til + G * GB + 16 * l + 8, qb + G * 32 + 8 * t, 8);
+    }
+    if (tid < 128) {  // scales: thread = (group G, MMA row m)
+        const int G = tid >> 4, j = tid & 15, g = j >> 1, ab = j & 1;
+        size_t q, c0;
+        tl_row_of(si, g + 8 * ab, q, c0);
+        uint8_t* sc = til + G * GB + 512;
+        if constexpr (FMT == FMT_SYM_F16) move(sc + 4 * g + 2 * ab, Q_BYTES + (c0 / 2 + G) * 2, 2);
+        else if constexpr (FMT == FMT_SYM_F32) move(sc + 8 * g + 4 * ab, Q_BYTES + (c0 / 2 + G) * 4, 4);
+        else {
+            move(sc + 8 * g + 4 * ab, Q_BYTES + (c0 + 2 * G) * 2, 4);  // [sc, mn] of the group's two chunks
+            if (G < 2) move(til + 8 * GB + 16 * g + 8 * ab + 4 * G, Q_BYTES + CHUNKS * 2 + (c0 / 8 + G) * 4, 4);  // (d, dm) of super-block G
+        }
+    }
+}
+
+struct TiledArgs {
+    const moexb_pair_item* subs;  // sub-items: at most ST_MAXP pairs each, slot = tiled blob
+    const int* nsub;
+    const moexb_pair* pairs;
+    const __nv_bfloat16* xs;      // gate/up: activations [token][2][H] (hi, lo), permuted; down: act [pair p][2][I]
+    float* act32;                 // gate/up: optional fp32 copy of act [p][I]
+    __nv_bfloat16* act_split;     // gate/up output [p][2][I], permuted
+    float* ypair;                 // down output [p][H]
+    int* err;
+};
+
+// Streaming expert kernel on the tiled layout. No producer warp: every warp is its own pipeline. A warp owns a ring of D
+// slice buffers; lane 0 issues one cp.async.bulk per slice (4-5 KB, one contiguous run of the blob) D slices ahead and
+// the warp waits on the slice's mbarrier before consuming it, so there is no cross-warp hand-off on the weight stream.
+// Work is split in rounds of NW consecutive row tiles of one sub-item (warp w takes tile w of the round); a CTA walks a
+// contiguous range of rounds, so its warps share the sub-item's 8 activation columns in shared memory and swap them
+// together when the range crosses into the next sub-item.
+// DOWN = false: row tile = 8 gate + 8 up rows, 4 slices (K = 2048); act = silu(gate) * up.
+// DOWN = true : row tile = 16 down rows, 1 slice (K = 512); ypair = w * (down . act).
+template <int FMT, bool DOWN, int NW, int D>
+__global__ void __launch_bounds__(NW * 32) stream_tiled_k(const TiledArgs a) {
+    constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
+    constexpr int KS = DOWN ? 1 : 4;                       // slices per row tile
+    constexpr int RPS = (DOWN ? 128 : 64) / NW;            // rounds per sub-item
+    constexpr int KB = DOWN ? EI : EH;
+    constexpr int BCOL = st_bcol_bytes<DOWN>();
+    constexpr bool Z = FMT == FMT_ZP;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* bsm = smem + NW * D * SB;                                 // 8 activation columns
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);      // full[NW][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
+    if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    const long long R = (long long)*a.nsub * RPS;
+    const int r0 = (int)(R * blockIdx.x / gridDim.x), r1 = (int)(R * (blockIdx.x + 1) / gridDim.x);
+    const int Q = (r1 - r0) * KS;  // slices this warp will consume
+    uint8_t* ring = smem + warp * D * SB;
+    uint64_t* full = bars + warp * D;
+
+    // slice q of this warp: round r0 + q / KS, row tile rin*NW + warp, K slice q % KS
+    auto issue = [&](int q) {
+        const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, wt = rin * NW + warp;
+        const uint8_t* src = a.subs[sub].slot + (size_t)(DOWN ? 256 + wt : wt * 4 + q % KS) * SB;
+        const uint32_t bar = smem_u32(full + q % D);
+        mbar_arrive_expect_tx(bar, SB);
+        bulk_g2s(smem_u32(ring + (q % D) * SB), src, SB, bar);
+    };
+    if (lane == 0)
+        for (int q = 0; q < D && q < Q; q++) issue(q);
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int cur_sub = -1, n = 0, start = 0;
+    const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
+    for (int q = 0; q < Q; q++) {
+        const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, ks = q % KS;
+        if (sub != cur_sub) {
+            // new sub-item: the CTA's warps swap the activation columns together (their weight copies stay in flight)
+            cur_sub = sub;
+            const moexb_pair_item it = a.subs[sub];
+            n = it.count; start = it.start;
+            __syncthreads();
+            constexpr int CHUNKS16 = KB * 2 / 16;
+            for (int i = threadIdx.x; i < 2 * n * CHUNKS16; i += NW * 32) {
+                const int col = i / CHUNKS16, ch = i % CHUNKS16;
+                const moexb_pair pr = a.pairs[start + (col >> 1)];
+                const size_t row = DOWN ? (size_t)pr.p : (size_t)pr.t;
+                cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (row * 2 + (col & 1)) * KB + ch * 8);
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncthreads();
+        }
+        if (!mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT)) return;
+        if (ks == 0) acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        const uint8_t* sl = ring + (q % D) * SB;
+        const uint8_t* bp = bcol + ks * 1024;  // 8 groups of 128 bytes per slice
+#pragma unroll 4
+        for (int G = 0; G < 8; G++) {
+            const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
+            const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
+            uint32_t Pa[2][4], Pb[2][4];
+            dq_word<!Z>(qq.x, Pa[0]); dq_word<!Z>(qq.y, Pa[1]);
+            dq_word<!Z>(qq.z, Pb[0]); dq_word<!Z>(qq.w, Pb[1]);
+            if constexpr (!Z) {
+                float sa, sb;
+                if constexpr (FMT == FMT_SYM_F16) {
+                    const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(sl + G * GB + 512 + 4 * g));
+                    sa = s2.x; sb = s2.y;
+                } else {
+                    const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
+                    sa = s2.x; sb = s2.y;
+                }
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};  // two chains: consecutive MMAs do not wait on each other
+                mma_bf16(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
+                mma_bf16(e, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
+                mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
+                mma_bf16(e, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
+                acc[0] = fmaf(c[0] + e[0], sa, acc[0]); acc[1] = fmaf(c[1] + e[1], sa, acc[1]);
+                acc[2] = fmaf(c[2] + e[2], sb, acc[2]); acc[3] = fmaf(c[3] + e[3], sb, acc[3]);
+            } else {
+                // zero point: each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial sums
+                // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 0 of the group, lanes t = 2,3 chunk 1, and an MMA
+                // mixes the quad's k-slots, so the chunks are separated by zeroing the other half's nibbles; sum(x)
+                // comes from an all-ones A fragment.
+                const uint2 cm = *reinterpret_cast<const uint2*>(sl + G * GB + 512 + 8 * g);      // A: sc0 mn0 sc1 mn1 | B: ...
+                const uint4 dd = *reinterpret_cast<const uint4*>(sl + 8 * GB + 16 * g);           // A sb0, A sb1, B sb0, B sb1
+                const uint32_t da = (G >> 2) ? dd.y : dd.x, db = (G >> 2) ? dd.w : dd.z;
+                const float2 dda = __half22float2(*reinterpret_cast<const __half2*>(&da)), ddb = __half22float2(*reinterpret_cast<const __half2*>(&db));
+#pragma unroll
+                for (int hc = 0; hc < 2; hc++) {
+                    const bool mine = (t >> 1) == hc;
+                    float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint32_t one = mine ? 0x3F803F80u : 0u;
+                    mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
+                    mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
+                    mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
+                    mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
+                    mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
+                    mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                    const uint32_t ca = (cm.x >> (16 * hc)) & 0xFFFFu, cb = (cm.y >> (16 * hc)) & 0xFFFFu;
+                    const float s_a = dda.x * (float)(ca & 0xFF), m_a = dda.y * (float)(int8_t)(ca >> 8);
+                    const float s_b = ddb.x * (float)(cb & 0xFF), m_b = ddb.y * (float)(int8_t)(cb >> 8);
+                    acc[0] += fmaf(s_a, c[0], m_a * c1[0]); acc[1] += fmaf(s_a, c[1], m_a * c1[1]);
+                    acc[2] += fmaf(s_b, c[2], m_b * c1[2]); acc[3] += fmaf(s_b, c[3], m_b * c1[3]);
+                }
+            }
+        }
+        // this slice is consumed: order the warp's reads before the copy that refills the buffer, then issue it
+        __syncwarp();
+        if (lane == 0 && q + D < Q) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(q + D);
+        }
+        if (ks == KS - 1 && t < n) {
+            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) belong to pair slot t
+            const moexb_pair pr = a.pairs[start + t];
+            const float va = acc[0] + acc[1], vb = acc[2] + acc[3];
+            const int wt = rin * NW + warp;
+            if (DOWN) {
+                const int d = 16 * wt + g;
+                a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
+                a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
+            } else {
+                const int row = 8 * wt + g;
+                const float v = va / (1.f + expf(-va)) * vb;
+                if (a.act32) a.act32[(size_t)pr.p * EI + row] = v;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                __nv_bfloat16* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(row);
+                dst[0] = hi; dst[EI] = lo;
+            }
+        }
+    }
+}
+
+template <int FMT, bool DOWN, int NW, int D>
+constexpr int tl_smem_bytes() { return NW * D * tl_slice_bytes<FMT>() + 8 * st_bcol_bytes<DOWN>() + NW * D * 8 + 64; }
+
+}  // namespace moexb

@@ -256,10 +256,39 @@ def layer_sym(ctx):
     L.close()
 
 
-@pytest.mark.parametrize("path", [0, 1])
+def test_tiled_layout_round_trip(ctx):
+    """A tiled layer holds the same bytes as the reference blobs: synthetic fill and host upload both export unchanged."""
+    for fmt in FMTS:
+        L = m.Layer(ctx, fmt, 32)
+        L.fill_synth(6, 3)
+        for e in (0, 17, 32):
+            assert np.array_equal(L.export_blob(e), m.synth_expert_host(fmt, 6, 3, e)), f"format {fmt} expert {e}"
+        blob = m.synth_expert_host(fmt, 8, 1, 5)
+        L.upload_blob(7, blob)
+        assert np.array_equal(L.export_blob(7), blob)
+        assert np.array_equal(L.export_blob(6), m.synth_expert_host(fmt, 6, 3, 6))  # neighbours untouched
+        assert np.array_equal(L.export_blob(8), m.synth_expert_host(fmt, 6, 3, 8))
+        L.close()
+
+
+@pytest.fixture(scope="module")
+def layer_sym_ref(ctx):
+    """The same layer kept in the reference blob layout (for the row-piece streaming kernels and the SIMT kernels)."""
+    rng = np.random.default_rng(0)
+    L = m.Layer(ctx, m.FMT_SYM_F16, 256, layout=m.LAYOUT_REFERENCE)
+    L.fill_synth(0, 0)
+    L.set_router((rng.standard_normal((257, 2048)) * 0.02).astype(np.float32))
+    yield L
+    L.close()
+
+
+@pytest.mark.parametrize("kernels", ["tiled", "row-piece", "simt"])
 @pytest.mark.parametrize("T", [1, 4, 64])
-def test_layer_forward_symmetric(ctx, layer_sym, T, path):
+def test_layer_forward_symmetric(ctx, layer_sym, layer_sym_ref, T, kernels):
     L, W, host = layer_sym
+    if kernels != "tiled":
+        L = layer_sym_ref
+    path = 1 if kernels == "simt" else 0
     ctx.set_path(path)
     rng = np.random.default_rng(100 + T)
     X = rng.standard_normal((T, 2048)).astype(np.float32)
@@ -270,7 +299,7 @@ def test_layer_forward_symmetric(ctx, layer_sym, T, path):
     assert np.allclose(w.cpu().numpy(), rw, rtol=2e-6, atol=0)
     ctx.set_path(0)
     assert ctx.status() == 0
-    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"layer T={T} path={path}")
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"layer T={T} kernels={kernels}")
 
 
 def test_layer_forward_bf16_input_and_no_shared(layer_sym):
@@ -288,12 +317,13 @@ def test_layer_forward_bf16_input_and_no_shared(layer_sym):
 def test_layer_forward_zero_point(ctx):
     rng = np.random.default_rng(1)
     E = 32
-    L = m.Layer(ctx, m.FMT_ZP, E, router_dtype=m.F16)
-    L.fill_synth(1, 0)
     W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float16)
-    L.set_router(W)
     host = [m.synth_expert_host(m.FMT_ZP, 1, 0, e) for e in range(E + 1)]
-    for T, path in ((1, 0), (5, 0), (1, 1), (5, 1)):
+    for T, path, layout in ((1, 0, m.LAYOUT_TILED), (5, 0, m.LAYOUT_TILED), (1, 0, m.LAYOUT_REFERENCE), (5, 0, m.LAYOUT_REFERENCE),
+                            (1, 1, m.LAYOUT_REFERENCE), (5, 1, m.LAYOUT_REFERENCE)):
+        L = m.Layer(ctx, m.FMT_ZP, E, router_dtype=m.F16, layout=layout)
+        L.fill_synth(1, 0)
+        L.set_router(W)
         ctx.set_path(path)
         X = rng.standard_normal((T, 2048)).astype(np.float32)
         idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
@@ -302,8 +332,8 @@ def test_layer_forward_zero_point(ctx):
         assert ctx.status() == 0
         ref, ri, _, _ = o.layer_forward(m.FMT_ZP, host, W, X, 8)
         assert np.array_equal(idx.cpu().numpy(), ri)
-        check_ffn(out.cpu().numpy(), ref, m.FMT_ZP, f"zero-point layer T={T}")
-    L.close()
+        check_ffn(out.cpu().numpy(), ref, m.FMT_ZP, f"zero-point layer T={T} path={path} layout={layout}")
+        L.close()
 
 
 def test_expert_parallel_partial_layers_sum_to_the_whole(ctx, layer_sym):
@@ -335,6 +365,7 @@ def test_residual_block_chain(ctx):
         L.set_router(W)
         layers.append(L); Ws.append(W); hosts.append([m.synth_expert_host(m.FMT_SYM_F16, 2, l, e) for e in range(E + 1)])
     x_ref = rng.standard_normal((T, 2048)).astype(np.float32)
+    x0 = x_ref.copy()
     x_gpu = dev(x_ref.copy())
     for l in range(NL):
         idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
@@ -345,6 +376,20 @@ def test_residual_block_chain(ctx):
         assert np.array_equal(idx.cpu().numpy(), ri)
         check_ffn(forced, x_ref, m.FMT_SYM_F16, f"block {l}")
     check_ffn(x_gpu.cpu().numpy(), x_ref, m.FMT_SYM_F16, "chained")
+    # the same chain captured once as a CUDA graph (each layer hands its normalised output to the next), device and host buffers
+    for dt, xin in ((m.F32, torch.from_numpy(x0)), (m.BF16, torch.from_numpy(x0).to(torch.bfloat16))):
+        stack = m.Stack(ctx, layers, T, 8, dt)
+        assert stack.kernel_count > 0
+        before = m.launch_count()
+        y1 = stack.run(xin.to(DEV)).cpu().numpy()
+        assert m.launch_count() - before == stack.kernel_count
+        out_h = torch.empty(T, 2048).pin_memory()
+        stack.run_host(xin.pin_memory(), out_h)
+        assert np.array_equal(y1, out_h.numpy())
+        if dt == m.F32:
+            check_ffn(y1, x_ref, m.FMT_SYM_F16, "stack graph")
+        assert ctx.status() == 0
+        stack.close()
     for L in layers:
         L.close()
 
