@@ -554,9 +554,8 @@ static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float*
     });
 }
 
-template <int FMT, bool DOWN>
-static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, void* stream) {
-    constexpr int NW = 4, D = 4;
+template <int FMT, bool DOWN, int NW, int D>
+static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
     constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -568,15 +567,23 @@ static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, void* stream) {
     return MOEXB_OK;
 }
 
+// Two shapes of the same kernel, both two CTAs per SM: a few tokens leave only a handful of row tiles per SM, so CTAs of
+// 4 warps with 4 slices in flight each spread them over every SM; from 8 tokens on there is work for 16 warps per SM
+// (CTAs of 8 warps, 2 slices in flight each - the same bytes in flight, twice the issue slots in use).
+template <int FMT, bool DOWN>
+static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* stream) {
+    return T >= 8 ? tiled_launch_cfg<FMT, DOWN, 8, 2>(c, a, stream) : tiled_launch_cfg<FMT, DOWN, 4, 4>(c, a, stream);
+}
+
 // The same on blobs in the tiled layout (sub-item slots point into a tiled layer image).
-static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream) {
+static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, int T, void* stream) {
     TiledArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->err};
     return by_fmt(fmt, [&]<int FMT>() {
-        int rc = tiled_launch_one<FMT, false>(c, a, stream);
+        int rc = tiled_launch_one<FMT, false>(c, a, T, stream);
         if (rc != MOEXB_OK) return rc;
         TiledArgs d = a;
         d.xs = c->act_split;
-        return tiled_launch_one<FMT, true>(c, d, stream);
+        return tiled_launch_one<FMT, true>(c, d, T, stream);
     });
 }
 
@@ -677,7 +684,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
         }
         ranks = 0;
     } else if (decode) {
-        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream) : stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
+        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream) : stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;
         ranks = K + 1;
     } else {
@@ -689,7 +696,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             // pairs of experts that are not held here are never written: their ypair rows must read as zero
             if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
         }
-        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
+        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
            : streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
                        : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;

@@ -96,7 +96,7 @@ struct TiledArgs {
 // DOWN = false: row tile = 8 gate + 8 up rows, 4 slices (K = 2048); act = silu(gate) * up.
 // DOWN = true : row tile = 16 down rows, 1 slice (K = 512); ypair = w * (down . act).
 template <int FMT, bool DOWN, int NW, int D>
-__global__ void __launch_bounds__(NW * 32) stream_tiled_k(const TiledArgs a) {
+__global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) {
     constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
     constexpr int KS = DOWN ? 1 : 4;                       // slices per row tile
     constexpr int RPS = (DOWN ? 128 : 64) / NW;            // rounds per sub-item
@@ -168,9 +168,9 @@ __global__ void __launch_bounds__(NW * 32) stream_tiled_k(const TiledArgs a) {
                     const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
                     sa = s2.x; sb = s2.y;
                 }
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};  // two chains: consecutive MMAs do not wait on each other
-                mma_bf16(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
-                mma_bf16(e, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
+                float c[4], e[4];  // two chains: consecutive MMAs do not wait on each other
+                mma_bf16_first(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
+                mma_bf16_first(e, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
                 mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
                 mma_bf16(e, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
                 acc[0] = fmaf(c[0] + e[0], sa, acc[0]); acc[1] = fmaf(c[1] + e[1], sa, acc[1]);
