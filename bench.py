@@ -265,6 +265,8 @@ def main():
     prof_ms, prof_n = ctx.profile_read()
     ctx.profile(False)
     distinct = float(np.mean([len(torch.unique(idx[l])) for l in range(NL)])) + 1  # + the shared expert
+    # passes over expert weights: an expert with n tokens is streamed ceil(n / 4) times (4 pairs per sub-item)
+    passes = float(np.mean([int(torch.ceil(torch.bincount(idx[l].flatten().long(), minlength=E) / 4).sum()) for l in range(NL)])) + (T + 3) // 4
     eb = m.expert_bytes(fmt)
     qb_gu, qb_dn = 2 * EI * EH // 2, EH * EI // 2
     sc_total = eb - m.Q_BYTES
@@ -287,7 +289,7 @@ def main():
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "gate_up (expert gate/up projection + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes_per_launch": bytes_gu,
-                     "us_per_launch": per_launch_us["gate_up"], "distinct_experts_per_layer": distinct,
+                     "us_per_launch": per_launch_us["gate_up"], "distinct_experts_per_layer": distinct, "expert_passes_per_layer": passes,
                      "down": {"achieved": bytes_dn / (per_launch_us["down"] * 1e-6) / 1e9, "us_per_launch": per_launch_us["down"],
                               "algorithmic_bytes_per_launch": bytes_dn},
                      "whole_layer": {"algorithmic_bytes": layer_bytes, "us": ms_step * 1e3 / NL, "achieved": layer_bytes / (ms_step * 1e-3 / NL) / 1e9,

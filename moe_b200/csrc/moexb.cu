@@ -90,7 +90,7 @@ struct moexb_ctx {
     const uint8_t** slots = nullptr;  // decode: K+1 blob pointers
     float* wts = nullptr;             // decode: K+1 weights
     // streaming (tensor-core) path
-    __nv_bfloat16 *xs = nullptr, *act_split = nullptr;  // activations / act as bf16 hi+lo, permuted
+    uint16_t *xs = nullptr, *act_split = nullptr;       // activations / act as 16-bit hi + lo halves, permuted
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
@@ -544,12 +544,12 @@ static int stream_launch_one(moexb_ctx* c, const StreamArgs& a, void* stream) {
 // gate/up then down over the sub-items already planned in the context (subs, nsub);
 // xs = the split activations [token][2][H]; act32 optional.
 static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream) {
-    StreamArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->err};
+    StreamArgs a{c->subs, c->nsub, pairs, reinterpret_cast<const __nv_bfloat16*>(c->xs), act32, reinterpret_cast<__nv_bfloat16*>(c->act_split), ypair, c->err};
     return by_fmt(fmt, [&]<int FMT>() {
         int rc = stream_launch_one<FMT, false>(c, a, stream);
         if (rc != MOEXB_OK) return rc;
         StreamArgs d = a;
-        d.xs = c->act_split;
+        d.xs = reinterpret_cast<const __nv_bfloat16*>(c->act_split);
         return stream_launch_one<FMT, true>(c, d, stream);
     });
 }
@@ -587,10 +587,12 @@ static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* 
     });
 }
 
-static int split_launch(moexb_ctx* c, const float* x, int rows, void* stream) {
+// f16: the consumer is the tiled kernel of a symmetric format (fp16 operands); otherwise bf16
+static int split_launch(moexb_ctx* c, const float* x, int rows, bool f16, void* stream) {
     PROF(c, MOEXB_PROF_OTHER, stream);
     const size_t n = (size_t)rows * EH;
-    split_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(x, c->xs, EH, n);
+    if (f16) split_rows_k<true><<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(x, c->xs, EH, n);
+    else split_rows_k<false><<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(x, c->xs, EH, n);
     LAUNCHED("split_rows");
     return MOEXB_OK;
 }
@@ -603,7 +605,7 @@ extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_it
     REQUIRE(npairs > 0 && npairs <= c->max_tokens * (c->top_k + 1), "pairs_forward_tc: npairs=%d exceeds the context's capacity %d", npairs, c->max_tokens * (c->top_k + 1));
     REQUIRE(n_items >= 0 && n_items <= c->max_experts + 1, "pairs_forward_tc: n_items=%d exceeds the context's capacity %d", n_items, c->max_experts + 1);
     if (n_items == 0) return MOEXB_OK;
-    int rc = split_launch(c, X, T, stream);
+    int rc = split_launch(c, X, T, false, stream);
     if (rc != MOEXB_OK) return rc;
     plan_subitems_k<<<1, 1024, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub);
     LAUNCHED("plan_subitems");
@@ -655,16 +657,18 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     cudaStream_t st = S(stream);
     const bool tiled = L->layout == MOEXB_LAYOUT_TILED;
     const bool streaming = tiled || c->path == 0;
+    const bool f16 = tiled && L->fmt != FMT_ZP;  // element type of the split activations the expert kernels read
     const float* xf = xin;  // what the router and the experts see
     if (block) {
         xf = c->xn;
         if (!pre_normed) {
             PROF(c, MOEXB_PROF_OTHER, stream);
-            rmsnorm_split_k<<<T, 256, 0, st>>>(xin, c->xn, c->xs, 1e-6f);
+            if (f16) rmsnorm_split_k<true><<<T, 256, 0, st>>>(xin, c->xn, c->xs, 1e-6f);
+            else rmsnorm_split_k<false><<<T, 256, 0, st>>>(xin, c->xn, c->xs, 1e-6f);
             LAUNCHED("rmsnorm_split");
         }
     } else if (streaming) {
-        const int rc = split_launch(c, xf, T, stream);
+        const int rc = split_launch(c, xf, T, f16, stream);
         if (rc != MOEXB_OK) return rc;
     }
     const bool decode = T == 1 && all_local && shared;
@@ -680,7 +684,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             PROF(c, MOEXB_PROF_COMBINE, stream);
             residual_add_k<<<(unsigned)((EH / 4 + 255) / 256), 256, 0, st>>>(xin, c->moe, out, EH);
             LAUNCHED("residual_add");
-            if (next_norm) { rmsnorm_split_k<<<1, 256, 0, st>>>(out, c->xn, c->xs, 1e-6f); LAUNCHED("rmsnorm_split"); }
+            if (next_norm) { rmsnorm_split_k<false><<<1, 256, 0, st>>>(out, c->xn, c->xs, 1e-6f); LAUNCHED("rmsnorm_split"); }
         }
         ranks = 0;
     } else if (decode) {
@@ -704,7 +708,8 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     }
     if (ranks) {
         PROF(c, MOEXB_PROF_COMBINE, stream);
-        reduce_residual_norm_k<<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
+        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
+        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
         LAUNCHED("reduce_residual_norm");
     }
     if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
@@ -765,7 +770,10 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     REQUIRE(n_layers > 0 && T > 0 && T <= c->max_tokens && K > 0 && K <= c->top_k, "stack_create: n_layers=%d T=%d K=%d", n_layers, T, K);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "stack_create: x_dtype=%d", x_dtype);
     REQUIRE(!c->profiling, "stack_create: switch profiling off before capturing a graph");
-    for (int l = 0; l < n_layers; l++) REQUIRE(layers[l] && layers[l]->ctx == c, "stack_create: layer %d is null or belongs to another context", l);
+    for (int l = 0; l < n_layers; l++) {
+        REQUIRE(layers[l] && layers[l]->ctx == c, "stack_create: layer %d is null or belongs to another context", l);
+        REQUIRE(layers[l]->fmt == layers[0]->fmt && layers[l]->layout == layers[0]->layout, "stack_create: layer %d differs from layer 0 in format or layout", l);
+    }
     CUDA_TRY(cudaSetDevice(c->device));
     moexb_stack* s = new (std::nothrow) moexb_stack;
     if (!s) return fail(MOEXB_ERR_NOMEM, "out of host memory");

@@ -96,6 +96,33 @@ __device__ __forceinline__ void dq_word(uint32_t q, uint32_t (&P)[4]) {
     }
 }
 
+// The same for fp16 operands, with one shift per word instead of three: fp16 has a 10-bit mantissa, so a nibble can also
+// be picked up at bit 4 of its half-word ((x & 0x00F000F0) ^ C' = 1024 + 16 * (v + 8)) and one fused multiply-add
+// (* 1/16, - 72) turns that into v exactly. Only two's-complement nibbles (the symmetric formats).
+__device__ __forceinline__ void dq_word_h(uint32_t q, uint32_t (&P)[4]) {
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const uint32_t x = q >> (8 * j);
+        uint32_t r0, r1;
+        asm("lop3.b32 %0, %1, 0x000F000F, 0x64086408, 0x6A;" : "=r"(r0) : "r"(x));
+        asm("lop3.b32 %0, %1, 0x00F000F0, 0x64806480, 0x6A;" : "=r"(r1) : "r"(x));
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(P[2 * j]) : "r"(r0), "r"(0x64086408u));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(P[2 * j + 1]) : "r"(r1), "r"(0x2C002C00u), "r"(0xD480D480u));
+    }
+}
+
+// hi + lo halves of v as 16-bit patterns: fp16 (22 significand bits together) or bf16 (16 bits, full fp32 range)
+template <bool F16>
+__device__ __forceinline__ void split_hi_lo(float v, uint16_t& hi, uint16_t& lo) {
+    if constexpr (F16) {
+        const __half h = __float2half_rn(v), l = __float2half_rn(v - __half2float(h));
+        hi = __half_as_ushort(h); lo = __half_as_ushort(l);
+    } else {
+        const __nv_bfloat16 h = __float2bfloat16_rn(v), l = __float2bfloat16_rn(v - __bfloat162float(h));
+        hi = __bfloat16_as_ushort(h); lo = __bfloat16_as_ushort(l);
+    }
+}
+
 // d = a * b (no accumulator input: the zero operand is an immediate, so nothing has to be cleared first)
 __device__ __forceinline__ void mma_bf16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -104,6 +131,18 @@ __device__ __forceinline__ void mma_bf16_first(float (&d)[4], uint32_t a0, uint3
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool F16>
+__device__ __forceinline__ void mma_16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, bool first) {
+    if constexpr (F16) {
+        if (first) asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+        else asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                          : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        if (first) mma_bf16_first(d, a0, a1, a2, a3, b0, b1); else mma_bf16(d, a0, a1, a2, a3, b0, b1);
+    }
 }
 
 struct StreamArgs {
@@ -299,21 +338,23 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
     }
 }
 
-// x [rows][K] fp32 -> xs [rows][2][K] bf16: hi = bf16(x), lo = bf16(x - hi), both in the permuted order of split_pos.
-__global__ void split_rows_k(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, int K, size_t n) {
+// x [rows][K] fp32 -> xs [rows][2][K] 16-bit: hi and lo halves (see split_hi_lo), both in the permuted order of split_pos.
+template <bool F16>
+__global__ void split_rows_k(const float* __restrict__ x, uint16_t* __restrict__ xs, int K, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t r = i / K; const int k = (int)(i % K);
-    const float v = x[i];
-    const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-    __nv_bfloat16* dst = xs + r * 2 * K + split_pos(k);
+    uint16_t hi, lo;
+    split_hi_lo<F16>(x[i], hi, lo);
+    uint16_t* dst = xs + r * 2 * K + split_pos(k);
     dst[0] = hi; dst[K] = lo;
 }
 
 // One row of D = 2048 floats held 8 per thread (thread i: elements 4i..4i+3 and 1024+4i..1024+4i+3): the sum of squares
 // in the pinned order of rmsnorm_rows_k, then the normalised row as fp32 (for the router) and as bf16 hi + lo in the
 // permuted order (for the streaming kernels).
-__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, __nv_bfloat16* __restrict__ xs, float eps) {
+template <bool F16>
+__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, uint16_t* __restrict__ xs, float eps) {
     __shared__ float part[8];
     float ss = 0.f;
 #pragma unroll
@@ -333,7 +374,8 @@ __device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __res
         const float f[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const __nv_bfloat16 hi = __float2bfloat16_rn(f[i]), lo = __float2bfloat16_rn(f[i] - __bfloat162float(hi));
+            uint16_t hi, lo;
+            split_hi_lo<F16>(f[i], hi, lo);
             const int pos = split_pos(k0 + i);
             xs[pos] = hi; xs[EH + pos] = lo;
         }
@@ -341,20 +383,22 @@ __device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __res
 }
 
 // xn[t] = rmsnorm(x[t]) and its bf16 split, one block of 256 per row (H = 2048).
-__global__ void __launch_bounds__(256) rmsnorm_split_k(const float* __restrict__ x, float* __restrict__ xn, __nv_bfloat16* __restrict__ xs, float eps) {
+template <bool F16>
+__global__ void __launch_bounds__(256) rmsnorm_split_k(const float* __restrict__ x, float* __restrict__ xn, uint16_t* __restrict__ xs, float eps) {
     const size_t t = blockIdx.x;
     float v[8];
     const float4 a = *reinterpret_cast<const float4*>(x + t * EH + 4 * threadIdx.x), b = *reinterpret_cast<const float4*>(x + t * EH + 1024 + 4 * threadIdx.x);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    norm_split_row(v, xn + t * EH, xs + t * 2 * EH, eps);
+    norm_split_row<F16>(v, xn + t * EH, xs + t * 2 * EH, eps);
 }
 
 // The end of a layer in one pass over the token's row: moe[t] = sum_{r<K} ypair[t*K+r] in rank order (+ extra[t]: the
 // shared expert's row), out[t] = x[t] + moe[t] when x is given (the residual block) else moe[t]; and, when xn_next is
 // given, the next layer's normalised input and its bf16 split straight from the registers. One block of 256 per token.
+template <bool F16>
 __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __restrict__ ypair, const float* __restrict__ extra, const float* __restrict__ x,
                                                               float* __restrict__ out, int K, float* __restrict__ xn_next,
-                                                              __nv_bfloat16* __restrict__ xs_next, float eps) {
+                                                              uint16_t* __restrict__ xs_next, float eps) {
     const size_t t = blockIdx.x;
     float v[8];
 #pragma unroll
@@ -376,7 +420,7 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
         *reinterpret_cast<float4*>(out + t * EH + k0) = acc;
         v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
     }
-    if (xn_next) norm_split_row(v, xn_next + t * EH, xs_next + t * 2 * EH, eps);
+    if (xn_next) norm_split_row<F16>(v, xn_next + t * EH, xs_next + t * 2 * EH, eps);
 }
 
 // Exclusive prefix sum over the 1024 threads of a block; every thread also gets the total.

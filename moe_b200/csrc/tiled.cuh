@@ -80,9 +80,9 @@ struct TiledArgs {
     const moexb_pair_item* subs;  // sub-items: at most ST_MAXP pairs each, slot = tiled blob
     const int* nsub;
     const moexb_pair* pairs;
-    const __nv_bfloat16* xs;      // gate/up: activations [token][2][H] (hi, lo), permuted; down: act [pair p][2][I]
+    const uint16_t* xs;           // gate/up: activations [token][2][H] (hi, lo: fp16 for the symmetric formats, bf16 for zero point), permuted; down: act [pair p][2][I]
     float* act32;                 // gate/up: optional fp32 copy of act [p][I]
-    __nv_bfloat16* act_split;     // gate/up output [p][2][I], permuted
+    uint16_t* act_split;          // gate/up output [p][2][I], permuted
     float* ypair;                 // down output [p][H]
     int* err;
 };
@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
     constexpr int KB = DOWN ? EI : EH;
     constexpr int BCOL = st_bcol_bytes<DOWN>();
     constexpr bool Z = FMT == FMT_ZP;
+    constexpr bool F16 = !Z;  // symmetric formats run on fp16 operands (cheaper unpacking, 22-bit activations); zero point on bf16
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* bsm = smem + NW * D * SB;                                 // 8 activation columns
     uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);      // full[NW][D]
@@ -157,8 +158,8 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
             const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
             const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
             uint32_t Pa[2][4], Pb[2][4];
-            dq_word<!Z>(qq.x, Pa[0]); dq_word<!Z>(qq.y, Pa[1]);
-            dq_word<!Z>(qq.z, Pb[0]); dq_word<!Z>(qq.w, Pb[1]);
+            if constexpr (F16) { dq_word_h(qq.x, Pa[0]); dq_word_h(qq.y, Pa[1]); dq_word_h(qq.z, Pb[0]); dq_word_h(qq.w, Pb[1]); }
+            else { dq_word<false>(qq.x, Pa[0]); dq_word<false>(qq.y, Pa[1]); dq_word<false>(qq.z, Pb[0]); dq_word<false>(qq.w, Pb[1]); }
             if constexpr (!Z) {
                 float sa, sb;
                 if constexpr (FMT == FMT_SYM_F16) {
@@ -168,13 +169,13 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
                     const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
                     sa = s2.x; sb = s2.y;
                 }
-                float c[4], e[4];  // two chains: consecutive MMAs do not wait on each other
-                mma_bf16_first(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y);
-                mma_bf16_first(e, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w);
-                mma_bf16(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y);
-                mma_bf16(e, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w);
-                acc[0] = fmaf(c[0] + e[0], sa, acc[0]); acc[1] = fmaf(c[1] + e[1], sa, acc[1]);
-                acc[2] = fmaf(c[2] + e[2], sb, acc[2]); acc[3] = fmaf(c[3] + e[3], sb, acc[3]);
+                float c[4];  // one chain of four MMAs per group; the unrolled groups interleave
+                mma_16<F16>(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y, true);
+                mma_16<F16>(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w, false);
+                mma_16<F16>(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y, false);
+                mma_16<F16>(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w, false);
+                acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
+                acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
             } else {
                 // zero point: each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial sums
                 // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 0 of the group, lanes t = 2,3 chunk 1, and an MMA
@@ -222,8 +223,9 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
                 const int row = 8 * wt + g;
                 const float v = va / (1.f + expf(-va)) * vb;
                 if (a.act32) a.act32[(size_t)pr.p * EI + row] = v;
-                const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-                __nv_bfloat16* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(row);
+                uint16_t hi, lo;
+                split_hi_lo<F16>(v, hi, lo);
+                uint16_t* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(row);
                 dst[0] = hi; dst[EI] = lo;
             }
         }
