@@ -77,7 +77,7 @@ const Tables& host_tables() {
 
 }  // namespace
 
-constexpr int STAGING_BLOBS = 8;
+constexpr int STAGING_BLOBS = 32;
 
 struct moexb_ctx {
     int device = 0, max_tokens = 0, max_experts = 0, top_k = 0;
@@ -144,7 +144,7 @@ static int gemv_any(const WT* W, const float* x, float* y, int I, int O, void* s
     REQUIRE(W && x && y, "gemv: null pointer");
     REQUIRE(I > 0 && I % 128 == 0 && O > 0 && rows > 0, "gemv: I=%d must be a positive multiple of 128, O=%d, rows=%d", I, O, rows);
     if (rows >= 8) {
-        constexpr int WARPS = 8, TO = 4, TR = 8;
+        constexpr int WARPS = 4, TO = 4, TR = 8;  // 16 outputs x 8 rows per block: 17 x 8 blocks for the 64-token router
         const int smem = TR * I * (int)sizeof(float);
         REQUIRE(smem <= 200 * 1024, "gemv: I=%d is too large for the batched kernel", I);
         static std::once_flag once;
@@ -174,8 +174,9 @@ static int topk_launch(const float* logits, int E, int K, int norm, int* idx, fl
     REQUIRE(E > 0 && E % 32 == 0 && E <= 1024, "router_topk: E=%d must be a multiple of 32 up to 1024", E);
     REQUIRE(K > 0 && K < 32 && K <= E, "router_topk: K=%d out of range", K);
     REQUIRE(T > 0 && ld >= E, "router_topk: T=%d, ld=%d", T, ld);
-    constexpr int WARPS = 4;
-    router_topk_k<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
+    constexpr int WARPS = 2;
+    if (E <= 256) router_topk_k<WARPS, 8><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
+    else router_topk_k<WARPS, 32><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
     LAUNCHED("router_topk");
     return MOEXB_OK;
 }
@@ -463,10 +464,8 @@ static int to_layer_layout(moexb_layer* L, const uint8_t* src, uint8_t* dst, int
         return MOEXB_OK;
     }
     return by_fmt(L->fmt, [&]<int FMT>() {
-        for (int i = 0; i < n; i++) {
-            tile_expert_k<FMT, true><<<TL_SLICES, 256, 0, st>>>(src + i * eb, dst + i * eb);
-            LAUNCHED("tile_expert");
-        }
+        tile_expert_k<FMT, true><<<dim3(TL_SLICES, n), 256, 0, st>>>(src, dst);
+        LAUNCHED("tile_expert");
         return (int)MOEXB_OK;
     });
 }

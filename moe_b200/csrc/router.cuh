@@ -23,10 +23,15 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_rows_k(const WT* __restrict__
     const float* xr = x + (size_t)blockIdx.y * I;
     const WT* wr = W + (size_t)o * I;
     float acc = 0.f;
-    for (int c = 0; c < I / 128; c++) {
-        const float4 w = ld_w4(wr, (size_t)128 * c + 4 * lane);
-        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + 128 * c + 4 * lane));
-        acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
+    constexpr int U = 8;  // loads of U steps are in flight before the first multiply-add; the summation order is unchanged
+    for (int c0 = 0; c0 < I / 128; c0 += U) {
+        float4 w[U], v[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) { w[u] = ld_w4(wr, (size_t)128 * (c0 + u) + 4 * lane); v[u] = __ldg(reinterpret_cast<const float4*>(xr + 128 * (c0 + u) + 4 * lane)); }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) { acc = fmaf(w[u].x, v[u].x, acc); acc = fmaf(w[u].y, v[u].y, acc); acc = fmaf(w[u].z, v[u].z, acc); acc = fmaf(w[u].w, v[u].w, acc); }
     }
     acc = warp_sum(acc);
     if (lane == 0) y[(size_t)blockIdx.y * O + o] = acc;
@@ -53,10 +58,17 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
     for (int r = 0; r < TR; r++)
 #pragma unroll
         for (int o = 0; o < TO; o++) acc[r][o] = 0.f;
+    float4 wn[TO];  // the next step's weights are loaded while this step's products run
+#pragma unroll
+    for (int o = 0; o < TO; o++) wn[o] = ld_w4(W + (size_t)min(o0 + o, O - 1) * I, (size_t)4 * lane);
     for (int c = 0; c < I / 128; c++) {
         float4 w[TO];
 #pragma unroll
-        for (int o = 0; o < TO; o++) w[o] = ld_w4(W + (size_t)min(o0 + o, O - 1) * I, (size_t)128 * c + 4 * lane);
+        for (int o = 0; o < TO; o++) w[o] = wn[o];
+        if (c + 1 < I / 128) {
+#pragma unroll
+            for (int o = 0; o < TO; o++) wn[o] = ld_w4(W + (size_t)min(o0 + o, O - 1) * I, (size_t)128 * (c + 1) + 4 * lane);
+        }
 #pragma unroll
         for (int r = 0; r < TR; r++) {
             const float4 v = *reinterpret_cast<const float4*>(xsm + r * I + 128 * c + 4 * lane);
@@ -83,7 +95,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
 // Selection compares logits (softmax is monotone). NaN logits count as -inf. Optional decode outputs: slots_out /
 // wts_out [K+1] = the selected experts' blob pointers and weights followed by the shared expert with weight
 // sigmoid(logits[E]); dsubs / dpairs / dnsub = the same K+1 experts as one-pair sub-items for the streaming kernels (T = 1).
-template <int WARPS>
+template <int WARPS, int NJ>
 __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restrict__ logits, int E, int K, int norm, int ld,
                                                             int* __restrict__ idx, float* __restrict__ w, int T,
                                                             const uint8_t* const* __restrict__ slot_table,
@@ -93,11 +105,11 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
     const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float* l = logits + (size_t)t * ld;
-    const int nj = E >> 5;
-    float v[32];
+    const int nj = E >> 5;  // <= NJ
+    float v[NJ];
     float m = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
+    for (int j = 0; j < NJ; j++) {
         v[j] = -INFINITY;
         if (j < nj) { const float a = l[lane + 32 * j]; v[j] = a != a ? -INFINITY : a; }
         m = fmaxf(m, v[j]);
@@ -106,7 +118,7 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 32; j++) if (j < nj) sum += expf(v[j] - m);
+    for (int j = 0; j < NJ; j++) if (j < nj) sum += expf(v[j] - m);
     sum = warp_sum(sum);
     unsigned taken = 0;
     float mine = 0.f, total = 0.f;  // lane k keeps the k-th probability
@@ -114,7 +126,7 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
     for (int k = 0; k < K; k++) {
         float bv = -INFINITY; int bi = 0x7fffffff;
 #pragma unroll
-        for (int j = 0; j < 32; j++)
+        for (int j = 0; j < NJ; j++)
             if (j < nj && !(taken >> j & 1) && (v[j] > bv || bi == 0x7fffffff)) { bv = v[j]; bi = lane + 32 * j; }
 #pragma unroll
         for (int o = 16; o; o >>= 1) {

@@ -405,9 +405,14 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
     for (int h = 0; h < 2; h++) {
         const int k0 = 1024 * h + 4 * threadIdx.x;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < K; r++) {
-            const float4 y = *reinterpret_cast<const float4*>(ypair + (t * K + r) * EH + k0);
-            acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+        for (int rb = 0; rb < K; rb += 4) {  // four rows in flight, added in rank order
+            float4 y[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (rb + u < K) y[u] = *reinterpret_cast<const float4*>(ypair + (t * K + rb + u) * EH + k0);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (rb + u < K) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
         }
         if (extra) {
             const float4 y = *reinterpret_cast<const float4*>(extra + t * EH + k0);

@@ -44,11 +44,13 @@ __device__ __forceinline__ void tl_row_of(int si, int m, size_t& qoff, size_t& c
     }
 }
 
-// One block per slice: reference-layout blob <-> tiled blob (TO_TILED = direction). 256 threads.
+// One block per slice, blockIdx.y = expert of the batch (both sides advance by the blob size): reference-layout blob <->
+// tiled blob (TO_TILED = direction). 256 threads.
 template <int FMT, bool TO_TILED>
 __global__ void __launch_bounds__(256) tile_expert_k(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst) {
     constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
     const int si = blockIdx.x, tid = threadIdx.x;
+    src += (size_t)blockIdx.y * expert_bytes(FMT); dst += (size_t)blockIdx.y * expert_bytes(FMT);
     const uint8_t* ref = TO_TILED ? src : dst;   // the reference-layout side
     uint8_t* til = const_cast<uint8_t*>(TO_TILED ? dst : src) + (size_t)si * SB;
     uint8_t* refw = const_cast<uint8_t*>(ref);
