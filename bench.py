@@ -167,7 +167,8 @@ def config_of(workload, n_gpus):
             "expert_format": {"sym_f16": "i4_gs64 (fp16 group scales)", "zp": "GGUF Q4_K as zero-point blobs"}[fmtname],
             "input_dtype": xdt, "router": "fp32", "l2": "weights of one step (%.1f GB) exceed L2; no flush needed" % (NL * (E + 1) * 1.671168e-3)
             if NL > 1 else "429 MB of layer weights exceed L2",
-            "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} replicas"}
+            "parallelism": "single GPU" if n_gpus == 1 else f"expert parallel over {n_gpus} GPUs: {E // n_gpus} routed experts per rank, router and "
+                           "shared expert replicated, one NCCL all-reduce of the partial outputs per layer"}
 
 
 def main():
@@ -199,17 +200,36 @@ def main():
     T, NL, fmtname, xdt = WORKLOADS[args.workload]
     fmt = m.FMT_ZP if fmtname == "zp" else m.FMT_SYM_F16
     ctx = m.Context(local, max_tokens=T, max_experts=E, top_k=K)
+    from moe_b200 import ep
+    first, count = ep.expert_range(E, rank, world)
     layers = []
     for l in range(NL):
-        L = m.Layer(ctx, fmt, E)
+        L = m.Layer(ctx, fmt, E, first_local=first, n_local=count)
         L.fill_synth(SEED, l)
         L.set_router(router_weights(l))
         layers.append(L)
     torch.cuda.synchronize()
     x_torch_dtype = torch.bfloat16 if xdt == "bf16" else torch.float32
-    stack = m.Stack(ctx, layers, T, K, m.BF16 if xdt == "bf16" else m.F32)
-    nsteps = args.warmup + args.steps
-    Xh = [torch.from_numpy(tokens(T, (rank * 1000 + s) % 8)).to(x_torch_dtype).pin_memory() for s in range(8)]
+    if world == 1:
+        stack = m.Stack(ctx, layers, T, K, m.BF16 if xdt == "bf16" else m.F32)
+    else:
+        # expert parallel: every rank sees the same tokens; the step is captured with its all-reduces in one graph
+        eps = ep.EPStack(ctx, layers, T, K, x_torch_dtype)
+
+        class _S:  # the Stack interface on top of the expert-parallel step
+            kernel_count = 0
+
+            def run(self, X, out):
+                out.copy_(eps.run(X))
+
+            def run_host(self, Xh_, out_h_):
+                out_h_.copy_(eps.run(Xh_), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+            def close(self):
+                pass
+        stack = _S()
+    Xh = [torch.from_numpy(tokens(T, s % 8)).to(x_torch_dtype).pin_memory() for s in range(8)]
     Xd = [x.to(dev) for x in Xh]
     out = torch.empty(T, EH, device=dev)
     out_h = torch.empty(T, EH).pin_memory()
@@ -256,17 +276,25 @@ def main():
     idx = torch.empty(NL, T, K, dtype=torch.int32, device=dev)
     reps = 3
     bufs = [torch.empty(T, EH, device=dev), torch.empty(T, EH, device=dev)]
+    sh0, sh1 = ep.shared_token_range(T, rank, world)
     for r in range(reps + 1):
         x = Xd[r % 8]
         for l, L in enumerate(layers):
-            x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2)
+            if world == 1:
+                x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2)
+            else:
+                part = L.forward_ep(x, T, K, bufs[l & 1], sh0, sh1, idx=idx[l])
+                dist.all_reduce(part)
+                x = x.float() + part
         if r == 0:
             ctx.profile_read()  # discard the first pass
     prof_ms, prof_n = ctx.profile_read()
     ctx.profile(False)
-    distinct = float(np.mean([len(torch.unique(idx[l])) for l in range(NL)])) + 1  # + the shared expert
+    def local(ix):  # the routed experts this rank holds
+        return ix[(ix >= first) & (ix < first + count)]
+    distinct = float(np.mean([len(torch.unique(local(idx[l]))) for l in range(NL)])) + 1  # + the shared expert
     # passes over expert weights: an expert with n tokens is streamed ceil(n / 4) times (4 pairs per sub-item)
-    passes = float(np.mean([int(torch.ceil(torch.bincount(idx[l].flatten().long(), minlength=E) / 4).sum()) for l in range(NL)])) + (T + 3) // 4
+    passes = float(np.mean([int(torch.ceil(torch.bincount(local(idx[l].flatten()).long(), minlength=E) / 4).sum()) for l in range(NL)])) + (sh1 - sh0 + 3) // 4
     eb = m.expert_bytes(fmt)
     qb_gu, qb_dn = 2 * EI * EH // 2, EH * EI // 2
     sc_total = eb - m.Q_BYTES
@@ -278,10 +306,10 @@ def main():
     peak, peak_kind = measured_peak()
     achieved = bytes_gu / (per_launch_us["gate_up"] * 1e-6) / 1e9
     layer_bytes = distinct * eb + (E + 1) * EH * 4 + 2 * T * EH * 4
-    tokens_total = T * world
+    tokens_total = T  # the same 64 tokens at every N: strong scaling
     line = {
         "metric": "MoE int4 expert-FFN tokens/s", "value": tokens_total / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 accumulate on int4 weights", "data": "synthetic",
         "config": config_of(args.workload, world),
         "e2e": {"value": tokens_total / (float(e2e_ms.item()) * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Xh[0].numel() * Xh[0].element_size(),

@@ -210,6 +210,14 @@ int moexb_layer_fill_synth(moexb_layer* layer, unsigned seed, int layer_index, v
 int moexb_layer_forward(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x_dtype, int T, int K, float* out,
                         int* idx_out, float* w_out, int flags, void* stream);
 
+/* The expert-parallel share of one residual block. Every rank of R holds the router, the shared expert and a slice of
+ * the routed experts (first_local / n_local of moexb_layer_create) and sees all T tokens: it normalises X, routes every
+ * token (the logits are bit-identical on all ranks), runs the pairs of the experts it holds, and the shared expert for
+ * the tokens [shared_t0, shared_t1) only. out [T][H] = that partial sum, without the residual; the ranks' outputs are
+ * then added (one all-reduce, the path's only exchange) and x_next = X + sum. The reference has no multi-GPU path. */
+int moexb_layer_forward_ep(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x_dtype, int T, int K, float* out,
+                           int* idx_out, float* w_out, int shared_t0, int shared_t1, void* stream);
+
 /* ---- a stack of layers as one replayable unit ---------------------------------------------------------------------- */
 
 typedef struct moexb_stack moexb_stack;

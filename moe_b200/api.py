@@ -221,6 +221,12 @@ class Layer:
         check(lib().moexb_layer_forward(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), flags, _stream()))
         return out
 
+    def forward_ep(self, X, T, K, out, shared_t0, shared_t1, idx=None, w=None):
+        """moexb_layer_forward_ep: this rank's partial of one residual block (no residual added)."""
+        x_dtype = BF16 if X.dtype == torch.bfloat16 else F32
+        check(lib().moexb_layer_forward_ep(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), shared_t0, shared_t1, _stream()))
+        return out
+
     def close(self):
         if self.h:
             lib().moexb_layer_destroy(self.h)

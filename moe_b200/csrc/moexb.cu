@@ -649,8 +649,9 @@ static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int
 // rmsnorm(xin) and its bf16 split (left there by the previous layer of a stack); next_norm: leave rmsnorm(out) and its
 // split in the context for the next layer.
 static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int K, float* out, int* idx_out, float* w_out, int flags,
-                      void* stream, bool pre_normed, bool next_norm) {
-    const bool shared = !(flags & 1), block = flags & 2;
+                      void* stream, bool pre_normed, bool next_norm, int sh0 = 0, int sh1 = -1) {
+    if (sh1 < 0) sh1 = T;
+    const bool shared = !(flags & 1) && sh1 > sh0, block = flags & 2, partial = flags & 4;
     const bool all_local = L->n_local == L->n_routed;
     const int E = L->n_routed, ld = E + 1;
     cudaStream_t st = S(stream);
@@ -670,11 +671,12 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
         const int rc = split_launch(c, xf, T, f16, stream);
         if (rc != MOEXB_OK) return rc;
     }
-    const bool decode = T == 1 && all_local && shared;
+    const bool decode = T == 1 && all_local && shared && !partial;
     int rc = layer_route(c, L, xf, T, K, stream, decode);
     if (rc != MOEXB_OK) return rc;
     int ranks = K;                  // rows of ypair per token that the final reduction adds
     const float* extra = nullptr;   // + the shared expert's rows
+    if (partial && !streaming) return fail(MOEXB_ERR_UNSUPPORTED, "layer_forward: partial outputs need the streaming kernels");
     if (decode && !streaming) {
         // one token on the fp32 SIMT kernels: the K routed experts and the shared expert as K+1 decode experts
         rc = decode_launch(c, L->fmt, c->slots, c->wts, K + 1, xf, c->act, block ? c->moe : out, stream, nullptr);
@@ -694,7 +696,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
         {
             PROF(c, MOEXB_PROF_GROUP, stream);
             group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                                                 shared ? c->logits + E : nullptr, ld);
+                                                                 shared ? c->logits + E : nullptr, ld, sh0, sh1);
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: their ypair rows must read as zero
             if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
@@ -707,8 +709,8 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     }
     if (ranks) {
         PROF(c, MOEXB_PROF_COMBINE, stream);
-        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
-        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, block ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f);
+        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1);
+        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1);
         LAUNCHED("reduce_residual_norm");
     }
     if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
@@ -739,6 +741,20 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
     return layer_impl(c, L, xin, T, K, out, idx_out, w_out, flags, stream, false, false);
+}
+
+int moexb_layer_forward_ep(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype, int T, int K, float* out, int* idx_out,
+                           float* w_out, int shared_t0, int shared_t1, void* stream) {
+    REQUIRE(c && L && X && out, "layer_forward_ep: null pointer");
+    REQUIRE(L->ctx == c, "layer_forward_ep: layer belongs to another context");
+    REQUIRE(T > 0 && T <= c->max_tokens, "layer_forward_ep: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
+    REQUIRE(K > 0 && K <= c->top_k, "layer_forward_ep: K=%d exceeds the context's top_k=%d", K, c->top_k);
+    REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "layer_forward_ep: x_dtype=%d", x_dtype);
+    REQUIRE(shared_t0 >= 0 && shared_t0 <= shared_t1 && shared_t1 <= T, "layer_forward_ep: shared token range [%d, %d) outside 0..%d", shared_t0, shared_t1, T);
+    const float* xin;
+    int rc = layer_input(c, X, x_dtype, T, stream, &xin);
+    if (rc != MOEXB_OK) return rc;
+    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, 2 | 4, stream, false, false, shared_t0, shared_t1);
 }
 
 // ---- stack of layers as one CUDA graph ----------------------------------------------------------------------------------

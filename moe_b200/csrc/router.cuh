@@ -236,12 +236,13 @@ __device__ __forceinline__ void block_scan3_256(int (&v)[3], int (&tot)[3]) {
 // Grouping and planning in one launch (the work of group_count_k + group_scatter_k, plus the sub-items of at most MAXP
 // pairs that the streaming kernels walk). Every block builds the per-expert histogram of the T*K pairs in shared memory
 // and scans it; then one warp per expert writes that expert's item, its sub-items and its pairs in token order.
-// Optional shared expert as in group_scatter_k. E <= 1024; 256 threads; grid ceil(E / 8).
+// Optional shared expert as in group_scatter_k, for the tokens [sh0, sh1). E <= 1024; 256 threads; grid ceil(E / 8).
 template <int MAXP>
 __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
                                                     const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
                                                     moexb_pair* __restrict__ pairs, int* __restrict__ nitems, moexb_pair_item* __restrict__ subs,
-                                                    int* __restrict__ nsub, const float* __restrict__ gate_logits, int gl_stride) {
+                                                    int* __restrict__ nsub, const float* __restrict__ gate_logits, int gl_stride,
+                                                    int sh0, int sh1) {
     __shared__ int cnt[1024], start[1024], item_of[1024], sub_at[1024];
     __shared__ int s_tot[3];
     const int n = T * K, tid = threadIdx.x, lane = tid & 31;
@@ -286,11 +287,13 @@ __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx,
     }
     if (blockIdx.x == 0) {
         const int np = s_tot[0], ni = s_tot[1], ns = s_tot[2];
-        if (gate_logits && slot_table[E]) {
+        if (gate_logits && slot_table[E] && sh1 > sh0) {
+            // the shared expert for tokens [sh0, sh1) (all of them on one GPU; a slice per rank under expert parallelism)
             const uint8_t* slot = slot_table[E];
-            if (tid == 0) { items[ni] = {slot, np, T}; *nitems = ni + 1; *nsub = ns + (T + MAXP - 1) / MAXP; }
-            for (int t = tid; t < T; t += 256) pairs[np + t] = {t, n + t, 1.f / (1.f + expf(-gate_logits[(size_t)t * gl_stride]))};
-            for (int j = tid; j * MAXP < T; j += 256) subs[ns + j] = {slot, np + j * MAXP, min(MAXP, T - j * MAXP)};
+            const int Ts = sh1 - sh0;
+            if (tid == 0) { items[ni] = {slot, np, Ts}; *nitems = ni + 1; *nsub = ns + (Ts + MAXP - 1) / MAXP; }
+            for (int t = tid; t < Ts; t += 256) pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gate_logits[(size_t)(sh0 + t) * gl_stride]))};
+            for (int j = tid; j * MAXP < Ts; j += 256) subs[ns + j] = {slot, np + j * MAXP, min(MAXP, Ts - j * MAXP)};
         } else if (tid == 0) { *nitems = ni; *nsub = ns; }
     }
 }

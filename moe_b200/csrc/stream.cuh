@@ -398,8 +398,9 @@ __global__ void __launch_bounds__(256) rmsnorm_split_k(const float* __restrict__
 template <bool F16>
 __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __restrict__ ypair, const float* __restrict__ extra, const float* __restrict__ x,
                                                               float* __restrict__ out, int K, float* __restrict__ xn_next,
-                                                              uint16_t* __restrict__ xs_next, float eps) {
+                                                              uint16_t* __restrict__ xs_next, float eps, int ex0, int ex1) {
     const size_t t = blockIdx.x;
+    if ((int)t < ex0 || (int)t >= ex1) extra = nullptr;  // extra rows exist only for tokens [ex0, ex1)
     float v[8];
 #pragma unroll
     for (int h = 0; h < 2; h++) {

@@ -352,6 +352,24 @@ def test_expert_parallel_partial_layers_sum_to_the_whole(ctx, layer_sym):
     check_ffn(parts[0] + parts[1], ref, m.FMT_SYM_F16, "expert-parallel halves")
 
 
+def test_expert_parallel_entry_point(ctx, layer_sym):
+    """moexb_layer_forward_ep as two ranks would call it (experts split 128/128, shared expert for tokens [0,3) and [3,8)):
+    X + the sum of the two partial outputs is the full residual block."""
+    _, W, host = layer_sym
+    T = 8
+    X = np.random.default_rng(19).standard_normal((T, 2048)).astype(np.float32)
+    total = np.zeros((T, 2048), np.float32)
+    for r, (t0, t1) in enumerate(((0, 3), (3, 8))):
+        L = m.Layer(ctx, m.FMT_SYM_F16, 256, first_local=128 * r, n_local=128)
+        L.fill_synth(0, 0); L.set_router(W)
+        out = torch.empty(T, 2048, device=DEV)
+        total += L.forward_ep(dev(X), T, 8, out, t0, t1).cpu().numpy()
+        L.close()
+    assert ctx.status() == 0
+    moe, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, o.rmsnorm(X), 8)
+    check_ffn(X + total, X + moe, m.FMT_SYM_F16, "expert-parallel block")
+
+
 def test_residual_block_chain(ctx):
     """x_{l+1} = x_l + moe_l(rmsnorm(x_l)) over 3 layers of 32 experts: every layer checked with the oracle's own input
     (teacher forcing), and the chained result end to end."""
