@@ -330,12 +330,16 @@ def main():
         line["cpu_baseline"], _ = cpu_arm(args.workload, 2 if T <= 64 else 1, 3)
     if rank == 0:
         print(json.dumps(line))
+    if dist:
+        # leave without tearing NCCL down under a live CUDA graph: everything has been measured and printed
+        sys.stdout.flush()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     stack.close()
     for L in layers:
         L.close()
     ctx.close()
-    if dist:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

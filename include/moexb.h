@@ -214,9 +214,14 @@ int moexb_layer_forward(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x
  * the routed experts (first_local / n_local of moexb_layer_create) and sees all T tokens: it normalises X, routes every
  * token (the logits are bit-identical on all ranks), runs the pairs of the experts it holds, and the shared expert for
  * the tokens [shared_t0, shared_t1) only. out [T][H] = that partial sum, without the residual; the ranks' outputs are
- * then added (one all-reduce, the path's only exchange) and x_next = X + sum. The reference has no multi-GPU path. */
+ * then added (one all-reduce, the path's only exchange) and x_next = X + sum. pre_normed != 0: the context already holds
+ * the normalised X (left by moexb_ep_residual_norm of the previous layer). The reference has no multi-GPU path. */
 int moexb_layer_forward_ep(moexb_ctx* ctx, moexb_layer* layer, const void* X, int x_dtype, int T, int K, float* out,
-                           int* idx_out, float* w_out, int shared_t0, int shared_t1, void* stream);
+                           int* idx_out, float* w_out, int shared_t0, int shared_t1, int pre_normed, void* stream);
+/* After the all-reduce: out = x + total (out may be x), and, when `next` is given, the normalised out and its 16-bit
+ * split are left in the context for next's moexb_layer_forward_ep(pre_normed = 1). */
+int moexb_ep_residual_norm(moexb_ctx* ctx, moexb_layer* next, const float* x, const float* total, float* out, int T,
+                           void* stream);
 
 /* ---- a stack of layers as one replayable unit ---------------------------------------------------------------------- */
 

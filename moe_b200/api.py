@@ -221,16 +221,23 @@ class Layer:
         check(lib().moexb_layer_forward(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), flags, _stream()))
         return out
 
-    def forward_ep(self, X, T, K, out, shared_t0, shared_t1, idx=None, w=None):
+    def forward_ep(self, X, T, K, out, shared_t0, shared_t1, idx=None, w=None, pre_normed=False):
         """moexb_layer_forward_ep: this rank's partial of one residual block (no residual added)."""
         x_dtype = BF16 if X.dtype == torch.bfloat16 else F32
-        check(lib().moexb_layer_forward_ep(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), shared_t0, shared_t1, _stream()))
+        check(lib().moexb_layer_forward_ep(self.ctx.h, self.h, _ptr(X), x_dtype, T, K, _ptr(out), _ptr(idx), _ptr(w), shared_t0, shared_t1,
+                                           int(pre_normed), _stream()))
         return out
 
     def close(self):
         if self.h:
             lib().moexb_layer_destroy(self.h)
             self.h = None
+
+
+def ep_residual_norm(ctx, next_layer, x, total, out, T):
+    """moexb_ep_residual_norm: out = x + total, plus the next layer's normalised input when next_layer is given."""
+    check(lib().moexb_ep_residual_norm(ctx.h, next_layer.h if next_layer is not None else None, _ptr(x), _ptr(total), _ptr(out), T, _stream()))
+    return out
 
 
 class Stack:

@@ -698,8 +698,9 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
                                                                  shared ? c->logits + E : nullptr, ld, sh0, sh1);
             LAUNCHED("group_plan");
-            // pairs of experts that are not held here are never written: their ypair rows must read as zero
-            if (!all_local) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
+            // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
+            // reduction skips them by expert id
+            if (!all_local && !streaming) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
         }
         rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
            : streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
@@ -709,8 +710,10 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     }
     if (ranks) {
         PROF(c, MOEXB_PROF_COMBINE, stream);
-        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1);
-        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1);
+        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1,
+                                                                    (!all_local && ranks == K) ? c->idx : nullptr, L->first_local, L->first_local + L->n_local);
+        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1,
+                                                                    (!all_local && ranks == K) ? c->idx : nullptr, L->first_local, L->first_local + L->n_local);
         LAUNCHED("reduce_residual_norm");
     }
     if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
@@ -744,7 +747,7 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
 }
 
 int moexb_layer_forward_ep(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype, int T, int K, float* out, int* idx_out,
-                           float* w_out, int shared_t0, int shared_t1, void* stream) {
+                           float* w_out, int shared_t0, int shared_t1, int pre_normed, void* stream) {
     REQUIRE(c && L && X && out, "layer_forward_ep: null pointer");
     REQUIRE(L->ctx == c, "layer_forward_ep: layer belongs to another context");
     REQUIRE(T > 0 && T <= c->max_tokens, "layer_forward_ep: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
@@ -754,7 +757,19 @@ int moexb_layer_forward_ep(moexb_ctx* c, moexb_layer* L, const void* X, int x_dt
     const float* xin;
     int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
-    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, 2 | 4, stream, false, false, shared_t0, shared_t1);
+    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, 2 | 4, stream, pre_normed != 0, false, shared_t0, shared_t1);
+}
+
+int moexb_ep_residual_norm(moexb_ctx* c, moexb_layer* next, const float* x, const float* total, float* out, int T, void* stream) {
+    REQUIRE(c && x && total && out, "ep_residual_norm: null pointer");
+    REQUIRE(T > 0 && T <= c->max_tokens, "ep_residual_norm: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
+    const bool f16 = next && next->layout == MOEXB_LAYOUT_TILED && next->fmt != FMT_ZP;
+    float* xn = next ? c->xn : nullptr;
+    PROF(c, MOEXB_PROF_COMBINE, stream);
+    if (f16) reduce_residual_norm_k<true><<<T, 256, 0, S(stream)>>>(total, nullptr, x, out, 1, xn, c->xs, 1e-6f, 0, 0, nullptr, 0, 0);
+    else reduce_residual_norm_k<false><<<T, 256, 0, S(stream)>>>(total, nullptr, x, out, 1, xn, c->xs, 1e-6f, 0, 0, nullptr, 0, 0);
+    LAUNCHED("ep_residual_norm");
+    return MOEXB_OK;
 }
 
 // ---- stack of layers as one CUDA graph ----------------------------------------------------------------------------------

@@ -398,9 +398,16 @@ __global__ void __launch_bounds__(256) rmsnorm_split_k(const float* __restrict__
 template <bool F16>
 __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __restrict__ ypair, const float* __restrict__ extra, const float* __restrict__ x,
                                                               float* __restrict__ out, int K, float* __restrict__ xn_next,
-                                                              uint16_t* __restrict__ xs_next, float eps, int ex0, int ex1) {
+                                                              uint16_t* __restrict__ xs_next, float eps, int ex0, int ex1,
+                                                              const int* __restrict__ idx, int e_lo, int e_hi) {
     const size_t t = blockIdx.x;
     if ((int)t < ex0 || (int)t >= ex1) extra = nullptr;  // extra rows exist only for tokens [ex0, ex1)
+    // idx given: only the ranks whose expert lies in [e_lo, e_hi) were computed here (expert parallelism); skip the others
+    unsigned have = 0xffffffffu;
+    if (idx) {
+        have = 0;
+        for (int r = 0; r < K; r++) { const int e = idx[t * K + r]; if (e >= e_lo && e < e_hi) have |= 1u << r; }
+    }
     float v[8];
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -410,10 +417,10 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
             float4 y[4];
 #pragma unroll
             for (int u = 0; u < 4; u++)
-                if (rb + u < K) y[u] = *reinterpret_cast<const float4*>(ypair + (t * K + rb + u) * EH + k0);
+                if (rb + u < K && (have >> (rb + u) & 1)) y[u] = *reinterpret_cast<const float4*>(ypair + (t * K + rb + u) * EH + k0);
 #pragma unroll
             for (int u = 0; u < 4; u++)
-                if (rb + u < K) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
+                if (rb + u < K && (have >> (rb + u) & 1)) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
         }
         if (extra) {
             const float4 y = *reinterpret_cast<const float4*>(extra + t * EH + k0);

@@ -63,11 +63,16 @@ class EPStack:
                 self._step()
 
     def _step(self):
-        self.x.copy_(self.x_in)
-        for L in self.layers:
-            L.forward_ep(self.x, self.T, self.K, self.part, self.sh0, self.sh1)
+        from .api import ep_residual_norm
+        n = len(self.layers)
+        for l, L in enumerate(self.layers):
+            # layer 0 reads the step's input (f32 or bf16) and normalises it; later layers find their normalised input in
+            # the context, left there by the residual kernel of the layer before
+            L.forward_ep(self.x_in if l == 0 else self.x, self.T, self.K, self.part, self.sh0, self.sh1, pre_normed=l > 0)
             dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group)
-            self.x.add_(self.part)
+            if l == 0:
+                self.x.copy_(self.x_in)
+            ep_residual_norm(self.ctx, self.layers[l + 1] if l + 1 < n else None, self.x, self.part, self.x, self.T)
 
     def run(self, X):
         self.x_in.copy_(X, non_blocking=True)

@@ -368,6 +368,16 @@ def test_expert_parallel_entry_point(ctx, layer_sym):
     assert ctx.status() == 0
     moe, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, o.rmsnorm(X), 8)
     check_ffn(X + total, X + moe, m.FMT_SYM_F16, "expert-parallel block")
+    # the residual kernel that follows the all-reduce, and a second block fed from the normalised input it leaves behind
+    L2 = m.Layer(ctx, m.FMT_SYM_F16, 256, first_local=0, n_local=256)
+    L2.fill_synth(0, 0); L2.set_router(W)
+    x1 = m.ep_residual_norm(ctx, L2, dev(X), dev(total), torch.empty(T, 2048, device=DEV), T)
+    check_ffn(x1.cpu().numpy(), X + moe, m.FMT_SYM_F16, "residual after the exchange")
+    part2 = L2.forward_ep(x1, T, 8, torch.empty(T, 2048, device=DEV), 0, T, pre_normed=True).cpu().numpy()
+    x1h = x1.cpu().numpy()
+    moe2, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, o.rmsnorm(x1h), 8)
+    check_ffn(x1h + part2, x1h + moe2, m.FMT_SYM_F16, "second block from the handed-over norm")
+    L2.close()
 
 
 def test_residual_block_chain(ctx):
