@@ -175,6 +175,9 @@ int moexb_ctx_destroy(moexb_ctx* ctx);
  * 256-byte row pieces (default), 1 = the fp32 SIMT kernels (the restatement of the reference's pairs_forward /
  * experts_forward, kept for cross-checks). TILED layers always use the tiled streaming kernels. */
 int moexb_ctx_set_path(moexb_ctx* ctx, int path);
+/* Batches of at least this many tokens run the experts on the tcgen05 grouped GEMM (TILED layers, symmetric formats);
+ * smaller ones on the streaming kernels. Default 256. */
+int moexb_ctx_set_prefill_min_tokens(moexb_ctx* ctx, int tokens);
 /* Waits for the device and reads the error word of the streaming kernels: 0 = none; 1 / 2 = a consumer warp / the producer
  * warp gave up waiting on a pipeline barrier (every device-side wait is bounded). The word is cleared. */
 int moexb_ctx_status(moexb_ctx* ctx, int* status);

@@ -149,6 +149,9 @@ class Context:
         """0 = streaming tensor-core kernels (default), 1 = fp32 SIMT kernels."""
         check(lib().moexb_ctx_set_path(self.h, path))
 
+    def set_prefill_min_tokens(self, tokens):
+        check(lib().moexb_ctx_set_prefill_min_tokens(self.h, tokens))
+
     def status(self):
         """Synchronises and returns the streaming kernels' error word (0 = fine)."""
         st = C.c_int(0)

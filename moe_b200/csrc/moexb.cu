@@ -6,6 +6,7 @@
 #include "formats.cuh"
 #include "stream.cuh"
 #include "tiled.cuh"
+#include "prefill.cuh"
 
 #include <cmath>
 #include <cstdarg>
@@ -94,6 +95,7 @@ struct moexb_ctx {
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
+    int prefill_min_tokens = 256;                       // batches from this size on use the tcgen05 grouped GEMM
     uint8_t* staging = nullptr;                         // reference-layout blobs on their way into a tiled image
     std::vector<void*> owned;
     // optional per-kernel timing of the layer-level calls
@@ -586,6 +588,53 @@ static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* 
     });
 }
 
+// ---- prefill: grouped GEMM on tcgen05 ----------------------------------------------------------------------------------------
+
+template <int FMT, bool DOWN>
+static int prefill_launch_one(moexb_ctx* c, const PrefillArgs& a, void* stream) {
+    constexpr int SMEM = pf_smem_bytes<FMT, DOWN>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(prefill_k<FMT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "prefill kernel shared memory: %s", cudaGetErrorString(attr_err));
+    PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
+    prefill_k<FMT, DOWN><<<c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
+    LAUNCHED(DOWN ? "prefill_down" : "prefill_gate_up");
+    return MOEXB_OK;
+}
+
+// Experts of a large batch on the tensor-core grouped GEMM: items/nitems = the grouped work list (tiled blobs), xf = the
+// activations as fp32 [T][H]; parts = 1 when xf holds exact bf16 values, else 2.
+static int prefill_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, const float* xf, int T, int parts, float* ypair, void* stream) {
+    {
+        PROF(c, MOEXB_PROF_OTHER, stream);
+        const size_t n = (size_t)T * EH;
+        split8_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(xf, c->xs, EH, parts, n);
+        LAUNCHED("split8_rows");
+    }
+    auto run = [&]<int FMT>() {
+        {
+            PROF(c, MOEXB_PROF_GROUP, stream);
+            plan_subitems_k<<<1, 1024, 0, S(stream)>>>(c->items, c->nitems, 0, c->subs, c->nsub, PF_NMAX / parts);
+            LAUNCHED("plan_subitems");
+        }
+        PrefillArgs a{c->subs, c->nsub, pairs, c->xs, c->act_split, nullptr, ypair, c->err, parts};
+        int rc = prefill_launch_one<FMT, false>(c, a, stream);
+        if (rc != MOEXB_OK) return rc;
+        if (parts != 2) {
+            PROF(c, MOEXB_PROF_GROUP, stream);
+            plan_subitems_k<<<1, 1024, 0, S(stream)>>>(c->items, c->nitems, 0, c->subs, c->nsub, PF_NMAX / 2);
+            LAUNCHED("plan_subitems");
+        }
+        PrefillArgs d = a;
+        d.xs = c->act_split; d.parts = 2;
+        return prefill_launch_one<FMT, true>(c, d, stream);
+    };
+    if (fmt == FMT_SYM_F16) return run.template operator()<FMT_SYM_F16>();
+    if (fmt == FMT_SYM_F32) return run.template operator()<FMT_SYM_F32>();
+    return fail(MOEXB_ERR_UNSUPPORTED, "prefill kernels: format %d", fmt);
+}
+
 // f16: the consumer is the tiled kernel of a symmetric format (fp16 operands); otherwise bf16
 static int split_launch(moexb_ctx* c, const float* x, int rows, bool f16, void* stream) {
     PROF(c, MOEXB_PROF_OTHER, stream);
@@ -606,9 +655,15 @@ extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_it
     if (n_items == 0) return MOEXB_OK;
     int rc = split_launch(c, X, T, false, stream);
     if (rc != MOEXB_OK) return rc;
-    plan_subitems_k<<<1, 1024, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub);
+    plan_subitems_k<<<1, 1024, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub, ST_MAXP);
     LAUNCHED("plan_subitems");
     return stream_experts(c, fmt, pairs, act, ypair, stream);
+}
+
+extern "C" int moexb_ctx_set_prefill_min_tokens(moexb_ctx* c, int tokens) {
+    REQUIRE(c && tokens >= 1, "ctx_set_prefill_min_tokens: bad argument");
+    c->prefill_min_tokens = tokens;
+    return MOEXB_OK;
 }
 
 extern "C" int moexb_ctx_set_path(moexb_ctx* c, int path) {
@@ -649,7 +704,7 @@ static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int
 // rmsnorm(xin) and its bf16 split (left there by the previous layer of a stack); next_norm: leave rmsnorm(out) and its
 // split in the context for the next layer.
 static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int K, float* out, int* idx_out, float* w_out, int flags,
-                      void* stream, bool pre_normed, bool next_norm, int sh0 = 0, int sh1 = -1) {
+                      void* stream, bool pre_normed, bool next_norm, int sh0 = 0, int sh1 = -1, bool x_bf16 = false) {
     if (sh1 < 0) sh1 = T;
     const bool shared = !(flags & 1) && sh1 > sh0, block = flags & 2, partial = flags & 4;
     const bool all_local = L->n_local == L->n_routed;
@@ -657,7 +712,9 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     cudaStream_t st = S(stream);
     const bool tiled = L->layout == MOEXB_LAYOUT_TILED;
     const bool streaming = tiled || c->path == 0;
-    const bool f16 = tiled && L->fmt != FMT_ZP;  // element type of the split activations the expert kernels read
+    // large batches of symmetric-format experts go to the tcgen05 grouped GEMM (bf16 operands); the rest to the streaming kernels
+    const bool prefill = tiled && L->fmt != FMT_ZP && T >= c->prefill_min_tokens;
+    const bool f16 = tiled && L->fmt != FMT_ZP && !prefill;  // element type of the split activations the streaming kernels read
     const float* xf = xin;  // what the router and the experts see
     if (block) {
         xf = c->xn;
@@ -667,7 +724,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             else rmsnorm_split_k<false><<<T, 256, 0, st>>>(xin, c->xn, c->xs, 1e-6f);
             LAUNCHED("rmsnorm_split");
         }
-    } else if (streaming) {
+    } else if (streaming && !prefill) {
         const int rc = split_launch(c, xf, T, f16, stream);
         if (rc != MOEXB_OK) return rc;
     }
@@ -702,7 +759,8 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             // reduction skips them by expert id
             if (!all_local && !streaming) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
         }
-        rc = tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
+        rc = prefill ? prefill_experts(c, L->fmt, c->pairs, xf, T, (x_bf16 && !block) ? 1 : 2, c->ypair, stream)
+           : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
            : streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
                        : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;
@@ -743,7 +801,7 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     const float* xin;
     int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
-    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, flags, stream, false, false);
+    return layer_impl(c, L, xin, T, K, out, idx_out, w_out, flags, stream, false, false, 0, -1, x_dtype == MOEXB_BF16);
 }
 
 int moexb_layer_forward_ep(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype, int T, int K, float* out, int* idx_out,

@@ -454,20 +454,20 @@ __device__ __forceinline__ int block_scan_1024(int v, int& total) {
     return inc - v + (w ? before : 0);
 }
 
-// Sub-items of at most ST_MAXP pairs from the items of a work list. One block of 1024 threads, one item per thread
+// Sub-items of at most maxp pairs from the items of a work list. One block of 1024 threads, one item per thread
 // and pass.
 __global__ void __launch_bounds__(1024) plan_subitems_k(const moexb_pair_item* __restrict__ items, const int* __restrict__ nitems_dev, int nitems_host,
-                                                        moexb_pair_item* __restrict__ subs, int* __restrict__ nsub) {
+                                                        moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int maxp) {
     const int ni = nitems_dev ? *nitems_dev : nitems_host;
     int done = 0;
     for (int base = 0; base < ni; base += 1024) {
         const int i = base + threadIdx.x;
         moexb_pair_item it = {nullptr, 0, 0};
         if (i < ni) it = items[i];
-        const int mine = (it.count + ST_MAXP - 1) / ST_MAXP;
+        const int mine = (it.count + maxp - 1) / maxp;
         int total;
         const int at = done + block_scan_1024(mine, total);
-        for (int j = 0; j < mine; j++) subs[at + j] = {it.slot, it.start + j * ST_MAXP, min(ST_MAXP, it.count - j * ST_MAXP)};
+        for (int j = 0; j < mine; j++) subs[at + j] = {it.slot, it.start + j * maxp, min(maxp, it.count - j * maxp)};
         done += total;
     }
     if (threadIdx.x == 0) *nsub = done;

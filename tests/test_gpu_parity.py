@@ -429,3 +429,32 @@ def test_layer_forward_rejects_oversize_requests(ctx, layer_sym):
         L.forward(X, 65, 8)
     with pytest.raises(m.MoexbError, match="top_k"):
         L.forward(X, 4, 9)
+
+
+@pytest.mark.parametrize("bf16_input", [True, False])
+def test_prefill_grouped_gemm_tcgen05(bf16_input):
+    """A batch large enough for the tcgen05 grouped GEMM (300 tokens, 64 experts: ragged tiles of 1..128 columns, the
+    shared expert spanning several tiles) against the oracle; bf16 inputs take one activation column per token, fp32
+    inputs two (hi + lo)."""
+    rng = np.random.default_rng(77)
+    E, T = 64, 300
+    c = m.Context(0, max_tokens=T, max_experts=E, top_k=8)
+    L = m.Layer(c, m.FMT_SYM_F16, E)
+    L.fill_synth(3, 0)
+    W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
+    L.set_router(W)
+    host = [m.synth_expert_host(m.FMT_SYM_F16, 3, 0, e) for e in range(E + 1)]
+    X = torch.from_numpy(rng.standard_normal((T, 2048)).astype(np.float32))
+    if bf16_input:
+        X = X.to(torch.bfloat16)
+    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+    out = L.forward(X.to(DEV), T, 8, idx=idx)
+    assert c.status() == 0
+    ref, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X.float().numpy(), 8)
+    assert np.array_equal(idx.cpu().numpy(), ri)
+    check_ffn(out.cpu().numpy(), ref, m.FMT_SYM_F16, f"prefill bf16_input={bf16_input}")
+    # the streaming kernels on the same batch agree (cross-check of the two tensor-core paths)
+    c.set_prefill_min_tokens(1 << 20)
+    out2 = L.forward(X.to(DEV), T, 8)
+    check_ffn(out2.cpu().numpy(), ref, m.FMT_SYM_F16, "streaming kernels on the same batch")
+    L.close(); c.close()
