@@ -631,7 +631,6 @@ static int prefill_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, const
         return prefill_launch_one<FMT, true>(c, d, stream);
     };
     if (fmt == FMT_SYM_F16) return run.template operator()<FMT_SYM_F16>();
-    if (fmt == FMT_SYM_F32) return run.template operator()<FMT_SYM_F32>();
     return fail(MOEXB_ERR_UNSUPPORTED, "prefill kernels: format %d", fmt);
 }
 
@@ -713,7 +712,7 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     const bool tiled = L->layout == MOEXB_LAYOUT_TILED;
     const bool streaming = tiled || c->path == 0;
     // large batches of symmetric-format experts go to the tcgen05 grouped GEMM (bf16 operands); the rest to the streaming kernels
-    const bool prefill = tiled && L->fmt != FMT_ZP && T >= c->prefill_min_tokens;
+    const bool prefill = tiled && L->fmt == FMT_SYM_F16 && T >= c->prefill_min_tokens;
     const bool f16 = tiled && L->fmt != FMT_ZP && !prefill;  // element type of the split activations the streaming kernels read
     const float* xf = xin;  // what the router and the experts see
     if (block) {
