@@ -10,7 +10,7 @@ Workloads (shapes of the reference model: hidden 2048, 256 routed + 1 shared exp
   decode1      1 token (f32) through 40 layers of i4_gs64 experts
   decode1_q4k  1 token (f32) through 40 layers of GGUF Q4_K experts (zero-point blobs)
   mtp4         4 tokens (f32) through 40 layers - speculative-verify batch
-  prefill2048  2048 tokens (bf16) through 1 layer
+  prefill2048  2048 tokens (bf16) through 1 layer (the plain layer, no norm or residual around it)
 Weights are seeded synthetic tensors generated on the device (17 GB for 40 layers, larger than L2, so every step streams
 them from HBM); inputs are seeded normal tokens.
 
@@ -211,7 +211,7 @@ def main():
     torch.cuda.synchronize()
     x_torch_dtype = torch.bfloat16 if xdt == "bf16" else torch.float32
     if world == 1:
-        stack = m.Stack(ctx, layers, T, K, m.BF16 if xdt == "bf16" else m.F32)
+        stack = m.Stack(ctx, layers, T, K, m.BF16 if xdt == "bf16" else m.F32, residual=NL > 1)
     else:
         # expert parallel: every rank sees the same tokens; the step is captured with its all-reduces in one graph
         eps = ep.EPStack(ctx, layers, T, K, x_torch_dtype)
@@ -281,7 +281,7 @@ def main():
         x = Xd[r % 8]
         for l, L in enumerate(layers):
             if world == 1:
-                x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2)
+                x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2 if NL > 1 else 0)
             else:
                 part = L.forward_ep(x, T, K, bufs[l & 1], sh0, sh1, idx=idx[l])
                 dist.all_reduce(part)

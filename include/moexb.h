@@ -233,8 +233,9 @@ typedef struct moexb_stack moexb_stack;
 /* Chains n_layers residual blocks x_{l+1} = x_l + moe_l(rmsnorm(x_l)) (unit norm weight, eps 1e-6; the structure of
  * the reference's decoder block around its MoE, moex.cu:1082, 1092) for a fixed token count T and captures the whole
  * sequence of launches in one CUDA graph, as the reference captures its per-step graph (moex.cu:1165-1181).
- * Input [T][H] of x_dtype, output x_{n_layers} [T][H] f32. The layers must outlive the stack. */
-int moexb_stack_create(moexb_ctx* ctx, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype,
+ * Input [T][H] of x_dtype, output x_{n_layers} [T][H] f32. residual = 0 chains the plain layers instead,
+ * x_{l+1} = moe_l(x_l) (one layer: exactly moexb_layer_forward). The layers must outlive the stack. */
+int moexb_stack_create(moexb_ctx* ctx, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, int residual,
                        moexb_stack** out);
 int moexb_stack_destroy(moexb_stack* stack);
 /* Device buffers: copies X in, replays the graph, copies the result to out; all on `stream`, no synchronisation. */

@@ -71,7 +71,7 @@ SIGNATURES = {
     "moexb_layer_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
     "moexb_layer_forward_ep": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moexb_ep_residual_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),
-    "moexb_stack_create": (_i, [_vp, C.POINTER(_vp), _i, _i, _i, _i, C.POINTER(_vp)]),
+    "moexb_stack_create": (_i, [_vp, C.POINTER(_vp), _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "moexb_stack_destroy": (_i, [_vp]),
     "moexb_stack_run": (_i, [_vp, _vp, _vp, _vp]),
     "moexb_stack_run_host": (_i, [_vp, _vp, _vp, _vp]),

@@ -246,10 +246,10 @@ def ep_residual_norm(ctx, next_layer, x, total, out, T):
 class Stack:
     """moexb_stack: n layers chained as residual blocks for a fixed token count, replayed as one CUDA graph."""
 
-    def __init__(self, ctx, layers, T, K=8, x_dtype=F32):
+    def __init__(self, ctx, layers, T, K=8, x_dtype=F32, residual=True):
         arr = (C.c_void_p * len(layers))(*[l.h for l in layers])
         h = C.c_void_p()
-        check(lib().moexb_stack_create(ctx.h, arr, len(layers), T, K, x_dtype, C.byref(h)))
+        check(lib().moexb_stack_create(ctx.h, arr, len(layers), T, K, x_dtype, int(residual), C.byref(h)))
         self.h, self.T, self.layers, self.x_dtype = h, T, layers, x_dtype
 
     @property

@@ -852,7 +852,7 @@ int moexb_stack_destroy(moexb_stack* s) {
     return MOEXB_OK;
 }
 
-int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, moexb_stack** out) {
+int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, int residual, moexb_stack** out) {
     REQUIRE(c && layers && out, "stack_create: null pointer");
     REQUIRE(n_layers > 0 && T > 0 && T <= c->max_tokens && K > 0 && K <= c->top_k, "stack_create: n_layers=%d T=%d K=%d", n_layers, T, K);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "stack_create: x_dtype=%d", x_dtype);
@@ -878,7 +878,8 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     int rc = layer_input(c, s->x_in, x_dtype, T, s->cap, &xin);
     for (int l = 0; l < n_layers && rc == MOEXB_OK; l++) {
         // layer l leaves rmsnorm(x_{l+1}) and its split in the context, so layer l+1 starts at its router
-        rc = layer_impl(c, layers[l], xin, T, K, s->buf[l & 1], nullptr, nullptr, 2, s->cap, l > 0, l + 1 < n_layers);
+        if (residual) rc = layer_impl(c, layers[l], xin, T, K, s->buf[l & 1], nullptr, nullptr, 2, s->cap, l > 0, l + 1 < n_layers);
+        else rc = layer_impl(c, layers[l], xin, T, K, s->buf[l & 1], nullptr, nullptr, 0, s->cap, false, false, 0, -1, l == 0 && x_dtype == MOEXB_BF16);
         xin = s->buf[l & 1];
     }
     e = cudaStreamEndCapture(s->cap, &s->graph);
