@@ -187,6 +187,7 @@ def main():
     ap.add_argument("--workload", default="serve64", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--pairs-per-pass", type=int, default=8, choices=[4, 8], help="sub-item width of the streaming kernels")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -208,6 +209,7 @@ def main():
     T, NL, fmtname, xdt = WORKLOADS[args.workload]
     fmt = m.FMT_ZP if fmtname == "zp" else m.FMT_SYM_F16
     ctx = m.Context(local, max_tokens=T, max_experts=E, top_k=K)
+    ctx.set_pairs_per_pass(args.pairs_per_pass)
     from moe_b200 import ep
     first, count = ep.expert_range(E, rank, world)
     layers = []
@@ -301,8 +303,9 @@ def main():
     def local(ix):  # the routed experts this rank holds
         return ix[(ix >= first) & (ix < first + count)]
     distinct = float(np.mean([len(torch.unique(local(idx[l]))) for l in range(NL)])) + 1  # + the shared expert
-    # passes over expert weights: an expert with n tokens is streamed ceil(n / 4) times (4 pairs per sub-item)
-    passes = float(np.mean([int(torch.ceil(torch.bincount(local(idx[l].flatten()).long(), minlength=E) / 4).sum()) for l in range(NL)])) + (sh1 - sh0 + 3) // 4
+    # passes over expert weights: an expert with n tokens is streamed ceil(n / maxp) times (maxp pairs per sub-item)
+    maxp = 128 if T >= 256 else args.pairs_per_pass if (T >= 8 and fmt != m.FMT_ZP) else 4
+    passes = float(np.mean([int(torch.ceil(torch.bincount(local(idx[l].flatten()).long(), minlength=E) / maxp).sum()) for l in range(NL)])) + (sh1 - sh0 + maxp - 1) // maxp
     eb = m.expert_bytes(fmt)
     qb_gu, qb_dn = 2 * EI * EH // 2, EH * EI // 2
     sc_total = eb - m.Q_BYTES

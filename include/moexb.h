@@ -178,6 +178,10 @@ int moexb_ctx_set_path(moexb_ctx* ctx, int path);
 /* Batches of at least this many tokens run the experts on the tcgen05 grouped GEMM (TILED layers, symmetric formats);
  * smaller ones on the streaming kernels. Default 256. */
 int moexb_ctx_set_prefill_min_tokens(moexb_ctx* ctx, int tokens);
+/* Pairs of one expert that a pass of the tiled streaming kernels takes (batches of 8 to prefill_min_tokens - 1 tokens,
+ * symmetric formats): 8 (default; an expert with 5-8 pairs is unpacked once) or 4. Smaller batches and zero-point blobs
+ * always take 4. */
+int moexb_ctx_set_pairs_per_pass(moexb_ctx* ctx, int pairs);
 /* Waits for the device and reads the error word of the streaming kernels: 0 = none; 1 / 2 = a consumer warp / the producer
  * warp gave up waiting on a pipeline barrier (every device-side wait is bounded). The word is cleared. */
 int moexb_ctx_status(moexb_ctx* ctx, int* status);

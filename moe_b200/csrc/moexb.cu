@@ -95,6 +95,7 @@ struct moexb_ctx {
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
+    int pairs_per_pass = 8;                             // sub-item width of the tiled streaming kernels from 8 tokens on
     int prefill_min_tokens = 256;                       // batches from this size on use the tcgen05 grouped GEMM
     uint8_t* staging = nullptr;                         // reference-layout blobs on their way into a tiled image
     std::vector<void*> owned;
@@ -390,7 +391,7 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
     A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
-    A(&c->nsub, 1); A(&c->err, 1); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
+    A(&c->nsub, 2); A(&c->err, 1); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
     if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
     if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
@@ -555,15 +556,16 @@ static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float*
     });
 }
 
-template <int FMT, bool DOWN, int NW, int D>
+template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2>
 static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
-    constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D>();
+    constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D, NB>();
+    static_assert(SMEM * CPS <= 227 * 1024, "shared memory of the resident CTAs");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "tiled stream kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
-    stream_tiled_k<FMT, DOWN, NW, D><<<2 * c->sms, NW * 32, SMEM, S(stream)>>>(a);
+    stream_tiled_k<FMT, DOWN, NW, D, NB, CPS><<<CPS * c->sms, NW * 32, SMEM, S(stream)>>>(a);
     LAUNCHED(DOWN ? "stream_tiled_down" : "stream_tiled_gate_up");
     return MOEXB_OK;
 }
@@ -571,10 +573,18 @@ static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
 // Two shapes of the same kernel, both two CTAs per SM: a few tokens leave only a handful of row tiles per SM, so CTAs of
 // 4 warps with 4 slices in flight each spread them over every SM; from 8 tokens on there is work for 16 warps per SM
 // (CTAs of 8 warps, 2 slices in flight each - the same bytes in flight, twice the issue slots in use).
+// From 8 tokens on the symmetric formats also take sub-items of up to 8 pairs (two column blocks; tiled_maxp below): the
+// gate/up columns of 8 pairs are 66 KB, so that kernel runs as one CTA of 16 warps per SM.
 template <int FMT, bool DOWN>
 static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* stream) {
-    return T >= 8 ? tiled_launch_cfg<FMT, DOWN, 8, 2>(c, a, stream) : tiled_launch_cfg<FMT, DOWN, 4, 4>(c, a, stream);
+    if (T < 8) return tiled_launch_cfg<FMT, DOWN, 4, 4>(c, a, stream);
+    if (FMT == FMT_ZP || c->pairs_per_pass == 4) return tiled_launch_cfg<FMT, DOWN, 8, 2>(c, a, stream);
+    if constexpr (FMT == FMT_ZP) return MOEXB_OK;
+    else if constexpr (DOWN) return tiled_launch_cfg<FMT, DOWN, 8, 2, 2, 2>(c, a, stream);
+    else return tiled_launch_cfg<FMT, DOWN, 16, 2, 2, 1>(c, a, stream);
 }
+// Pairs per sub-item that tiled_launch_one's kernels take.
+static int tiled_maxp(const moexb_ctx* c, int fmt, int T) { return (T >= 8 && fmt != FMT_ZP) ? c->pairs_per_pass : 4; }
 
 // The same on blobs in the tiled layout (sub-item slots point into a tiled layer image).
 static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, int T, void* stream) {
@@ -657,6 +667,12 @@ extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_it
     plan_subitems_k<<<1, 1024, 0, S(stream)>>>(items, nullptr, n_items, c->subs, c->nsub, ST_MAXP);
     LAUNCHED("plan_subitems");
     return stream_experts(c, fmt, pairs, act, ypair, stream);
+}
+
+extern "C" int moexb_ctx_set_pairs_per_pass(moexb_ctx* c, int pairs) {
+    REQUIRE(c && (pairs == 4 || pairs == 8), "ctx_set_pairs_per_pass: 4 or 8");
+    c->pairs_per_pass = pairs;
+    return MOEXB_OK;
 }
 
 extern "C" int moexb_ctx_set_prefill_min_tokens(moexb_ctx* c, int tokens) {
@@ -751,8 +767,12 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     } else {
         {
             PROF(c, MOEXB_PROF_GROUP, stream);
-            group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                                                 shared ? c->logits + E : nullptr, ld, sh0, sh1);
+            if (tiled && !prefill && tiled_maxp(c, L->fmt, T) == 8)
+                group_plan_k<8><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
+                                                              shared ? c->logits + E : nullptr, ld, sh0, sh1);
+            else
+                group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
+                                                                     shared ? c->logits + E : nullptr, ld, sh0, sh1);
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
             // reduction skips them by expert id

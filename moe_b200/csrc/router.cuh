@@ -210,13 +210,14 @@ __global__ void __launch_bounds__(WARPS * 32) group_scatter_k(const int* __restr
     }
 }
 
-// Exclusive prefix sums of three per-thread values over a block of 256 threads; totals returned through tot[].
-__device__ __forceinline__ void block_scan3_256(int (&v)[3], int (&tot)[3]) {
-    __shared__ int ws[3][8];
+// Exclusive prefix sums of N per-thread values over a block of 256 threads; totals returned through tot[].
+template <int N>
+__device__ __forceinline__ void block_scan_256(int (&v)[N], int (&tot)[N]) {
+    __shared__ int ws[N][8];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    int inc[3];
+    int inc[N];
 #pragma unroll
-    for (int i = 0; i < 3; i++) {
+    for (int i = 0; i < N; i++) {
         inc[i] = v[i];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, inc[i], o); if (lane >= o) inc[i] += u; }
@@ -224,7 +225,7 @@ __device__ __forceinline__ void block_scan3_256(int (&v)[3], int (&tot)[3]) {
     }
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 3; i++) {
+    for (int i = 0; i < N; i++) {
         int before = 0, all = 0;
 #pragma unroll
         for (int j = 0; j < 8; j++) { const int x = ws[i][j]; all += x; if (j < w) before += x; }
@@ -236,15 +237,20 @@ __device__ __forceinline__ void block_scan3_256(int (&v)[3], int (&tot)[3]) {
 // Grouping and planning in one launch (the work of group_count_k + group_scatter_k, plus the sub-items of at most MAXP
 // pairs that the streaming kernels walk). Every block builds the per-expert histogram of the T*K pairs in shared memory
 // and scans it; then one warp per expert writes that expert's item, its sub-items and its pairs in token order.
+// Sub-items of more than MAXP / 2 pairs ("wide") come first in subs[], the others after them, and nsub[1] receives the
+// number of wide ones: a pass over a wide sub-item costs the streaming kernels more, and with the two kinds apart a kernel
+// can split the work evenly from nsub[0] and nsub[1] alone. (An expert's sub-items are all wide except possibly its last.)
 // Optional shared expert as in group_scatter_k, for the tokens [sh0, sh1). E <= 1024; 256 threads; grid ceil(E / 8).
+__host__ __device__ constexpr int plan_wide(int c, int maxp) { return c / maxp + (c % maxp > maxp / 2); }
+__host__ __device__ constexpr int plan_narrow(int c, int maxp) { return c % maxp > 0 && c % maxp <= maxp / 2; }
 template <int MAXP>
 __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
                                                     const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
                                                     moexb_pair* __restrict__ pairs, int* __restrict__ nitems, moexb_pair_item* __restrict__ subs,
                                                     int* __restrict__ nsub, const float* __restrict__ gate_logits, int gl_stride,
                                                     int sh0, int sh1) {
-    __shared__ int cnt[1024], start[1024], item_of[1024], sub_at[1024];
-    __shared__ int s_tot[3];
+    __shared__ int cnt[1024], start[1024], item_of[1024], wide_at[1024], narrow_at[1024];
+    __shared__ int s_tot[4];
     const int n = T * K, tid = threadIdx.x, lane = tid & 31;
     for (int e = tid; e < E; e += 256) cnt[e] = 0;
     __syncthreads();
@@ -252,31 +258,35 @@ __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx,
     __syncthreads();
     {
         const int per = (E + 255) / 256, e0 = tid * per;
-        int c[4], v[3] = {0, 0, 0}, tot[3];
+        int c[4], v[4] = {0, 0, 0, 0}, tot[4];
         for (int i = 0; i < per; i++) {
             const int e = e0 + i;
             c[i] = (e < E && slot_table[e]) ? cnt[e] : 0;
-            v[0] += c[i]; v[1] += c[i] != 0; v[2] += (c[i] + MAXP - 1) / MAXP;
+            v[0] += c[i]; v[1] += c[i] != 0; v[2] += plan_wide(c[i], MAXP); v[3] += plan_narrow(c[i], MAXP);
         }
-        block_scan3_256(v, tot);
+        block_scan_256<4>(v, tot);
         for (int i = 0; i < per; i++) {
             const int e = e0 + i;
             if (e < E) {
-                start[e] = v[0]; item_of[e] = c[i] ? v[1] : -1; sub_at[e] = v[2];
+                start[e] = v[0]; item_of[e] = c[i] ? v[1] : -1; wide_at[e] = v[2]; narrow_at[e] = v[3];
                 cnt[e] = c[i];
             }
-            v[0] += c[i]; v[1] += c[i] != 0; v[2] += (c[i] + MAXP - 1) / MAXP;
+            v[0] += c[i]; v[1] += c[i] != 0; v[2] += plan_wide(c[i], MAXP); v[3] += plan_narrow(c[i], MAXP);
         }
-        if (tid == 0) { s_tot[0] = tot[0]; s_tot[1] = tot[1]; s_tot[2] = tot[2]; }
+        if (tid == 0) { s_tot[0] = tot[0]; s_tot[1] = tot[1]; s_tot[2] = tot[2]; s_tot[3] = tot[3]; }
     }
     __syncthreads();
+    const bool with_shared = gate_logits && slot_table[E] && sh1 > sh0;
+    const int Ts = with_shared ? sh1 - sh0 : 0;
+    const int nw = s_tot[2] + plan_wide(Ts, MAXP);   // all wide sub-items: the routed experts', then the shared expert's
     const int e = blockIdx.x * 8 + (tid >> 5);
     if (e < E && item_of[e] >= 0) {
         const uint8_t* slot = slot_table[e];
         int at = start[e];
-        const int c = cnt[e];
+        const int c = cnt[e], cw = plan_wide(c, MAXP);
         if (lane == 0) items[item_of[e]] = {slot, at, c};
-        for (int j = lane; j * MAXP < c; j += 32) subs[sub_at[e] + j] = {slot, at + j * MAXP, min(MAXP, c - j * MAXP)};
+        for (int j = lane; j * MAXP < c; j += 32)
+            subs[j < cw ? wide_at[e] + j : nw + narrow_at[e]] = {slot, at + j * MAXP, min(MAXP, c - j * MAXP)};
         for (int p0 = 0; p0 < n; p0 += 32) {
             const int p = p0 + lane;
             const bool hit = p < n && __ldg(idx + p) == e;
@@ -286,15 +296,15 @@ __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx,
         }
     }
     if (blockIdx.x == 0) {
-        const int np = s_tot[0], ni = s_tot[1], ns = s_tot[2];
-        if (gate_logits && slot_table[E] && sh1 > sh0) {
+        const int np = s_tot[0], ni = s_tot[1], ns = nw + s_tot[3];  // ns: where the shared expert's narrow sub-item goes
+        if (with_shared) {
             // the shared expert for tokens [sh0, sh1) (all of them on one GPU; a slice per rank under expert parallelism)
             const uint8_t* slot = slot_table[E];
-            const int Ts = sh1 - sh0;
-            if (tid == 0) { items[ni] = {slot, np, Ts}; *nitems = ni + 1; *nsub = ns + (Ts + MAXP - 1) / MAXP; }
+            const int cw = plan_wide(Ts, MAXP);
+            if (tid == 0) { items[ni] = {slot, np, Ts}; *nitems = ni + 1; nsub[0] = ns + plan_narrow(Ts, MAXP); nsub[1] = nw; }
             for (int t = tid; t < Ts; t += 256) pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gate_logits[(size_t)(sh0 + t) * gl_stride]))};
-            for (int j = tid; j * MAXP < Ts; j += 256) subs[ns + j] = {slot, np + j * MAXP, min(MAXP, Ts - j * MAXP)};
-        } else if (tid == 0) { *nitems = ni; *nsub = ns; }
+            for (int j = tid; j * MAXP < Ts; j += 256) subs[j < cw ? s_tot[2] + j : ns] = {slot, np + j * MAXP, min(MAXP, Ts - j * MAXP)};
+        } else if (tid == 0) { *nitems = ni; nsub[0] = ns; nsub[1] = nw; }
     }
 }
 

@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) tile_expert_k(const uint8_t* __restrict__
 }
 
 struct TiledArgs {
-    const moexb_pair_item* subs;  // sub-items: at most ST_MAXP pairs each, slot = tiled blob
+    const moexb_pair_item* subs;  // sub-items: at most 4 * NB pairs each, slot = tiled blob
     const int* nsub;
     const moexb_pair* pairs;
     const uint16_t* xs;           // gate/up: activations [token][2][H] (hi, lo: fp16 for the symmetric formats, bf16 for zero point), permuted; down: act [pair p][2][I]
@@ -97,8 +97,11 @@ struct TiledArgs {
 // together when the range crosses into the next sub-item.
 // DOWN = false: row tile = 8 gate + 8 up rows, 4 slices (K = 2048); act = silu(gate) * up.
 // DOWN = true : row tile = 16 down rows, 1 slice (K = 512); ypair = w * (down . act).
-template <int FMT, bool DOWN, int NW, int D>
-__global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) {
+// NB = 8-column blocks of activations per sub-item (1: up to 4 pairs, 2: up to 8 pairs - the weights of an expert with 5-8
+// pairs are then unpacked once instead of twice); CPS = CTAs per SM the launch is sized for.
+template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2>
+__global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a) {
+    static_assert(NB == 1 || FMT != FMT_ZP, "two column blocks are built for the symmetric formats only");
     constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
     constexpr int KS = DOWN ? 1 : 4;                       // slices per row tile
     constexpr int RPS = (DOWN ? 128 : 64) / NW;            // rounds per sub-item
@@ -107,14 +110,19 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
     constexpr bool Z = FMT == FMT_ZP;
     constexpr bool F16 = !Z;  // symmetric formats run on fp16 operands (cheaper unpacking, 22-bit activations); zero point on bf16
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* bsm = smem + NW * D * SB;                                 // 8 activation columns
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);      // full[NW][D]
+    uint8_t* bsm = smem + NW * D * SB;                                 // 8 * NB activation columns
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * NB * BCOL); // full[NW][D]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
     if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    const long long R = (long long)*a.nsub * RPS;
-    const int r0 = (int)(R * blockIdx.x / gridDim.x), r1 = (int)(R * (blockIdx.x + 1) / gridDim.x);
+    // This CTA's contiguous range of rounds: an equal share of the cost, a round of a wide sub-item (more than 4 pairs,
+    // they come first in subs[]) counting CW and any other CN.
+    constexpr int CN = 10, CW = NB == 2 ? (DOWN ? 14 : 12) : 10;
+    const long long RW = NB == 2 ? (long long)a.nsub[1] * RPS : 0, R = (long long)a.nsub[0] * RPS;
+    const long long C = RW * CW + (R - RW) * CN;
+    auto round_at = [&](long long x) { return (int)(x < RW * CW ? x / CW : RW + (x - RW * CW) / CN); };
+    const int r0 = round_at(C * blockIdx.x / gridDim.x), r1 = round_at(C * (blockIdx.x + 1) / gridDim.x);
     const int Q = (r1 - r0) * KS;  // slices this warp will consume
     uint8_t* ring = smem + warp * D * SB;
     uint64_t* full = bars + warp * D;
@@ -130,7 +138,7 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
     if (lane == 0)
         for (int q = 0; q < D && q < Q; q++) issue(q);
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};  // acd: the second column block
     int cur_sub = -1, n = 0, start = 0;
     const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
     for (int q = 0; q < Q; q++) {
@@ -152,9 +160,10 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
             __syncthreads();
         }
         if (!mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT)) return;
-        if (ks == 0) acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        if (ks == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; acd[0] = acd[1] = acd[2] = acd[3] = 0.f; }
         const uint8_t* sl = ring + (q % D) * SB;
         const uint8_t* bp = bcol + ks * 1024;  // 8 groups of 128 bytes per slice
+        auto groups = [&]<bool WIDE>() {
 #pragma unroll 4
         for (int G = 0; G < 8; G++) {
             const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
@@ -178,6 +187,18 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
                 mma_16<F16>(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w, false);
                 acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
                 acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
+                if constexpr (WIDE) {
+                    {  // the same weight fragments against columns 8-15
+                        const uint4 C0 = *reinterpret_cast<const uint4*>(bp + 8 * BCOL + G * 128), C1 = *reinterpret_cast<const uint4*>(bp + 8 * BCOL + G * 128 + 64);
+                        float d[4];
+                        mma_16<F16>(d, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], C0.x, C0.y, true);
+                        mma_16<F16>(d, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], C0.z, C0.w, false);
+                        mma_16<F16>(d, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], C1.x, C1.y, false);
+                        mma_16<F16>(d, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], C1.z, C1.w, false);
+                        acd[0] = fmaf(d[0], sa, acd[0]); acd[1] = fmaf(d[1], sa, acd[1]);
+                        acd[2] = fmaf(d[2], sb, acd[2]); acd[3] = fmaf(d[3], sb, acd[3]);
+                    }
+                }
             } else {
                 // zero point: each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial sums
                 // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 0 of the group, lanes t = 2,3 chunk 1, and an MMA
@@ -206,35 +227,42 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_tiled_k(const TiledArgs a) 
                 }
             }
         }
+        };
+        // one branch per slice, none inside the unrolled groups (their MMA chains interleave)
+        if (NB == 2 && n > 4) groups.template operator()<NB == 2>(); else groups.template operator()<false>();
         // this slice is consumed: order the warp's reads before the copy that refills the buffer, then issue it
         __syncwarp();
         if (lane == 0 && q + D < Q) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(q + D);
         }
-        if (ks == KS - 1 && t < n) {
-            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) belong to pair slot t
-            const moexb_pair pr = a.pairs[start + t];
-            const float va = acc[0] + acc[1], vb = acc[2] + acc[3];
+        if (ks == KS - 1) {
+            // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) of column block b belong to pair slot 4b + t
             const int wt = rin * NW + warp;
-            if (DOWN) {
-                const int d = 16 * wt + g;
-                a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
-                a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
-            } else {
-                const int row = 8 * wt + g;
-                const float v = va / (1.f + expf(-va)) * vb;
-                if (a.act32) a.act32[(size_t)pr.p * EI + row] = v;
-                uint16_t hi, lo;
-                split_hi_lo<F16>(v, hi, lo);
-                uint16_t* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(row);
-                dst[0] = hi; dst[EI] = lo;
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                if (4 * b + t >= n) break;
+                const moexb_pair pr = a.pairs[start + 4 * b + t];
+                const float va = b ? acd[0] + acd[1] : acc[0] + acc[1], vb = b ? acd[2] + acd[3] : acc[2] + acc[3];
+                if (DOWN) {
+                    const int d = 16 * wt + g;
+                    a.ypair[(size_t)pr.p * EH + d] = pr.w * va;
+                    a.ypair[(size_t)pr.p * EH + d + 8] = pr.w * vb;
+                } else {
+                    const int row = 8 * wt + g;
+                    const float v = va / (1.f + expf(-va)) * vb;
+                    if (a.act32) a.act32[(size_t)pr.p * EI + row] = v;
+                    uint16_t hi, lo;
+                    split_hi_lo<F16>(v, hi, lo);
+                    uint16_t* dst = a.act_split + (size_t)pr.p * 2 * EI + split_pos(row);
+                    dst[0] = hi; dst[EI] = lo;
+                }
             }
         }
     }
 }
 
-template <int FMT, bool DOWN, int NW, int D>
-constexpr int tl_smem_bytes() { return NW * D * tl_slice_bytes<FMT>() + 8 * st_bcol_bytes<DOWN>() + NW * D * 8 + 64; }
+template <int FMT, bool DOWN, int NW, int D, int NB = 1>
+constexpr int tl_smem_bytes() { return NW * D * tl_slice_bytes<FMT>() + 8 * NB * st_bcol_bytes<DOWN>() + NW * D * 8 + 64; }
 
 }  // namespace moexb
