@@ -24,6 +24,15 @@ __host__ __device__ constexpr size_t expert_bytes(int fmt) {
          : fmt == FMT_ZP ? Q_BYTES + CHUNKS * 2 + CHUNKS / 8 * 4 : 0;
 }
 
+// Programmatic dependent launch. A kernel started with the programmatic-serialization launch attribute may begin while
+// its predecessor in the stream still runs: pdl_wait() blocks until the predecessor has finished and its writes are
+// visible, so everything a kernel does before it must touch only data the predecessor does not write (weights, shared
+// memory set-up). pdl_trigger() lets the successor's blocks be scheduled as soon as every block of this grid has
+// called it; every kernel here calls it after its own pdl_wait(), so a successor never runs (not even its part before the
+// wait) until the kernel two places ahead of it has finished. Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

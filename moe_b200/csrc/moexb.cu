@@ -39,6 +39,24 @@ int fail(int code, const char* fmt, ...) {
 std::atomic<long long> g_launches{0};
 
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Launch with programmatic stream serialization: the kernel's blocks may be scheduled before the kernel ahead of it in
+// the stream has finished, and wait for it inside (pdl_wait in common.cuh). Only kernels that call pdl_wait before they
+// touch their inputs are launched this way. MOEXB_PDL=0 in the environment turns it off (plain launches).
+static bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("MOEXB_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+template <typename... P, typename... A>
+static cudaError_t launch_dep(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
+}
 inline bool fmt_ok(int fmt) { return fmt == FMT_SYM_F32 || fmt == FMT_SYM_F16 || fmt == FMT_ZP; }
 
 // Calls f.template operator()<FMT>() for the run-time format.
@@ -154,10 +172,10 @@ static int gemv_any(const WT* W, const float* x, float* y, int I, int O, void* s
         static cudaError_t attr_err = cudaSuccess;
         std::call_once(once, [] { attr_err = cudaFuncSetAttribute(gemm_rows_k<WT, WARPS, TO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
         if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "gemv: shared memory attribute: %s", cudaGetErrorString(attr_err));
-        gemm_rows_k<WT, WARPS, TO, TR><<<dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, smem, S(stream)>>>(W, x, y, I, O, rows);
+        CUDA_TRY(launch_dep(gemm_rows_k<WT, WARPS, TO, TR>, dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, smem, S(stream), W, x, y, I, O, rows));
     } else {
         constexpr int WARPS = 8;
-        gemv_rows_k<WT, WARPS><<<dim3((O + WARPS - 1) / WARPS, rows), WARPS * 32, 0, S(stream)>>>(W, x, y, I, O);
+        CUDA_TRY(launch_dep(gemv_rows_k<WT, WARPS>, dim3((O + WARPS - 1) / WARPS, rows), WARPS * 32, 0, S(stream), W, x, y, I, O));
     }
     LAUNCHED("gemv");
     return MOEXB_OK;
@@ -178,8 +196,8 @@ static int topk_launch(const float* logits, int E, int K, int norm, int* idx, fl
     REQUIRE(K > 0 && K < 32 && K <= E, "router_topk: K=%d out of range", K);
     REQUIRE(T > 0 && ld >= E, "router_topk: T=%d, ld=%d", T, ld);
     constexpr int WARPS = 2;
-    if (E <= 256) router_topk_k<WARPS, 8><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
-    else router_topk_k<WARPS, 32><<<(T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream)>>>(logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub);
+    if (E <= 256) CUDA_TRY(launch_dep(router_topk_k<WARPS, 8>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub));
+    else CUDA_TRY(launch_dep(router_topk_k<WARPS, 32>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub));
     LAUNCHED("router_topk");
     return MOEXB_OK;
 }
@@ -565,7 +583,7 @@ static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "tiled stream kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
-    stream_tiled_k<FMT, DOWN, NW, D, NB, CPS><<<CPS * c->sms, NW * 32, SMEM, S(stream)>>>(a);
+    CUDA_TRY(launch_dep(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, CPS * c->sms, NW * 32, SMEM, S(stream), a));
     LAUNCHED(DOWN ? "stream_tiled_down" : "stream_tiled_gate_up");
     return MOEXB_OK;
 }
@@ -768,11 +786,11 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
         {
             PROF(c, MOEXB_PROF_GROUP, stream);
             if (tiled && !prefill && tiled_maxp(c, L->fmt, T) == 8)
-                group_plan_k<8><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                                              shared ? c->logits + E : nullptr, ld, sh0, sh1);
+                CUDA_TRY(launch_dep(group_plan_k<8>, (E + 7) / 8, 256, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
+                                    shared ? c->logits + E : nullptr, ld, sh0, sh1));
             else
-                group_plan_k<ST_MAXP><<<(E + 7) / 8, 256, 0, st>>>(c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                                                     shared ? c->logits + E : nullptr, ld, sh0, sh1);
+                CUDA_TRY(launch_dep(group_plan_k<ST_MAXP>, (E + 7) / 8, 256, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
+                                    shared ? c->logits + E : nullptr, ld, sh0, sh1));
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
             // reduction skips them by expert id
@@ -787,10 +805,11 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     }
     if (ranks) {
         PROF(c, MOEXB_PROF_COMBINE, stream);
-        if (f16) reduce_residual_norm_k<true><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1,
-                                                                    (!all_local && ranks == K) ? c->idx : nullptr, L->first_local, L->first_local + L->n_local);
-        else reduce_residual_norm_k<false><<<T, 256, 0, st>>>(c->ypair, extra, (block && !partial) ? xin : nullptr, out, ranks, next_norm ? c->xn : nullptr, c->xs, 1e-6f, sh0, sh1,
-                                                                    (!all_local && ranks == K) ? c->idx : nullptr, L->first_local, L->first_local + L->n_local);
+        const float* xres = (block && !partial) ? xin : nullptr;
+        float* xn_next = next_norm ? c->xn : nullptr;
+        const int* held = (!all_local && ranks == K) ? c->idx : nullptr;
+        if (f16) CUDA_TRY(launch_dep(reduce_residual_norm_k<true>, T, 256, 0, st, c->ypair, extra, xres, out, ranks, xn_next, c->xs, 1e-6f, sh0, sh1, held, L->first_local, L->first_local + L->n_local));
+        else CUDA_TRY(launch_dep(reduce_residual_norm_k<false>, T, 256, 0, st, c->ypair, extra, xres, out, ranks, xn_next, c->xs, 1e-6f, sh0, sh1, held, L->first_local, L->first_local + L->n_local));
         LAUNCHED("reduce_residual_norm");
     }
     if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, c->idx, (size_t)T * K * sizeof(int), cudaMemcpyDeviceToDevice, st));
@@ -843,8 +862,9 @@ int moexb_ep_residual_norm(moexb_ctx* c, moexb_layer* next, const float* x, cons
     const bool f16 = next && next->layout == MOEXB_LAYOUT_TILED && next->fmt != FMT_ZP;
     float* xn = next ? c->xn : nullptr;
     PROF(c, MOEXB_PROF_COMBINE, stream);
-    if (f16) reduce_residual_norm_k<true><<<T, 256, 0, S(stream)>>>(total, nullptr, x, out, 1, xn, c->xs, 1e-6f, 0, 0, nullptr, 0, 0);
-    else reduce_residual_norm_k<false><<<T, 256, 0, S(stream)>>>(total, nullptr, x, out, 1, xn, c->xs, 1e-6f, 0, 0, nullptr, 0, 0);
+    const float* no_extra = nullptr; const int* no_idx = nullptr;
+    if (f16) CUDA_TRY(launch_dep(reduce_residual_norm_k<true>, T, 256, 0, S(stream), total, no_extra, x, out, 1, xn, c->xs, 1e-6f, 0, 0, no_idx, 0, 0));
+    else CUDA_TRY(launch_dep(reduce_residual_norm_k<false>, T, 256, 0, S(stream), total, no_extra, x, out, 1, xn, c->xs, 1e-6f, 0, 0, no_idx, 0, 0));
     LAUNCHED("ep_residual_norm");
     return MOEXB_OK;
 }

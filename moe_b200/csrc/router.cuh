@@ -23,15 +23,31 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_rows_k(const WT* __restrict__
     const float* xr = x + (size_t)blockIdx.y * I;
     const WT* wr = W + (size_t)o * I;
     float acc = 0.f;
-    constexpr int U = 8;  // loads of U steps are in flight before the first multiply-add; the summation order is unchanged
-    for (int c0 = 0; c0 < I / 128; c0 += U) {
-        float4 w[U], v[U];
+    constexpr int U = 16;  // loads of U steps are in flight before the first multiply-add; the summation order is unchanged
+    auto steps = [&](int c0, const float4 (&w)[U]) {
+        float4 v[U];
 #pragma unroll
         for (int u = 0; u < U; u++)
-            if (c0 + u < I / 128) { w[u] = ld_w4(wr, (size_t)128 * (c0 + u) + 4 * lane); v[u] = __ldg(reinterpret_cast<const float4*>(xr + 128 * (c0 + u) + 4 * lane)); }
+            if (c0 + u < I / 128) v[u] = __ldg(reinterpret_cast<const float4*>(xr + 128 * (c0 + u) + 4 * lane));
 #pragma unroll
         for (int u = 0; u < U; u++)
             if (c0 + u < I / 128) { acc = fmaf(w[u].x, v[u].x, acc); acc = fmaf(w[u].y, v[u].y, acc); acc = fmaf(w[u].z, v[u].z, acc); acc = fmaf(w[u].w, v[u].w, acc); }
+    };
+    {   // the weights of the first U steps do not depend on the kernel before this one: they are requested before the wait
+        float4 w[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (u < I / 128) w[u] = ld_w4(wr, (size_t)128 * u + 4 * lane);
+        pdl_wait();
+        pdl_trigger();
+        steps(0, w);
+    }
+    for (int c0 = U; c0 < I / 128; c0 += U) {
+        float4 w[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) w[u] = ld_w4(wr, (size_t)128 * (c0 + u) + 4 * lane);
+        steps(c0, w);
     }
     acc = warp_sum(acc);
     if (lane == 0) y[(size_t)blockIdx.y * O + o] = acc;
@@ -46,6 +62,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
                                                           float* __restrict__ y, int I, int O, int rows) {
     extern __shared__ __align__(16) float xsm[];  // [TR][I]
     const int r0 = blockIdx.y * TR, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_trigger();
     for (int i = threadIdx.x * 4; i < TR * I; i += WARPS * 128) {
         const int r = min(r0 + i / I, rows - 1);
         *reinterpret_cast<float4*>(xsm + i) = __ldg(reinterpret_cast<const float4*>(x + (size_t)r * I + i % I));
@@ -103,6 +121,8 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
                                                             moexb_pair_item* __restrict__ dsubs, moexb_pair* __restrict__ dpairs,
                                                             int* __restrict__ dnsub) {
     const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_trigger();
     if (t >= T) return;
     const float* l = logits + (size_t)t * ld;
     const int nj = E >> 5;  // <= NJ
@@ -254,6 +274,8 @@ __global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx,
     const int n = T * K, tid = threadIdx.x, lane = tid & 31;
     for (int e = tid; e < E; e += 256) cnt[e] = 0;
     __syncthreads();
+    pdl_wait();
+    pdl_trigger();
     for (int p = tid; p < n; p += 256) atomicAdd(&cnt[__ldg(idx + p)], 1);
     __syncthreads();
     {

@@ -400,6 +400,8 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
                                                               float* __restrict__ out, int K, float* __restrict__ xn_next,
                                                               uint16_t* __restrict__ xs_next, float eps, int ex0, int ex1,
                                                               const int* __restrict__ idx, int e_lo, int e_hi) {
+    pdl_wait();
+    pdl_trigger();
     const size_t t = blockIdx.x;
     if ((int)t < ex0 || (int)t >= ex1) extra = nullptr;  // extra rows exist only for tokens [ex0, ex1)
     // idx given: only the ranks whose expert lies in [e_lo, e_hi) were computed here (expert parallelism); skip the others

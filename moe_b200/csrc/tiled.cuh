@@ -116,6 +116,11 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
     if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    // Gate/up: the sub-items come from the kernel before this one. Down: they are older (the gate/up kernel read them
+    // too), so the weight copies start while gate/up still runs; only the activation columns wait for it.
+    // The trigger comes after the wait so that the down kernel, which reads the sub-items before its own wait, cannot
+    // start before the kernel that writes them has finished.
+    if (!DOWN) { pdl_wait(); pdl_trigger(); }
     // This CTA's contiguous range of rounds: an equal share of the cost, a round of a wide sub-item (more than 4 pairs,
     // they come first in subs[]) counting CW and any other CN.
     constexpr int CN = 10, CW = NB == 2 ? (DOWN ? 14 : 12) : 10;
@@ -137,6 +142,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     };
     if (lane == 0)
         for (int q = 0; q < D && q < Q; q++) issue(q);
+    if (DOWN) { pdl_wait(); pdl_trigger(); }
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};  // acd: the second column block
     int cur_sub = -1, n = 0, start = 0;
