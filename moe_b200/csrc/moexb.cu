@@ -112,6 +112,7 @@ struct moexb_ctx {
     uint16_t *xs = nullptr, *act_split = nullptr;       // activations / act as 16-bit hi + lo halves, permuted
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
+    int* route_done = nullptr;                          // per token tile: blocks of the routing kernel that have finished (returns to zero)
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
     int pairs_per_pass = 8;                             // sub-item width of the tiled streaming kernels from 8 tokens on
     int prefill_min_tokens = 256;                       // batches from this size on use the tcgen05 grouped GEMM
@@ -196,8 +197,9 @@ static int topk_launch(const float* logits, int E, int K, int norm, int* idx, fl
     REQUIRE(K > 0 && K < 32 && K <= E, "router_topk: K=%d out of range", K);
     REQUIRE(T > 0 && ld >= E, "router_topk: T=%d, ld=%d", T, ld);
     constexpr int WARPS = 2;
-    if (E <= 256) CUDA_TRY(launch_dep(router_topk_k<WARPS, 8>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub));
-    else CUDA_TRY(launch_dep(router_topk_k<WARPS, 32>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, idx, w, T, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub));
+    const TopkOut o{idx, w, slot_table, slots_out, wts_out, dsubs, dpairs, dnsub};
+    if (E <= 256) CUDA_TRY(launch_dep(router_topk_k<WARPS, 8>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, T, o));
+    else CUDA_TRY(launch_dep(router_topk_k<WARPS, 32>, (T + WARPS - 1) / WARPS, WARPS * 32, 0, S(stream), logits, E, K, norm, ld, T, o));
     LAUNCHED("router_topk");
     return MOEXB_OK;
 }
@@ -409,8 +411,9 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
     A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
-    A(&c->nsub, 2); A(&c->err, 1); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
+    A(&c->nsub, 2); A(&c->err, 1); A(&c->route_done, (size_t)max_tokens); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
     if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
+    if (rc == MOEXB_OK && cudaMemset(c->route_done, 0, (size_t)max_tokens * sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
     if (rc != MOEXB_OK) { moexb_ctx_destroy(c); return rc; }
     const Tables& t = host_tables();
@@ -719,18 +722,45 @@ extern "C" {
 
 // Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
 // decode: also emit the K+1 one-pair sub-items of a single token (slots, weights, sub-items, pairs).
+}  // extern "C"
+// Router logits (into the context, [T][E + 1]) and the top-K selection in one launch; decode: also the K + 1 one-pair
+// sub-items of a single token.
+template <typename WT>
+static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode) {
+    const int E = L->n_routed;
+    const WT* W = static_cast<const WT*>(L->router);
+    const TopkOut o{c->idx, c->w, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
+                    decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr};
+    auto run = [&]<int NJ>() -> int {
+        if (T < 8) {
+            constexpr int WARPS = 8;
+            CUDA_TRY(launch_dep(route_gemv_k<WT, WARPS, NJ>, dim3((E + 1 + WARPS - 1) / WARPS, T), WARPS * 32, 0, S(stream), W, xf, c->logits, EH, E, K, 1, c->route_done, o));
+        } else {
+            // 16 outputs per block spread a small batch over more SMs; a prefill chunk has blocks to spare and re-reads
+            // the router weights less with 32 outputs per block
+            auto gemm = [&]<int TO>() -> int {
+                constexpr int WARPS = 8, TR = 8, SMEM = TR * EH * (int)sizeof(float);
+                static std::once_flag once;
+                static cudaError_t attr_err = cudaSuccess;
+                std::call_once(once, [] { attr_err = cudaFuncSetAttribute(route_gemm_k<WT, WARPS, TO, TR, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+                if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
+                CUDA_TRY(launch_dep(route_gemm_k<WT, WARPS, TO, TR, NJ>, dim3((E + 1 + WARPS * TO - 1) / (WARPS * TO), (T + TR - 1) / TR), WARPS * 32, SMEM, S(stream),
+                                    W, xf, c->logits, EH, E, K, 1, T, c->route_done, o));
+                return MOEXB_OK;
+            };
+            const int rc = T >= 256 ? gemm.template operator()<4>() : gemm.template operator()<2>();
+            if (rc != MOEXB_OK) return rc;
+        }
+        LAUNCHED("route");
+        return MOEXB_OK;
+    };
+    return E <= 256 ? run.template operator()<8>() : run.template operator()<32>();
+}
+
+extern "C" {
 static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode) {
-    const int E = L->n_routed, ld = E + 1;
-    int rc;
-    {
-        PROF(c, MOEXB_PROF_ROUTER, stream);
-        rc = L->router_dtype == MOEXB_F32 ? gemv_any(static_cast<const float*>(L->router), xf, c->logits, EH, ld, stream, T)
-                                          : gemv_any(static_cast<const __half*>(L->router), xf, c->logits, EH, ld, stream, T);
-    }
-    if (rc != MOEXB_OK) return rc;
-    PROF(c, MOEXB_PROF_TOPK, stream);
-    return topk_launch(c->logits, E, K, 1, c->idx, c->w, stream, T, ld, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
-                       decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr);
+    PROF(c, MOEXB_PROF_ROUTER, stream);
+    return L->router_dtype == MOEXB_F32 ? route_launch<float>(c, L, xf, T, K, stream, decode) : route_launch<__half>(c, L, xf, T, K, stream, decode);
 }
 
 // One layer. xin: the layer input as f32 [T][H]. flags as moexb_layer_forward. pre_normed: the context already holds

@@ -107,70 +107,211 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_rows_k(const WT* __restrict__
         }
 }
 
-// Softmax over E logits and the K largest, one warp per token (kernels.cuh:373-406 does it with a block per token).
-// Lane l holds logits l, l+32, ..; each round every lane offers its best remaining (value, index), a butterfly keeps
-// the larger value and on equal values the lower index, and the winner is struck from its owner's mask.
-// Selection compares logits (softmax is monotone). NaN logits count as -inf. Optional decode outputs: slots_out /
-// wts_out [K+1] = the selected experts' blob pointers and weights followed by the shared expert with weight
-// sigmoid(logits[E]); dsubs / dpairs / dnsub = the same K+1 experts as one-pair sub-items for the streaming kernels (T = 1).
-template <int WARPS, int NJ>
-__global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restrict__ logits, int E, int K, int norm, int ld,
-                                                            int* __restrict__ idx, float* __restrict__ w, int T,
-                                                            const uint8_t* const* __restrict__ slot_table,
-                                                            const uint8_t** __restrict__ slots_out, float* __restrict__ wts_out,
-                                                            moexb_pair_item* __restrict__ dsubs, moexb_pair* __restrict__ dpairs,
-                                                            int* __restrict__ dnsub) {
-    const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    pdl_wait();
-    pdl_trigger();
-    if (t >= T) return;
-    const float* l = logits + (size_t)t * ld;
+// Softmax over E logits and the K largest by one warp (kernels.cuh:373-406 does it with a block per token).
+// Lane l holds logits l, l+32, ..; each round every lane offers its best remaining value as an order-preserving
+// integer key, one warp reduction finds the largest key and a second the lowest index that holds it (ties go to the
+// lower index), and the winner is struck from its owner's mask. Selection compares logits (softmax is monotone). NaN
+// logits count as -inf. Optional decode outputs: slots_out / wts_out [K+1] = the selected experts' blob pointers and
+// weights followed by the shared expert with weight sigmoid(logits[E]); dsubs / dpairs / dnsub = the same K+1 experts as
+// one-pair sub-items for the streaming kernels (T = 1).
+struct TopkOut {
+    int* idx; float* w;
+    const uint8_t* const* slot_table; const uint8_t** slots_out; float* wts_out;
+    moexb_pair_item* dsubs; moexb_pair* dpairs; int* dnsub;
+};
+__device__ __forceinline__ unsigned f2key(float v) { const unsigned u = __float_as_uint(v); return (u & 0x80000000u) ? ~u : (u | 0x80000000u); }
+__device__ __forceinline__ float key2f(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
+
+// CG: the logits were written by other blocks of the same launch - read them past L1.
+template <int NJ, bool CG>
+__device__ __forceinline__ void topk_token(const float* __restrict__ l, int t, int E, int K, int norm, int lane, const TopkOut& o) {
     const int nj = E >> 5;  // <= NJ
     float v[NJ];
     float m = -INFINITY;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         v[j] = -INFINITY;
-        if (j < nj) { const float a = l[lane + 32 * j]; v[j] = a != a ? -INFINITY : a; }
+        if (j < nj) { const float a = CG ? __ldcg(l + lane + 32 * j) : l[lane + 32 * j]; v[j] = a != a ? -INFINITY : a; }
         m = fmaxf(m, v[j]);
     }
+    const float gate_logit = (o.slots_out && lane == K) ? (CG ? __ldcg(l + E) : l[E]) : 0.f;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) if (j < nj) sum += expf(v[j] - m);
     sum = warp_sum(sum);
-    unsigned taken = 0;
+    unsigned key[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) key[j] = j < nj ? f2key(v[j]) : 0u;  // 0 = not a candidate (below every real key)
     float mine = 0.f, total = 0.f;  // lane k keeps the k-th probability
     int mine_i = 0;
     for (int k = 0; k < K; k++) {
-        float bv = -INFINITY; int bi = 0x7fffffff;
+        unsigned bk = 0; int bj = 0;
 #pragma unroll
-        for (int j = 0; j < NJ; j++)
-            if (j < nj && !(taken >> j & 1) && (v[j] > bv || bi == 0x7fffffff)) { bv = v[j]; bi = lane + 32 * j; }
+        for (int j = 0; j < NJ; j++) if (key[j] > bk) { bk = key[j]; bj = j; }
+        const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+        const unsigned win = __reduce_min_sync(0xffffffffu, bk == top ? (unsigned)(lane + 32 * bj) : 0x7fffffffu);
+        if ((int)(win & 31) == lane) {
 #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            for (int j = 0; j < NJ; j++) if (j == (int)(win >> 5)) key[j] = 0u;
         }
-        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-        const float p = expf(bv - m) / sum;
+        const float p = expf(key2f(top) - m) / sum;
         total += p;
-        if (lane == k) { mine = p; mine_i = bi; }
+        if (lane == k) { mine = p; mine_i = (int)win; }
     }
     if (lane < K) {
         const float wk = norm ? mine / total : mine;
-        idx[(size_t)t * K + lane] = mine_i;
-        w[(size_t)t * K + lane] = wk;
-        if (slots_out) { slots_out[(size_t)t * (K + 1) + lane] = slot_table[mine_i]; wts_out[(size_t)t * (K + 1) + lane] = wk; }
-        if (dsubs) { dsubs[lane] = {slot_table[mine_i], lane, 1}; dpairs[lane] = {0, lane, wk}; }  // one token: expert k = sub-item k
+        o.idx[(size_t)t * K + lane] = mine_i;
+        o.w[(size_t)t * K + lane] = wk;
+        if (o.slots_out) { o.slots_out[(size_t)t * (K + 1) + lane] = o.slot_table[mine_i]; o.wts_out[(size_t)t * (K + 1) + lane] = wk; }
+        if (o.dsubs) { o.dsubs[lane] = {o.slot_table[mine_i], lane, 1}; o.dpairs[lane] = {0, lane, wk}; }  // one token: expert k = sub-item k
     }
-    if (slots_out && lane == K) {
-        const float gate = 1.f / (1.f + expf(-l[E]));
-        slots_out[(size_t)t * (K + 1) + K] = slot_table[E];
-        wts_out[(size_t)t * (K + 1) + K] = gate;
-        if (dsubs) { dsubs[K] = {slot_table[E], K, 1}; dpairs[K] = {0, K, gate}; *dnsub = K + 1; }
+    if (o.slots_out && lane == K) {
+        const float gate = 1.f / (1.f + expf(-gate_logit));
+        o.slots_out[(size_t)t * (K + 1) + K] = o.slot_table[E];
+        o.wts_out[(size_t)t * (K + 1) + K] = gate;
+        if (o.dsubs) { o.dsubs[K] = {o.slot_table[E], K, 1}; o.dpairs[K] = {0, K, gate}; o.dnsub[0] = K + 1; o.dnsub[1] = 0; }
     }
+}
+
+// One warp per token.
+template <int WARPS, int NJ>
+__global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restrict__ logits, int E, int K, int norm, int ld, int T, const TopkOut o) {
+    const int t = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_trigger();
+    if (t >= T) return;
+    topk_token<NJ, false>(logits + (size_t)t * ld, t, E, K, norm, lane, o);
+}
+
+// Whether this block is the last of `expected` blocks to reach this point for counter *cnt (every block calls it once,
+// after its global writes); the last one sees the writes of all the others and resets the counter for the next launch.
+__device__ __forceinline__ bool last_block_done(int* cnt, int expected) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(cnt, 1);
+        s_last = ticket == expected - 1;
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (s_last) __threadfence();
+    return s_last;
+}
+
+// Router logits and top-K selection of a few tokens in one launch: gemv_rows_k's grid (ceil(O / WARPS) blocks per
+// token, O = E + 1), and the last block of a token to finish selects that token's experts - no second launch, no wait:
+// the block that comes last simply does the extra work. done[t] must be zero before the first launch.
+template <typename WT, int WARPS, int NJ>
+__global__ void __launch_bounds__(WARPS * 32) route_gemv_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int I,
+                                                           int E, int K, int norm, int* __restrict__ done, const TopkOut o) {
+    const int O = E + 1, t = blockIdx.y;
+    const int out = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const float* xr = x + (size_t)t * I;
+    const WT* wr = W + (size_t)min(out, O - 1) * I;
+    float acc = 0.f;
+    constexpr int U = 16;
+    auto steps = [&](int c0, const float4 (&w)[U]) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) v[u] = __ldg(reinterpret_cast<const float4*>(xr + 128 * (c0 + u) + 4 * lane));
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) { acc = fmaf(w[u].x, v[u].x, acc); acc = fmaf(w[u].y, v[u].y, acc); acc = fmaf(w[u].z, v[u].z, acc); acc = fmaf(w[u].w, v[u].w, acc); }
+    };
+    {
+        float4 w[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (u < I / 128) w[u] = ld_w4(wr, (size_t)128 * u + 4 * lane);
+        pdl_wait();
+        pdl_trigger();
+        steps(0, w);
+    }
+    for (int c0 = U; c0 < I / 128; c0 += U) {
+        float4 w[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (c0 + u < I / 128) w[u] = ld_w4(wr, (size_t)128 * (c0 + u) + 4 * lane);
+        steps(c0, w);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0 && out < O) y[(size_t)t * O + out] = acc;
+    if (!last_block_done(done + t, gridDim.x)) return;
+    if (threadIdx.x < 32) topk_token<NJ, true>(y + (size_t)t * O, t, E, K, norm, lane, o);
+}
+
+// The same for a batch: gemm_rows_k's tiling (a block stages TR token rows in shared memory, each of its WARPS warps owns
+// TO outputs, every dot product in gemv_rows_k's summation order) with the weights of U steps requested at a time and
+// the next U already in flight; the last block of a token tile to finish selects the experts of its TR tokens (warp r
+// takes token r, so TR <= WARPS). grid (ceil((E + 1) / (WARPS * TO)), ceil(T / TR)); dynamic shared memory TR * I floats;
+// done[tile] zero before the first launch.
+template <typename WT, int WARPS, int TO, int TR, int NJ>
+__global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int I,
+                                                           int E, int K, int norm, int T, int* __restrict__ done, const TopkOut o) {
+    static_assert(TR <= WARPS, "one warp per token in the selection");
+    extern __shared__ __align__(16) float xsm[];  // [TR][I]
+    constexpr int U = 4;
+    const int O = E + 1, r0 = blockIdx.y * TR, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int o0 = (blockIdx.x * WARPS + warp) * TO;
+    const WT* wr[TO];
+#pragma unroll
+    for (int i = 0; i < TO; i++) wr[i] = W + (size_t)min(o0 + i, O - 1) * I;
+    float4 wn[TO][U];  // the weights of the next U steps
+    auto load_w = [&](int c0) {
+#pragma unroll
+        for (int i = 0; i < TO; i++)
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (c0 + u < I / 128) wn[i][u] = ld_w4(wr[i], (size_t)128 * (c0 + u) + 4 * lane);
+    };
+    load_w(0);  // weights do not depend on the kernel before this one
+    pdl_wait();
+    pdl_trigger();
+    for (int i = threadIdx.x * 4; i < TR * I; i += WARPS * 128) {
+        const int r = min(r0 + i / I, T - 1);
+        *reinterpret_cast<float4*>(xsm + i) = __ldg(reinterpret_cast<const float4*>(x + (size_t)r * I + i % I));
+    }
+    __syncthreads();
+    float acc[TR][TO];
+#pragma unroll
+    for (int r = 0; r < TR; r++)
+#pragma unroll
+        for (int i = 0; i < TO; i++) acc[r][i] = 0.f;
+    for (int c0 = 0; c0 < I / 128; c0 += U) {
+        float4 w[TO][U];
+#pragma unroll
+        for (int i = 0; i < TO; i++)
+#pragma unroll
+            for (int u = 0; u < U; u++) w[i][u] = wn[i][u];
+        if (c0 + U < I / 128) load_w(c0 + U);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (c0 + u >= I / 128) break;
+#pragma unroll
+            for (int r = 0; r < TR; r++) {
+                const float4 v = *reinterpret_cast<const float4*>(xsm + r * I + 128 * (c0 + u) + 4 * lane);
+#pragma unroll
+                for (int i = 0; i < TO; i++) {
+                    float a = acc[r][i];
+                    a = fmaf(w[i][u].x, v.x, a); a = fmaf(w[i][u].y, v.y, a); a = fmaf(w[i][u].z, v.z, a); a = fmaf(w[i][u].w, v.w, a);
+                    acc[r][i] = a;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < TR; r++)
+#pragma unroll
+        for (int i = 0; i < TO; i++) {
+            const float sum = warp_sum(acc[r][i]);
+            if (lane == 0 && r0 + r < T && o0 + i < O) y[(size_t)(r0 + r) * O + o0 + i] = sum;
+        }
+    if (!last_block_done(done + blockIdx.y, gridDim.x)) return;
+    if (warp < TR && r0 + warp < T) topk_token<NJ, true>(y + (size_t)(r0 + warp) * O, r0 + warp, E, K, norm, lane, o);
 }
 
 // ---- pair grouping: bucket the T*K (token, rank) pairs by expert (moex.cu:1466-1486; kernels.cuh:1030-1045) ----------
