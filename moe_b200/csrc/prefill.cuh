@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 2);
     int* s_fail = reinterpret_cast<int*>(s_tmem + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) { mbar_init(smem_u32(bars), 1); mbar_init(smem_u32(bars + 1), 1); *s_fail = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    if (tid == 0) { mbar_init(smem_u32(bars), 2); mbar_init(smem_u32(bars + 1), 2); *s_fail = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "n"(PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -205,17 +205,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
             tmem_st16(tmem + lane_base + col + 32, lo);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         };
-        // issue the 16 MMAs of group G (one thread): D[half] += (-A_nh + A_lo)[half] * B over the group's four K steps
-        auto issue = [&](int G) {
+        // issue the 8 MMAs of weight half h of group G (one thread per half - issuing an MMA costs its thread about 90 cycles
+        // whatever N is, so the two halves are issued from two warps): D[h] += (-A_nh + A_lo)[h] * B over the four K steps
+        auto issue = [&](int G, int h) {
             const uint32_t aT = tmem + (uint32_t)(PF_TMEM_A + (G & 1) * 128), bB = smem_u32(sB + (G % 3) * PF_B_STAGE);
 #pragma unroll
-            for (int h = 0; h < 2; h++)
+            for (int hl = 0; hl < 2; hl++)
 #pragma unroll
-                for (int hl = 0; hl < 2; hl++)
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        umma_f16_ts(tmem + (uint32_t)(h * PF_NMAX), aT + (uint32_t)(h * 64 + hl * 32 + ks * 8),
-                                    umma_desc(bB + ks * 2 * (N * 16), N * 16, 128), hl ? idesc : (idesc | UMMA_NEGATE_A), G > 0 || hl > 0 || ks > 0);
+                for (int ks = 0; ks < 4; ks++)
+                    umma_f16_ts(tmem + (uint32_t)(h * PF_NMAX), aT + (uint32_t)(h * 64 + hl * 32 + ks * 8),
+                                umma_desc(bB + ks * 2 * (N * 16), N * 16, 128), hl ? idesc : (idesc | UMMA_NEGATE_A), G > 0 || hl > 0 || ks > 0);
             umma_commit(smem_u32(bars + (G & 1)));
         };
         auto wait_mma = [&](int G) {  // MMAs of group G (and all before) done (bounded)
@@ -236,7 +235,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
         unpack(0);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        if (tid == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(0); }
+        if ((tid & ~32) == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(0, tid >> 5); }
         for (int G = 0; G < NG; G++) {
             // group G is on the tensor core. Meanwhile: unpack group G+1 (visible since the previous barrier), request what
             // comes later, and make sure that everything requested before this iteration has landed before the next barrier.
@@ -251,7 +250,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             if (*s_fail) break;
-            if (G + 1 < NG && tid == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(G + 1); }
+            if (G + 1 < NG && (tid & ~32) == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(G + 1, tid >> 5); }
         }
         if (*s_fail) break;
         wait_mma(NG - 1);
