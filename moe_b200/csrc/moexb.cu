@@ -738,8 +738,8 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
         } else {
             // 16 outputs per block spread a small batch over more SMs; a prefill chunk has blocks to spare and re-reads
             // the router weights less with 32 outputs per block
-            auto gemm = [&]<int TO>() -> int {
-                constexpr int WARPS = 8, TR = 8, SMEM = TR * EH * (int)sizeof(float);
+            auto gemm = [&]<int TO, int TR>() -> int {
+                constexpr int WARPS = 8, SMEM = TR * EH * (int)sizeof(float);
                 static std::once_flag once;
                 static cudaError_t attr_err = cudaSuccess;
                 std::call_once(once, [] { attr_err = cudaFuncSetAttribute(route_gemm_k<WT, WARPS, TO, TR, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
@@ -748,7 +748,9 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
                                     W, xf, c->logits, EH, E, K, 1, T, c->route_done, o));
                 return MOEXB_OK;
             };
-            const int rc = T >= 256 ? gemm.template operator()<4>() : gemm.template operator()<2>();
+            // a small batch: 16 outputs x 8 tokens per block, to reach every SM; a prefill chunk has blocks to spare and
+            // re-reads the router weights less with 32 outputs x 16 tokens per block
+            const int rc = T >= 256 ? gemm.template operator()<4, 16>() : gemm.template operator()<2, 8>();
             if (rc != MOEXB_OK) return rc;
         }
         LAUNCHED("route");

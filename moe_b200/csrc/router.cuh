@@ -247,12 +247,11 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemv_k(const WT* __restrict_
 // The same for a batch: gemm_rows_k's tiling (a block stages TR token rows in shared memory, each of its WARPS warps owns
 // TO outputs, every dot product in gemv_rows_k's summation order) with the weights of U steps requested at a time and
 // the next U already in flight; the last block of a token tile to finish selects the experts of its TR tokens (warp r
-// takes token r, so TR <= WARPS). grid (ceil((E + 1) / (WARPS * TO)), ceil(T / TR)); dynamic shared memory TR * I floats;
+// takes tokens r, r + WARPS, ..). grid (ceil((E + 1) / (WARPS * TO)), ceil(T / TR)); dynamic shared memory TR * I floats;
 // done[tile] zero before the first launch.
 template <typename WT, int WARPS, int TO, int TR, int NJ>
 __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int I,
                                                            int E, int K, int norm, int T, int* __restrict__ done, const TopkOut o) {
-    static_assert(TR <= WARPS, "one warp per token in the selection");
     extern __shared__ __align__(16) float xsm[];  // [TR][I]
     constexpr int U = 4;
     const int O = E + 1, r0 = blockIdx.y * TR, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -311,7 +310,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
             if (lane == 0 && r0 + r < T && o0 + i < O) y[(size_t)(r0 + r) * O + o0 + i] = sum;
         }
     if (!last_block_done(done + blockIdx.y, gridDim.x)) return;
-    if (warp < TR && r0 + warp < T) topk_token<NJ, true>(y + (size_t)(r0 + warp) * O, r0 + warp, E, K, norm, lane, o);
+    for (int r = warp; r < TR && r0 + r < T; r += WARPS) topk_token<NJ, true>(y + (size_t)(r0 + r) * O, r0 + r, E, K, norm, lane, o);
 }
 
 // ---- pair grouping: bucket the T*K (token, rank) pairs by expert (moex.cu:1466-1486; kernels.cuh:1030-1045) ----------

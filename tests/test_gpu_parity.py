@@ -458,3 +458,75 @@ def test_prefill_grouped_gemm_tcgen05(bf16_input):
     out2 = L.forward(X.to(DEV), T, 8)
     check_ffn(out2.cpu().numpy(), ref, m.FMT_SYM_F16, "streaming kernels on the same batch")
     L.close(); c.close()
+
+
+def test_pairs_per_pass_4_and_8_agree_bit_for_bit(ctx, layer_sym):
+    """Sub-items of 8 pairs (two column blocks, wide ones first, cost-weighted split) and of 4 pairs compute every pair's
+    sums in the same order, so the outputs are identical bit for bit; a skewed batch (every token is the same vector, so
+    eight experts get 48 pairs each) exercises wide sub-items, their tails and the shared expert together."""
+    L, W, host = layer_sym
+    rng = np.random.default_rng(9)
+    T = 48
+    for name, X in (("random", rng.standard_normal((T, 2048)).astype(np.float32)),
+                    ("skewed", np.repeat(rng.standard_normal((1, 2048)).astype(np.float32), T, axis=0))):
+        outs = []
+        for p in (4, 8):
+            ctx.set_pairs_per_pass(p)
+            outs.append(L.forward(dev(X), T, 8).cpu().numpy().copy())
+        ctx.set_pairs_per_pass(8)
+        assert ctx.status() == 0
+        assert np.array_equal(outs[0], outs[1]), name
+        ref, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X, 8)
+        check_ffn(outs[1], ref, m.FMT_SYM_F16, f"pairs per pass, {name} batch")
+    with pytest.raises(m.MoexbError, match="4 or 8"):
+        ctx.set_pairs_per_pass(6)
+
+
+@pytest.mark.parametrize("T", [1, 5, 64, 300])
+def test_fused_routing_matches_the_entry_points(ctx, layer_sym, T):
+    """The layer's routing (logits and top-K in one launch; the last block of a token tile selects) gives the same ids and
+    weights as moexb_gemv_f32 followed by moexb_router_topk, bit for bit."""
+    L, W, host = layer_sym
+    rng = np.random.default_rng(40 + T)
+    c = ctx if T <= 64 else m.Context(0, max_tokens=T, max_experts=256, top_k=8)
+    if T > 64:
+        L = m.Layer(c, m.FMT_SYM_F16, 256)
+        L.fill_synth(3, 0); L.set_router(W)
+    X = rng.standard_normal((T, 2048)).astype(np.float32)
+    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV); w = torch.empty(T, 8, device=DEV)
+    L.forward(dev(X), T, 8, idx=idx, w=w)
+    logits = m.gemv_f32(dev(W), dev(X), rows=T)
+    idx2, w2 = m.router_topk(logits, 256, 8, T=T, ld=257)
+    assert np.array_equal(idx.cpu().numpy(), idx2.cpu().numpy())
+    assert np.array_equal(w.cpu().numpy(), w2.cpu().numpy())
+    if T > 64:
+        L.close(); c.close()
+
+
+def test_prefill_chunk_of_2048_tokens_both_kernel_families_agree():
+    """The full prefill chunk (2048 bf16 tokens, 256 + 1 experts): the tcgen05 grouped GEMM and the streaming kernels are
+    independent implementations; on the same batch they select the same experts and their outputs agree within the parity
+    bars (each against the other as reference), and a sample of tokens is checked against the oracle."""
+    rng = np.random.default_rng(2048)
+    E, T = 256, 2048
+    c = m.Context(0, max_tokens=T, max_experts=E, top_k=8)
+    L = m.Layer(c, m.FMT_SYM_F16, E)
+    L.fill_synth(0, 0)
+    W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
+    L.set_router(W)
+    X = torch.from_numpy(rng.standard_normal((T, 2048)).astype(np.float32)).to(torch.bfloat16)
+    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+    out_tc = L.forward(X.to(DEV), T, 8, idx=idx).cpu().numpy().copy()
+    assert c.status() == 0
+    c.set_prefill_min_tokens(1 << 20)
+    idx2 = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+    out_st = L.forward(X.to(DEV), T, 8, idx=idx2).cpu().numpy().copy()
+    assert c.status() == 0
+    assert np.array_equal(idx.cpu().numpy(), idx2.cpu().numpy())
+    check_ffn(out_tc, out_st, m.FMT_SYM_F16, "tcgen05 grouped GEMM against the streaming kernels, 2048 tokens")
+    sample = rng.choice(T, 24, replace=False)
+    host = [m.synth_expert_host(m.FMT_SYM_F16, 0, 0, e) for e in range(E + 1)]
+    ref, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X.float().numpy()[sample], 8)
+    assert np.array_equal(idx.cpu().numpy()[sample], ri)
+    check_ffn(out_tc[sample], ref, m.FMT_SYM_F16, "2048-token chunk, sampled tokens against the oracle")
+    L.close(); c.close()
