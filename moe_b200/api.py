@@ -152,6 +152,9 @@ class Context:
     def set_prefill_min_tokens(self, tokens):
         check(lib().moexb_ctx_set_prefill_min_tokens(self.h, tokens))
 
+    def set_fused_decode(self, on):
+        check(lib().moexb_ctx_set_fused_decode(self.h, int(on)))
+
     def set_pairs_per_pass(self, pairs):
         check(lib().moexb_ctx_set_pairs_per_pass(self.h, pairs))
 

@@ -1,0 +1,343 @@
+// One token through a whole stack of residual MoE blocks in ONE cooperative launch.
+//
+// A single token touches 17 MB per layer - 2.6 us of HBM time - so a layer made of separate launches is all latency: every
+// kernel is a chain of dependent global round trips plus its launch. Here one persistent CTA per SM (all co-resident:
+// cudaLaunchCooperativeKernel) walks the layers, and what every CTA needs of the token (the residual row, its rmsnorm, the
+// fp16 hi + lo split, the selected experts) lives in its own shared memory, recomputed redundantly by every CTA instead of
+// being passed through global memory. Per layer:
+//   P1  router logits: CTA b computes rows b, b + grid, .. of W . xn (one warp per row, the pinned summation order of
+//       gemv_rows_k) -> logits[E + 1] in global memory.                                        -- grid barrier --
+//   P2  every CTA: top-K of the logits (warp 0, topk_token), the K + 1 expert blobs and weights into shared memory.
+//   P3  gate/up: (expert, row tile of 8 gate + 8 up rows) units, two per CTA pass, the four K slices of a unit on four
+//       warps (one 4.3 KB bulk copy each, issued as soon as P2 is done), partial sums added in shared memory, SiLU * up
+//       -> act[K + 1][2][I] (fp16 hi, lo) in global memory. The warps' down slices (P4) are requested at the same time.
+//                                                                                              -- grid barrier --
+//   P4  down: (expert, row tile of 16 rows) units, one slice per warp; the expert's act row comes from L2
+//       -> ypair[K + 1][H] in global memory.                                                   -- grid barrier --
+//   P5  every CTA: x += sum of the K + 1 rows in rank order (the order of reduce_residual_norm_k), rmsnorm and split for
+//       the next layer, all in shared memory.
+// The grid barrier is a monotonic counter in global memory (zeroed by the host before the launch): one thread per CTA adds
+// 1 and polls until the counter reaches (barriers so far) x grid. Every poll loop is bounded; a time-out sets the error
+// word and an abort flag that all other loops watch, and the CTAs leave after waiting (bounded) for their copies in flight.
+// The arithmetic of a slice is that of stream_tiled_k (exact fp16 nibbles, hi + lo activations, mma.sync, fp32 group
+// scales), so results agree with the multi-launch path to rounding of the partial-sum order; logits, selected experts and
+// the rmsnorm are bit-identical.
+#pragma once
+#include "common.cuh"
+#include "router.cuh"
+#include "stream.cuh"
+#include "tiled.cuh"
+
+namespace moexb {
+
+struct DecodeLayer {
+    const void* router;                   // [E + 1][H] f32 or f16
+    const uint8_t* const* slot_table;     // E + 1 blob pointers (tiled layout)
+};
+
+struct DecodeStackArgs {
+    const DecodeLayer* layers;
+    int n_layers, E, K;
+    const void* x_in;        // [H] f32 or bf16
+    float* x_out;            // [H]
+    float* logits;           // [E + 1]
+    uint16_t* act;           // [K + 1][2][I] fp16 hi, lo in split_pos order
+    float* ypair;            // [K + 1][H]
+    int* idx_out;            // optional [n_layers][K]
+    float* w_out;            // optional [n_layers][K]
+    unsigned* sync;          // [0] barrier counter, [1] abort flag; zero before the launch
+    int* err;
+};
+
+constexpr int DS_WARPS = 8, DS_THREADS = DS_WARPS * 32;
+constexpr int DS_D = 3;                       // slice buffers per warp
+constexpr int DS_XCOL = EH * 2 + 64;          // stride between the hi and lo columns of the token (bytes)
+constexpr int DS_ACOL = EI * 2 + 64;          // the same for an expert's act row
+constexpr int DS_MAXK = 8;
+constexpr int DS_POLL_LIMIT = 1 << 22;
+constexpr int DS_ERR_BARRIER = 5, DS_ERR_COPY = 6;
+
+template <int FMT> constexpr int ds_smem_bytes() {
+    return DS_WARPS * DS_D * tl_slice_bytes<FMT>() + 2 * DS_XCOL + DS_WARPS * 2 * DS_ACOL + 2 * EH * 4 /* xres, xn */ +
+           2 * 4 * 16 * 2 * 4 /* partial sums */ + DS_WARPS * DS_D * 8 + 256;
+}
+
+// 8 groups of one slice against the lane's two activation columns (bp: the lane's column pointer, already offset to the
+// slice's first input); acc[0..1] += row g, acc[2..3] += row g + 8 (columns 2t, 2t + 1).
+template <int FMT>
+__device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4]) {
+    constexpr int GB = tl_group_bytes<FMT>();
+    const int g = lane >> 2;
+#pragma unroll 4
+    for (int G = 0; G < 8; G++) {
+        const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
+        const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
+        uint32_t Pa[2][4], Pb[2][4];
+        dq_word_h(qq.x, Pa[0]); dq_word_h(qq.y, Pa[1]); dq_word_h(qq.z, Pb[0]); dq_word_h(qq.w, Pb[1]);
+        float sa, sb;
+        if constexpr (FMT == FMT_SYM_F16) {
+            const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(sl + G * GB + 512 + 4 * g));
+            sa = s2.x; sb = s2.y;
+        } else {
+            const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
+            sa = s2.x; sb = s2.y;
+        }
+        float c[4];
+        mma_16<true>(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y, true);
+        mma_16<true>(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w, false);
+        mma_16<true>(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y, false);
+        mma_16<true>(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w, false);
+        acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
+        acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
+    }
+}
+
+// WT: router weight type; XBF: the input row is bf16. Symmetric formats only (fp16 operands).
+template <int FMT, typename WT, bool XBF>
+__global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStackArgs a) {
+    static_assert(FMT != FMT_ZP, "zero-point blobs take the multi-launch path");
+    constexpr int SB = tl_slice_bytes<FMT>();
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;                                               // [warp][DS_D][SB]
+    uint8_t* xcol = ring + DS_WARPS * DS_D * SB;                        // token hi, lo columns (fp16, split_pos order)
+    uint8_t* acol = xcol + 2 * DS_XCOL;                                 // [warp][2][DS_ACOL] act columns for the down slice
+    float* xres = reinterpret_cast<float*>(acol + DS_WARPS * 2 * DS_ACOL);  // [H] the residual row
+    float* xn = xres + EH;                                              // [H] its rmsnorm
+    float* part = xn + EH;                                              // [2 units][4 k slices][16 rows][2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(part + 2 * 4 * 16 * 2);    // [warp][DS_D]
+    __shared__ int s_idx[DS_MAXK];
+    __shared__ float s_w[DS_MAXK];
+    __shared__ const uint8_t* s_slot[DS_MAXK + 1];
+    __shared__ float s_wt[DS_MAXK + 1];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int grid = gridDim.x, b = blockIdx.x, E = a.E, K = a.K, O = E + 1;
+    if (tid < DS_WARPS * DS_D) mbar_init(smem_u32(bars + tid), 1);
+    if (tid == 0) { s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    // the token: residual row, rmsnorm, split (every CTA its own copy)
+    float v[8];
+    {
+        float x8[8];
+        if constexpr (XBF) {
+            const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a.x_in);
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) x8[4 * h + i] = __bfloat162float(x[1024 * h + 4 * tid + i]);
+        } else {
+            const float* x = static_cast<const float*>(a.x_in);
+            const float4 p = *reinterpret_cast<const float4*>(x + 4 * tid), q = *reinterpret_cast<const float4*>(x + 1024 + 4 * tid);
+            x8[0] = p.x; x8[1] = p.y; x8[2] = p.z; x8[3] = p.w; x8[4] = q.x; x8[5] = q.y; x8[6] = q.z; x8[7] = q.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = x8[i];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            *reinterpret_cast<float4*>(xres + 1024 * h + 4 * tid) = make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+    }
+    __syncthreads();
+    norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
+    __syncthreads();
+
+    unsigned barriers = 0;   // grid barriers passed
+    // all CTAs have finished the phase before this call; false: time-out or abort
+    auto grid_barrier = [&]() -> bool {
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(a.sync, 1u);
+            const unsigned target = (barriers + 1) * (unsigned)grid;
+            int i = 0;
+            for (; i < DS_POLL_LIMIT; i++) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.sync) : "memory");
+                if (seen >= target) break;
+                if ((i & 63) == 63) {
+                    unsigned ab;
+                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(a.sync + 1) : "memory");
+                    if (ab) { s_abort = 1; break; }
+                }
+            }
+            if (i == DS_POLL_LIMIT) { atomicExch(a.err, DS_ERR_BARRIER); atomicExch(a.sync + 1, 1u); s_abort = 1; }
+        }
+        barriers++;
+        __syncthreads();
+        return !s_abort;
+    };
+
+    // slices of this warp per layer: n3 gate/up passes (unit = 2 * (pass * grid + b) + (warp >> 2), K slice warp & 3), then n4
+    // down passes (unit = (pass * grid + b) * DS_WARPS + warp)
+    const int U3 = (K + 1) * 64, U4 = (K + 1) * 128;
+    const int n3 = (U3 + 2 * grid - 1) / (2 * grid), n4 = (U4 + DS_WARPS * grid - 1) / (DS_WARPS * grid), nS = n3 + n4;
+    uint8_t* myring = ring + warp * DS_D * SB;
+    uint64_t* mybars = bars + warp * DS_D;
+    long long S0 = 0;        // slices (list entries) of this warp in earlier layers
+    // source of list entry s of this layer, or null when the entry is empty
+    auto slice_src = [&](int s) -> const uint8_t* {
+        if (s < n3) {
+            const int u = 2 * (s * grid + b) + (warp >> 2);
+            if (u >= U3) return nullptr;
+            return s_slot[u >> 6] + (size_t)((u & 63) * 4 + (warp & 3)) * SB;
+        }
+        const int u = ((s - n3) * grid + b) * DS_WARPS + warp;
+        if (u >= U4) return nullptr;
+        return s_slot[u >> 7] + (size_t)(256 + (u & 127)) * SB;
+    };
+    auto issue = [&](int s) {   // lane 0
+        const uint8_t* src = slice_src(s);
+        if (!src) return;
+        const long long S = S0 + s;
+        const uint32_t bar = smem_u32(mybars + S % DS_D);
+        mbar_arrive_expect_tx(bar, SB);
+        bulk_g2s(smem_u32(myring + (S % DS_D) * SB), src, SB, bar);
+    };
+    uint32_t phase = 0;      // bit j: parity of the next completion of buffer j's barrier (empty list entries skip a buffer)
+    auto wait_slice = [&](int s) -> bool {
+        const int j = (int)((S0 + s) % DS_D);
+        const bool in = mbar_wait(smem_u32(mybars + j), (phase >> j) & 1u, a.err, DS_ERR_COPY);
+        phase ^= 1u << j;
+        if (!in) { atomicExch(a.sync + 1, 1u); s_abort = 1; }
+        return in;
+    };
+    int issued = 0, consumed = 0;   // list entries of this layer (the warp's lanes agree)
+    bool ok = true;
+
+    for (int l = 0; l < a.n_layers && ok; l++) {
+        const DecodeLayer L = a.layers[l];
+        // ---- P1: router logits of rows b, b + grid, .. (one warp each) ----
+        for (int r = b + warp * grid; r < O; r += DS_WARPS * grid) {
+            const WT* wr = static_cast<const WT*>(L.router) + (size_t)r * EH;
+            float4 w[16];
+#pragma unroll
+            for (int u = 0; u < 16; u++) w[u] = ld_w4(wr, (size_t)128 * u + 4 * lane);
+            float acc = 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; u++) {
+                const float4 x = *reinterpret_cast<const float4*>(xn + 128 * u + 4 * lane);
+                acc = fmaf(w[u].x, x.x, acc); acc = fmaf(w[u].y, x.y, acc); acc = fmaf(w[u].z, x.z, acc); acc = fmaf(w[u].w, x.w, acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) __stcg(a.logits + r, acc);
+        }
+        if (!(ok = grid_barrier())) break;
+        // ---- P2: selection (every CTA), blob pointers and weights of the K + 1 experts ----
+        if (warp == 0) {
+            const TopkOut o{s_idx, s_w, L.slot_table, s_slot, s_wt, nullptr, nullptr, nullptr};
+            topk_token<8, true>(a.logits, 0, E, K, 1, lane, o);
+            if (b == 0 && lane < K) {
+                if (a.idx_out) a.idx_out[(size_t)l * K + lane] = s_idx[lane];
+                if (a.w_out) a.w_out[(size_t)l * K + lane] = s_w[lane];
+            }
+        }
+        __syncthreads();
+        // ---- P3: gate/up. All copies this layer needs that fit the ring are requested now, the down slices included ----
+        issued = 0; consumed = 0;
+        if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the buffers were read by the warp in the layer before
+            for (; issued < nS && issued < DS_D; issued++) issue(issued);
+        }
+        issued = __shfl_sync(0xffffffffu, issued, 0);
+        if (l + 1 < a.n_layers && warp < 2) {   // the next layer's router rows of this CTA: into L2 while the experts stream
+            const int r = b + warp * grid;
+            if (r < O) {
+                const char* p = static_cast<const char*>(a.layers[l + 1].router) + (size_t)r * EH * sizeof(WT);
+                for (int i = lane * 128; i < EH * (int)sizeof(WT); i += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
+            }
+        }
+        for (int pass = 0; pass < n3 && ok; pass++) {
+            const int u = 2 * (pass * grid + b) + (warp >> 2);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (u < U3) {
+                if (!wait_slice(pass)) { ok = false; }
+                else ds_slice<FMT>(myring + ((S0 + pass) % DS_D) * SB, xcol + (g & 1) * DS_XCOL + t * 16 + (warp & 3) * 1024, lane, acc);
+            }
+            consumed = pass + 1;
+            __syncwarp();
+            if (lane == 0 && issued < nS) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue(issued); }
+            if (issued < nS) issued++;
+            if (t == 0 && u < U3) {
+                float* p = part + (((warp >> 2) * 4 + (warp & 3)) * 16 + g) * 2;
+                p[0] = acc[0] + acc[1]; p[1] = acc[2] + acc[3];
+            }
+            __syncthreads();
+            if ((warp & 3) == 0 && lane < 8 && u < U3) {   // rows 8*wt + lane of gate and up: add the four K slices, SiLU * up
+                const float* p = part + ((warp >> 2) * 4 * 16 + lane) * 2;
+                float G = 0.f, U = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) { G += p[ks * 32]; U += p[ks * 32 + 1]; }
+                const float val = G / (1.f + expf(-G)) * U;
+                uint16_t hi, lo;
+                split_hi_lo<true>(val, hi, lo);
+                const int k = u >> 6, row = 8 * (u & 63) + lane;
+                uint16_t* dst = a.act + (size_t)k * 2 * EI + split_pos(row);
+                __stcg(dst, hi); __stcg(dst + EI, lo);
+            }
+            ok = __syncthreads_and(ok);   // also: every warp leaves the loop together when a copy timed out
+        }
+        if (!ok || !(ok = grid_barrier())) break;
+        // ---- P4: down. The slice is (mostly) in shared memory already; the expert's act row comes from L2 ----
+        for (int pass = 0; pass < n4 && ok; pass++) {
+            const int u = (pass * grid + b) * DS_WARPS + warp;
+            if (u < U4) {
+                const int k = u >> 7, wt = u & 127;
+                uint8_t* ac = acol + warp * 2 * DS_ACOL;
+                const uint4* src = reinterpret_cast<const uint4*>(a.act + (size_t)k * 2 * EI);   // 2 x 1024 bytes
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int c = lane + 32 * i;   // 16-byte chunk 0..127: column c >> 6, chunk c & 63
+                    *reinterpret_cast<uint4*>(ac + (c >> 6) * DS_ACOL + (c & 63) * 16) = __ldcg(src + c);
+                }
+                __syncwarp();
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                if (!wait_slice(n3 + pass)) ok = false;
+                else {
+                    ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc);
+                    if (t == 0) {
+                        const float w = s_wt[k];
+                        const int d = 16 * wt + g;
+                        __stcg(a.ypair + (size_t)k * EH + d, w * (acc[0] + acc[1]));
+                        __stcg(a.ypair + (size_t)k * EH + d + 8, w * (acc[2] + acc[3]));
+                    }
+                }
+            }
+            consumed = n3 + pass + 1;
+            __syncwarp();
+            if (lane == 0 && issued < nS) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue(issued); }
+            if (issued < nS) issued++;
+        }
+        S0 += nS;
+        if (!__syncthreads_and(ok) || !(ok = grid_barrier())) { ok = false; break; }
+        // ---- P5: x += the K + 1 rows in rank order, rmsnorm + split for the next layer (every CTA) ----
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int k0 = 1024 * h + 4 * tid;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int rb = 0; rb <= K; rb += 3) {
+                float4 y[3];
+#pragma unroll
+                for (int u = 0; u < 3; u++) if (rb + u <= K) y[u] = __ldcg(reinterpret_cast<const float4*>(a.ypair + (size_t)(rb + u) * EH + k0));
+#pragma unroll
+                for (int u = 0; u < 3; u++) if (rb + u <= K) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
+            }
+            const float4 x = *reinterpret_cast<const float4*>(xres + k0);
+            acc.x = x.x + acc.x; acc.y = x.y + acc.y; acc.z = x.z + acc.z; acc.w = x.w + acc.w;
+            *reinterpret_cast<float4*>(xres + k0) = acc;
+            v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
+        }
+        __syncthreads();   // part[] of norm_split_row and xn / xcol are free: every warp is past P1 and P3 of this layer
+        if (l + 1 < a.n_layers) norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
+        __syncthreads();
+    }
+    // leave: no copy may still be in flight into this CTA's shared memory
+    if (!ok) {
+        for (int s = consumed; s < issued; s++)
+            if (slice_src(s)) wait_slice(s);
+        return;
+    }
+    if (b == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) *reinterpret_cast<float4*>(a.x_out + 1024 * h + 4 * tid) = *reinterpret_cast<const float4*>(xres + 1024 * h + 4 * tid);
+    }
+}
+
+}  // namespace moexb

@@ -7,6 +7,7 @@
 #include "stream.cuh"
 #include "tiled.cuh"
 #include "prefill.cuh"
+#include "decode_stack.cuh"
 
 #include <cmath>
 #include <cstdarg>
@@ -114,6 +115,7 @@ struct moexb_ctx {
     int *nsub = nullptr, *err = nullptr;
     int* route_done = nullptr;                          // per token tile: blocks of the routing kernel that have finished (returns to zero)
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
+    int fused_decode = 1;                               // one-token residual stacks run as one cooperative launch
     int pairs_per_pass = 8;                             // sub-item width of the tiled streaming kernels from 8 tokens on
     int prefill_min_tokens = 256;                       // batches from this size on use the tcgen05 grouped GEMM
     uint8_t* staging = nullptr;                         // reference-layout blobs on their way into a tiled image
@@ -690,6 +692,12 @@ extern "C" int moexb_pairs_forward_tc(moexb_ctx* c, int fmt, const moexb_pair_it
     return stream_experts(c, fmt, pairs, act, ypair, stream);
 }
 
+extern "C" int moexb_ctx_set_fused_decode(moexb_ctx* c, int on) {
+    REQUIRE(c, "ctx_set_fused_decode: null context");
+    c->fused_decode = on != 0;
+    return MOEXB_OK;
+}
+
 extern "C" int moexb_ctx_set_pairs_per_pass(moexb_ctx* c, int pairs) {
     REQUIRE(c && (pairs == 4 || pairs == 8), "ctx_set_pairs_per_pass: 4 or 8");
     c->pairs_per_pass = pairs;
@@ -912,6 +920,11 @@ struct moexb_stack {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     cudaStream_t cap = nullptr;
+    // one-token residual stacks: a single cooperative launch instead of a graph
+    bool fused = false;
+    DecodeLayer* dlayers = nullptr;   // device
+    unsigned* dsync = nullptr;        // device: barrier counter, abort flag
+    int fmt = 0, router_dtype = 0, n_routed = 0;
 };
 
 int moexb_stack_destroy(moexb_stack* s) {
@@ -919,10 +932,43 @@ int moexb_stack_destroy(moexb_stack* s) {
     if (s->exec) cudaGraphExecDestroy(s->exec);
     if (s->graph) cudaGraphDestroy(s->graph);
     if (s->cap) cudaStreamDestroy(s->cap);
-    cudaFree(s->x_in); cudaFree(s->buf[0]); cudaFree(s->buf[1]);
+    cudaFree(s->x_in); cudaFree(s->buf[0]); cudaFree(s->buf[1]); cudaFree(s->dlayers); cudaFree(s->dsync);
     delete s;
     return MOEXB_OK;
 }
+
+}  // extern "C"
+template <int FMT, typename WT, bool XBF>
+static int decode_stack_launch(moexb_stack* s, void* stream) {
+    moexb_ctx* c = s->ctx;
+    constexpr int SMEM = ds_smem_bytes<FMT>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    static int per_sm = 0;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(decode_stack_k<FMT, WT, XBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (attr_err == cudaSuccess) attr_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_k<FMT, WT, XBF>, DS_THREADS, SMEM);
+    });
+    if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "decode stack kernel: %s", cudaGetErrorString(attr_err));
+    if (per_sm < 1) return fail(MOEXB_ERR_UNSUPPORTED, "decode stack kernel does not fit an SM");
+    CUDA_TRY(cudaMemsetAsync(s->dsync, 0, 2 * sizeof(unsigned), S(stream)));
+    DecodeStackArgs a{s->dlayers, s->n_layers, s->n_routed, s->K, s->x_in, s->buf[0], c->logits, c->act_split, c->ypair, nullptr, nullptr, s->dsync, c->err};
+    void* args[] = {&a};
+    // cooperative: every CTA is resident, which the grid barrier inside relies on
+    CUDA_TRY(cudaLaunchCooperativeKernel((void*)decode_stack_k<FMT, WT, XBF>, dim3(c->sms), dim3(DS_THREADS), args, SMEM, S(stream)));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return MOEXB_OK;
+}
+static int decode_stack_run(moexb_stack* s, void* stream) {
+    auto by_x = [&]<int FMT, typename WT>() {
+        return s->x_dtype == MOEXB_BF16 ? decode_stack_launch<FMT, WT, true>(s, stream) : decode_stack_launch<FMT, WT, false>(s, stream);
+    };
+    auto by_w = [&]<int FMT>() {
+        return s->router_dtype == MOEXB_F32 ? by_x.template operator()<FMT, float>() : by_x.template operator()<FMT, __half>();
+    };
+    return s->fmt == FMT_SYM_F16 ? by_w.template operator()<FMT_SYM_F16>() : by_w.template operator()<FMT_SYM_F32>();
+}
+extern "C" {
 
 int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, int residual, moexb_stack** out) {
     REQUIRE(c && layers && out, "stack_create: null pointer");
@@ -943,6 +989,23 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     if (e == cudaSuccess) e = cudaMalloc((void**)&s->buf[1], n * 4);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->cap, cudaStreamNonBlocking);
     if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_NOMEM, "stack_create: %s", cudaGetErrorString(e)); }
+    // one token through residual blocks of resident symmetric-format experts: one cooperative launch for the whole stack
+    bool fused = c->fused_decode && T == 1 && residual && K <= DS_MAXK && layers[0]->layout == MOEXB_LAYOUT_TILED && layers[0]->fmt != FMT_ZP;
+    for (int l = 0; l < n_layers && fused; l++)
+        fused = layers[l]->n_local == layers[l]->n_routed && layers[l]->n_routed == layers[0]->n_routed && layers[l]->n_routed <= 256 &&
+                layers[l]->n_routed % 32 == 0 && layers[l]->router_dtype == layers[0]->router_dtype;
+    if (fused) {
+        std::vector<DecodeLayer> h(n_layers);
+        for (int l = 0; l < n_layers; l++) h[l] = {layers[l]->router, layers[l]->slot_table};
+        e = cudaMalloc((void**)&s->dlayers, n_layers * sizeof(DecodeLayer));
+        if (e == cudaSuccess) e = cudaMalloc((void**)&s->dsync, 2 * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemcpy(s->dlayers, h.data(), n_layers * sizeof(DecodeLayer), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_NOMEM, "stack_create: %s", cudaGetErrorString(e)); }
+        s->fused = true; s->fmt = layers[0]->fmt; s->router_dtype = layers[0]->router_dtype; s->n_routed = layers[0]->n_routed;
+        s->kernels = 1; s->result = s->buf[0];
+        *out = s;
+        return MOEXB_OK;
+    }
     const long long before = g_launches.load();
     e = cudaStreamBeginCapture(s->cap, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "stack_create: begin capture: %s", cudaGetErrorString(e)); }
@@ -971,8 +1034,11 @@ int moexb_stack_run(moexb_stack* s, const void* X, float* out, void* stream) {
     REQUIRE(s && X && out, "stack_run: null pointer");
     const size_t n = (size_t)s->T * EH;
     CUDA_TRY(cudaMemcpyAsync(s->x_in, X, n * (s->x_dtype == MOEXB_BF16 ? 2 : 4), cudaMemcpyDeviceToDevice, S(stream)));
-    CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
-    g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    if (s->fused) { const int rc = decode_stack_run(s, stream); if (rc != MOEXB_OK) return rc; }
+    else {
+        CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
+        g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    }
     CUDA_TRY(cudaMemcpyAsync(out, s->result, n * 4, cudaMemcpyDeviceToDevice, S(stream)));
     return MOEXB_OK;
 }
@@ -981,8 +1047,11 @@ int moexb_stack_run_host(moexb_stack* s, const void* X_host, float* out_host, vo
     REQUIRE(s && X_host && out_host, "stack_run_host: null pointer");
     const size_t n = (size_t)s->T * EH;
     CUDA_TRY(cudaMemcpyAsync(s->x_in, X_host, n * (s->x_dtype == MOEXB_BF16 ? 2 : 4), cudaMemcpyHostToDevice, S(stream)));
-    CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
-    g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    if (s->fused) { const int rc = decode_stack_run(s, stream); if (rc != MOEXB_OK) return rc; }
+    else {
+        CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
+        g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
+    }
     CUDA_TRY(cudaMemcpyAsync(out_host, s->result, n * 4, cudaMemcpyDeviceToHost, S(stream)));
     CUDA_TRY(cudaStreamSynchronize(S(stream)));
     return MOEXB_OK;

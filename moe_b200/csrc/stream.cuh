@@ -353,8 +353,9 @@ __global__ void split_rows_k(const float* __restrict__ x, uint16_t* __restrict__
 // One row of D = 2048 floats held 8 per thread (thread i: elements 4i..4i+3 and 1024+4i..1024+4i+3): the sum of squares
 // in the pinned order of rmsnorm_rows_k, then the normalised row as fp32 (for the router) and as bf16 hi + lo in the
 // permuted order (for the streaming kernels).
+// lo_off: distance (elements) from the hi row to the lo row of the split.
 template <bool F16>
-__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, uint16_t* __restrict__ xs, float eps) {
+__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, uint16_t* __restrict__ xs, float eps, int lo_off = EH) {
     __shared__ float part[8];
     float ss = 0.f;
 #pragma unroll
@@ -377,7 +378,7 @@ __device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __res
             uint16_t hi, lo;
             split_hi_lo<F16>(f[i], hi, lo);
             const int pos = split_pos(k0 + i);
-            xs[pos] = hi; xs[EH + pos] = lo;
+            xs[pos] = hi; xs[lo_off + pos] = lo;
         }
     }
 }

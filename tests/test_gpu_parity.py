@@ -530,3 +530,47 @@ def test_prefill_chunk_of_2048_tokens_both_kernel_families_agree():
     assert np.array_equal(idx.cpu().numpy()[sample], ri)
     check_ffn(out_tc[sample], ref, m.FMT_SYM_F16, "2048-token chunk, sampled tokens against the oracle")
     L.close(); c.close()
+
+
+@pytest.mark.parametrize("E,fmt,router", [(256, m.FMT_SYM_F16, np.float32), (64, m.FMT_SYM_F32, np.float16)])
+def test_one_token_stack_as_one_cooperative_launch(E, fmt, router):
+    """A one-token stack of residual blocks runs as a single cooperative kernel (grid barriers inside). Against the graph of
+    per-layer kernels on the same layers: the result agrees within the parity bars (the two add the four K slices of a
+    gate/up row in a different order), twice in a row (the barrier counter is reset per launch), for f32 and bf16 inputs
+    and through host buffers; and against the oracle chain."""
+    rng = np.random.default_rng(11)
+    NL, T = 5, 1
+    c = m.Context(0, max_tokens=4, max_experts=E, top_k=8)
+    layers, hosts, Ws = [], [], []
+    for l in range(NL):
+        L = m.Layer(c, fmt, E, router_dtype=m.F16 if router == np.float16 else m.F32)
+        L.fill_synth(5, l)
+        W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(router)
+        L.set_router(W)
+        layers.append(L); Ws.append(W); hosts.append([m.synth_expert_host(fmt, 5, l, e) for e in range(E + 1)])
+    x0 = rng.standard_normal((T, 2048)).astype(np.float32)
+    x_ref = x0.copy()
+    for l in range(NL):
+        moe, _, _, _ = o.layer_forward(fmt, hosts[l], Ws[l], o.rmsnorm(x_ref), 8)
+        x_ref = x_ref + moe
+    for dt, xin in ((m.F32, torch.from_numpy(x0)), (m.BF16, torch.from_numpy(x0).to(torch.bfloat16))):
+        c.set_fused_decode(False)
+        graph = m.Stack(c, layers, T, 8, dt)
+        y_graph = graph.run(xin.to(DEV)).cpu().numpy().copy()
+        graph.close()
+        c.set_fused_decode(True)
+        fused = m.Stack(c, layers, T, 8, dt)
+        assert fused.kernel_count == 1
+        y1 = fused.run(xin.to(DEV)).cpu().numpy().copy()
+        y2 = fused.run(xin.to(DEV)).cpu().numpy().copy()
+        out_h = torch.empty(T, 2048).pin_memory()
+        fused.run_host(xin.pin_memory(), out_h)
+        assert c.status() == 0
+        assert np.array_equal(y1, y2) and np.array_equal(y1, out_h.numpy())
+        check_ffn(y1, y_graph, fmt, "cooperative launch against the graph of kernels")
+        if dt == m.F32:
+            check_ffn(y1, x_ref, fmt, "cooperative launch against the oracle chain")
+        fused.close()
+    for L in layers:
+        L.close()
+    c.close()
