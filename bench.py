@@ -340,6 +340,14 @@ def main():
         "clocks": clocks,
         "per_layer": {"us": ms_step * 1e3 / NL, "tokens_per_s": tokens_total / (ms_step * 1e-3 / NL)},
     }
+    if T == 1 and world == 1 and fmt != m.FMT_ZP and stack.kernel_count == 1:
+        # the one-token stack is ONE cooperative kernel: its roofline is the whole step
+        r = line["roofline"]
+        step_bytes = layer_bytes * NL
+        r.update({"kernel": "decode_stack_k (all layers of the stack in one cooperative launch)", "achieved": step_bytes / (ms_step * 1e-3) / 1e9,
+                  "algorithmic_bytes_per_launch": step_bytes, "us_per_launch": ms_step * 1e3, "traffic": None,
+                  "note": "kernel_us_per_launch below are the per-layer kernels of the multi-launch path, timed separately"})
+        r["frac"] = r["achieved"] / r["peak"]
     if T >= 256:
         # the prefill chunk is a dense contraction: gate/up grouped GEMM against the measured cuBLAS bf16 burst figure
         npairs = int(sum(int(((idx[l] >= first) & (idx[l] < first + count)).sum()) for l in range(NL)) / NL) + (sh1 - sh0)

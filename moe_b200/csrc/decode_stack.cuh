@@ -5,8 +5,8 @@
 // cudaLaunchCooperativeKernel) walks the layers, and what every CTA needs of the token (the residual row, its rmsnorm, the
 // fp16 hi + lo split, the selected experts) lives in its own shared memory, recomputed redundantly by every CTA instead of
 // being passed through global memory. Per layer:
-//   P1  router logits: CTA b computes rows b, b + grid, .. of W . xn (one warp per row, the pinned summation order of
-//       gemv_rows_k) -> logits[E + 1] in global memory.                                        -- grid barrier --
+//   P1  router logits: CTA b computes rows b and b + grid of W . xn (one warp per row, the pinned summation order of
+//       gemv_rows_k; the rows were copied into shared memory during the layer before) -> logits[E + 1] in global memory.                                        -- grid barrier --
 //   P2  every CTA: top-K of the logits (warp 0, topk_token), the K + 1 expert blobs and weights into shared memory.
 //   P3  gate/up: (expert, row tile of 8 gate + 8 up rows) units, two per CTA pass, the four K slices of a unit on four
 //       warps (one 4.3 KB bulk copy each, issued as soon as P2 is done), partial sums added in shared memory, SiLU * up
@@ -54,12 +54,13 @@ constexpr int DS_D = 3;                       // slice buffers per warp
 constexpr int DS_XCOL = EH * 2 + 64;          // stride between the hi and lo columns of the token (bytes)
 constexpr int DS_ACOL = EI * 2 + 64;          // the same for an expert's act row
 constexpr int DS_MAXK = 8;
+constexpr int DS_MAXLAYERS = 128;
 constexpr int DS_POLL_LIMIT = 1 << 22;
 constexpr int DS_ERR_BARRIER = 5, DS_ERR_COPY = 6;
 
 template <int FMT> constexpr int ds_smem_bytes() {
     return DS_WARPS * DS_D * tl_slice_bytes<FMT>() + 2 * DS_XCOL + DS_WARPS * 2 * DS_ACOL + 2 * EH * 4 /* xres, xn */ +
-           2 * 4 * 16 * 2 * 4 /* partial sums */ + DS_WARPS * DS_D * 8 + 256;
+           2 * 4 * 16 * 2 * 4 /* partial sums */ + DS_WARPS * DS_D * 8 + 2 * EH * 4 /* router rows */ + (256 + 1) * 8 + 8 /* slot table */ + 256;
 }
 
 // 8 groups of one slice against the lane's two activation columns (bp: the lane's column pointer, already offset to the
@@ -105,15 +106,19 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     float* xn = xres + EH;                                              // [H] its rmsnorm
     float* part = xn + EH;                                              // [2 units][4 k slices][16 rows][2]
     uint64_t* bars = reinterpret_cast<uint64_t*>(part + 2 * 4 * 16 * 2);    // [warp][DS_D]
+    uint8_t* rrow = reinterpret_cast<uint8_t*>(bars + DS_WARPS * DS_D);     // this CTA's (at most two) router rows of the coming layer
+    const uint8_t** table = reinterpret_cast<const uint8_t**>(rrow + 2 * EH * 4);   // the coming layer's E + 1 blob pointers
     __shared__ int s_idx[DS_MAXK];
     __shared__ float s_w[DS_MAXK];
     __shared__ const uint8_t* s_slot[DS_MAXK + 1];
     __shared__ float s_wt[DS_MAXK + 1];
     __shared__ int s_abort;
+    __shared__ DecodeLayer s_layers[DS_MAXLAYERS];   // the layer descriptors: no global round trip when a layer is staged
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int grid = gridDim.x, b = blockIdx.x, E = a.E, K = a.K, O = E + 1;
     if (tid < DS_WARPS * DS_D) mbar_init(smem_u32(bars + tid), 1);
     if (tid == 0) { s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    for (int i = tid; i < a.n_layers; i += DS_THREADS) s_layers[i] = a.layers[i];
     // the token: residual row, rmsnorm, split (every CTA its own copy)
     float v[8];
     {
@@ -139,6 +144,22 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
     __syncthreads();
 
+    // The router rows this CTA owns and the slot table of layer l: requested (cp.async) while the layer before still streams
+    // its experts, so that P1 and P2 find them in shared memory.
+    auto stage_layer = [&](int l) {
+        const DecodeLayer Ln = s_layers[l];
+        for (int w = 0; w < 2; w++) {
+            const int r = b + w * grid;
+            if (r < O) {
+                const uint8_t* src = static_cast<const uint8_t*>(Ln.router) + (size_t)r * EH * sizeof(WT);
+                for (int i = tid * 16; i < EH * (int)sizeof(WT); i += DS_THREADS * 16) cp_async16(smem_u32(rrow + w * EH * sizeof(WT) + i), src + i);
+            }
+        }
+        for (int i = tid; i < O; i += DS_THREADS) cp_async8(smem_u32(table + i), Ln.slot_table + i);
+    };
+    stage_layer(0);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
     unsigned barriers = 0;   // grid barriers passed
     // all CTAs have finished the phase before this call; false: time-out or abort
     auto grid_barrier = [&]() -> bool {
@@ -203,18 +224,22 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     bool ok = true;
 
     for (int l = 0; l < a.n_layers && ok; l++) {
-        const DecodeLayer L = a.layers[l];
-        // ---- P1: router logits of rows b, b + grid, .. (one warp each) ----
-        for (int r = b + warp * grid; r < O; r += DS_WARPS * grid) {
-            const WT* wr = static_cast<const WT*>(L.router) + (size_t)r * EH;
-            float4 w[16];
-#pragma unroll
-            for (int u = 0; u < 16; u++) w[u] = ld_w4(wr, (size_t)128 * u + 4 * lane);
+            // ---- P1: router logits of rows b, b + grid, .. (one warp each) ----
+        if (warp < 2 && b + warp * grid < O) {
+            const int r = b + warp * grid;
+            const WT* wr = reinterpret_cast<const WT*>(rrow + warp * EH * sizeof(WT));
             float acc = 0.f;
 #pragma unroll
             for (int u = 0; u < 16; u++) {
+                float4 w;
+                if constexpr (sizeof(WT) == 4) w = *reinterpret_cast<const float4*>(wr + 128 * u + 4 * lane);
+                else {
+                    const uint2 h = *reinterpret_cast<const uint2*>(wr + 128 * u + 4 * lane);
+                    const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), q = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+                    w = make_float4(p.x, p.y, q.x, q.y);
+                }
                 const float4 x = *reinterpret_cast<const float4*>(xn + 128 * u + 4 * lane);
-                acc = fmaf(w[u].x, x.x, acc); acc = fmaf(w[u].y, x.y, acc); acc = fmaf(w[u].z, x.z, acc); acc = fmaf(w[u].w, x.w, acc);
+                acc = fmaf(w.x, x.x, acc); acc = fmaf(w.y, x.y, acc); acc = fmaf(w.z, x.z, acc); acc = fmaf(w.w, x.w, acc);
             }
             acc = warp_sum(acc);
             if (lane == 0) __stcg(a.logits + r, acc);
@@ -222,7 +247,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         if (!(ok = grid_barrier())) break;
         // ---- P2: selection (every CTA), blob pointers and weights of the K + 1 experts ----
         if (warp == 0) {
-            const TopkOut o{s_idx, s_w, L.slot_table, s_slot, s_wt, nullptr, nullptr, nullptr};
+            const TopkOut o{s_idx, s_w, table, s_slot, s_wt, nullptr, nullptr, nullptr};
             topk_token<8, true>(a.logits, 0, E, K, 1, lane, o);
             if (b == 0 && lane < K) {
                 if (a.idx_out) a.idx_out[(size_t)l * K + lane] = s_idx[lane];
@@ -237,13 +262,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             for (; issued < nS && issued < DS_D; issued++) issue(issued);
         }
         issued = __shfl_sync(0xffffffffu, issued, 0);
-        if (l + 1 < a.n_layers && warp < 2) {   // the next layer's router rows of this CTA: into L2 while the experts stream
-            const int r = b + warp * grid;
-            if (r < O) {
-                const char* p = static_cast<const char*>(a.layers[l + 1].router) + (size_t)r * EH * sizeof(WT);
-                for (int i = lane * 128; i < EH * (int)sizeof(WT); i += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
-            }
-        }
+        if (l + 1 < a.n_layers) stage_layer(l + 1);   // lands while the experts stream; waited for at the end of the layer
         for (int pass = 0; pass < n3 && ok; pass++) {
             const int u = 2 * (pass * grid + b) + (warp >> 2);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -326,6 +345,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         }
         __syncthreads();   // part[] of norm_split_row and xn / xcol are free: every warp is past P1 and P3 of this layer
         if (l + 1 < a.n_layers) norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
+        asm volatile("cp.async.wait_all;" ::: "memory");   // the next layer's router rows and slot table
         __syncthreads();
     }
     // leave: no copy may still be in flight into this CTA's shared memory
