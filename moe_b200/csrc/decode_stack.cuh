@@ -7,15 +7,18 @@
 // being passed through global memory. Per layer:
 //   P1  router logits: CTA b computes rows b and b + grid of W . xn (one warp per row, the pinned summation order of
 //       gemv_rows_k; the rows were copied into shared memory during the layer before) -> logits[E + 1] in global memory.                                        -- grid barrier --
-//   P2  every CTA: top-K of the logits (warp 0, topk_token), the K + 1 expert blobs and weights into shared memory.
+//   P2  every CTA: which K experts - thread i ranks logit i among all of them (how many are larger, ties to the lower
+//       index; 256 threads, no sequential rounds) and the K with rank < K are the selection, in rank order. The softmax
+//       weights are off this path: the last CTA takes no expert work and instead runs topk_token on the same logits
+//       (the same experts by construction) and publishes the K + 1 weights, which are first needed in P5.
 //   P3  gate/up: (expert, row tile of 8 gate + 8 up rows) units, two per CTA pass, the four K slices of a unit on four
 //       warps (one 4.3 KB bulk copy each, issued as soon as P2 is done), partial sums added in shared memory, SiLU * up
 //       -> act[K + 1][2][I] (fp16 hi, lo) in global memory. The warps' down slices (P4) are requested at the same time.
 //                                                                                              -- grid barrier --
 //   P4  down: (expert, row tile of 16 rows) units, one slice per warp; the expert's act row comes from L2
 //       -> ypair[K + 1][H] in global memory.                                                   -- grid barrier --
-//   P5  every CTA: x += sum of the K + 1 rows in rank order (the order of reduce_residual_norm_k), rmsnorm and split for
-//       the next layer, all in shared memory.
+//   P5  every CTA: x += sum of the K + 1 weighted rows in rank order (the products and the order of the down kernel +
+//       reduce_residual_norm_k), rmsnorm and split for the next layer, all in shared memory.
 // The grid barrier is a monotonic counter in global memory (zeroed by the host before the launch): one thread per CTA adds
 // 1 and polls until the counter reaches (barriers so far) x grid. Every poll loop is bounded; a time-out sets the error
 // word and an abort flag that all other loops watch, and the CTAs leave after waiting (bounded) for their copies in flight.
@@ -42,7 +45,8 @@ struct DecodeStackArgs {
     float* x_out;            // [H]
     float* logits;           // [E + 1]
     uint16_t* act;           // [K + 1][2][I] fp16 hi, lo in split_pos order
-    float* ypair;            // [K + 1][H]
+    float* ypair;            // [K + 1][H], not yet multiplied by the routing weights
+    float* wts;              // [K + 1] routing weights of the selected experts, then the shared expert's gate
     int* idx_out;            // optional [n_layers][K]
     float* w_out;            // optional [n_layers][K]
     unsigned* sync;          // [0] barrier counter, [1] abort flag; zero before the launch
@@ -113,6 +117,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     __shared__ const uint8_t* s_slot[DS_MAXK + 1];
     __shared__ float s_wt[DS_MAXK + 1];
     __shared__ int s_abort;
+    __shared__ __align__(16) unsigned s_keys[DS_THREADS];   // the logits as ordered integer keys (0 beyond E)
+    __shared__ int s_idx2[DS_MAXK];
+    __shared__ const uint8_t* s_slot2[DS_MAXK + 1];
     __shared__ DecodeLayer s_layers[DS_MAXLAYERS];   // the layer descriptors: no global round trip when a layer is staged
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int grid = gridDim.x, b = blockIdx.x, E = a.E, K = a.K, O = E + 1;
@@ -165,8 +172,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     auto grid_barrier = [&]() -> bool {
         __syncthreads();
         if (tid == 0) {
-            __threadfence();
-            atomicAdd(a.sync, 1u);
+            // release: the CTA's writes (ordered before this by the barrier above) are visible to whoever sees the count
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.sync) : "memory");
             const unsigned target = (barriers + 1) * (unsigned)grid;
             int i = 0;
             for (; i < DS_POLL_LIMIT; i++) {
@@ -188,19 +195,24 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
 
     // slices of this warp per layer: n3 gate/up passes (unit = 2 * (pass * grid + b) + (warp >> 2), K slice warp & 3), then n4
     // down passes (unit = (pass * grid + b) * DS_WARPS + warp)
+    // The last CTA computes the routing weights instead of expert work (a one-CTA grid does both, weights first).
+    const bool weights_cta = b == grid - 1;
+    const int wgrid = grid > 1 ? grid - 1 : 1;
+    const bool worker = grid == 1 || !weights_cta;
     const int U3 = (K + 1) * 64, U4 = (K + 1) * 128;
-    const int n3 = (U3 + 2 * grid - 1) / (2 * grid), n4 = (U4 + DS_WARPS * grid - 1) / (DS_WARPS * grid), nS = n3 + n4;
+    const int n3 = (U3 + 2 * wgrid - 1) / (2 * wgrid), n4 = (U4 + DS_WARPS * wgrid - 1) / (DS_WARPS * wgrid), nS = n3 + n4;
     uint8_t* myring = ring + warp * DS_D * SB;
     uint64_t* mybars = bars + warp * DS_D;
     long long S0 = 0;        // slices (list entries) of this warp in earlier layers
     // source of list entry s of this layer, or null when the entry is empty
     auto slice_src = [&](int s) -> const uint8_t* {
+        if (!worker) return nullptr;
         if (s < n3) {
-            const int u = 2 * (s * grid + b) + (warp >> 2);
+            const int u = 2 * (s * wgrid + b) + (warp >> 2);
             if (u >= U3) return nullptr;
             return s_slot[u >> 6] + (size_t)((u & 63) * 4 + (warp & 3)) * SB;
         }
-        const int u = ((s - n3) * grid + b) * DS_WARPS + warp;
+        const int u = ((s - n3) * wgrid + b) * DS_WARPS + warp;
         if (u >= U4) return nullptr;
         return s_slot[u >> 7] + (size_t)(256 + (u & 127)) * SB;
     };
@@ -245,16 +257,50 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             if (lane == 0) __stcg(a.logits + r, acc);
         }
         if (!(ok = grid_barrier())) break;
-        // ---- P2: selection (every CTA), blob pointers and weights of the K + 1 experts ----
-        if (warp == 0) {
-            const TopkOut o{s_idx, s_w, table, s_slot, s_wt, nullptr, nullptr, nullptr};
-            topk_token<8, true>(a.logits, 0, E, K, 1, lane, o);
-            if (b == 0 && lane < K) {
-                if (a.idx_out) a.idx_out[(size_t)l * K + lane] = s_idx[lane];
-                if (a.w_out) a.w_out[(size_t)l * K + lane] = s_w[lane];
+        // ---- P2: selection (every CTA): the rank of logit i = how many logits come before it (larger, or equal with a lower
+        // index - the order of topk_token's rounds); warp w compares with >= against the blocks of 32 below it, with > against
+        // those above, and index by index inside its own ----
+        {
+            unsigned key = 0u;
+            if (tid < E) { const float x = __ldcg(a.logits + tid); key = f2key(x != x ? -INFINITY : x); }
+            s_keys[tid] = key;
+            __syncthreads();
+            if (tid < E) {
+                const uint4* kv = reinterpret_cast<const uint4*>(s_keys);
+                int cnt = 0;
+                for (int blk = 0; blk < DS_THREADS / 32; blk++) {
+                    if (blk == warp) continue;
+                    const bool below = blk < warp;
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const uint4 k4 = kv[blk * 8 + q];
+                        if (below) cnt += (k4.x >= key) + (k4.y >= key) + (k4.z >= key) + (k4.w >= key);
+                        else cnt += (k4.x > key) + (k4.y > key) + (k4.z > key) + (k4.w > key);
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const uint4 k4 = kv[warp * 8 + q];
+                    const int j = 4 * q;   // lanes j .. j + 3 of this warp
+                    cnt += (k4.x > key || (k4.x == key && j < lane)) + (k4.y > key || (k4.y == key && j + 1 < lane)) +
+                           (k4.z > key || (k4.z == key && j + 2 < lane)) + (k4.w > key || (k4.w == key && j + 3 < lane));
+                }
+                if (cnt < K) {
+                    s_idx[cnt] = tid; s_slot[cnt] = table[tid];
+                    if (b == 0 && a.idx_out) a.idx_out[(size_t)l * K + cnt] = tid;
+                }
             }
+            if (tid == 0) s_slot[K] = table[E];
+            __syncthreads();
         }
-        __syncthreads();
+        if (weights_cta && warp == 0) {
+            // the softmax weights, off the other CTAs' path: first read after two more grid barriers
+            const TopkOut o{s_idx2, s_w, table, s_slot2, s_wt, nullptr, nullptr, nullptr};
+            topk_token<8, true>(a.logits, 0, E, K, 1, lane, o);
+            __syncwarp();
+            if (lane <= K) __stcg(a.wts + lane, s_wt[lane]);
+            if (lane < K && a.w_out) a.w_out[(size_t)l * K + lane] = s_w[lane];
+        }
         // ---- P3: gate/up. All copies this layer needs that fit the ring are requested now, the down slices included ----
         issued = 0; consumed = 0;
         if (lane == 0) {
@@ -264,7 +310,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         issued = __shfl_sync(0xffffffffu, issued, 0);
         if (l + 1 < a.n_layers) stage_layer(l + 1);   // lands while the experts stream; waited for at the end of the layer
         for (int pass = 0; pass < n3 && ok; pass++) {
-            const int u = 2 * (pass * grid + b) + (warp >> 2);
+            const int u = worker ? 2 * (pass * wgrid + b) + (warp >> 2) : U3;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (u < U3) {
                 if (!wait_slice(pass)) { ok = false; }
@@ -295,8 +341,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         }
         if (!ok || !(ok = grid_barrier())) break;
         // ---- P4: down. The slice is (mostly) in shared memory already; the expert's act row comes from L2 ----
+        // (the routing weights were published before the barrier just passed: one copy per CTA, read in P5)
+        if (!weights_cta && tid <= K) s_wt[tid] = __ldcg(a.wts + tid);
         for (int pass = 0; pass < n4 && ok; pass++) {
-            const int u = (pass * grid + b) * DS_WARPS + warp;
+            const int u = worker ? (pass * wgrid + b) * DS_WARPS + warp : U4;
             if (u < U4) {
                 const int k = u >> 7, wt = u & 127;
                 uint8_t* ac = acol + warp * 2 * DS_ACOL;
@@ -312,10 +360,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
                 else {
                     ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc);
                     if (t == 0) {
-                        const float w = s_wt[k];
                         const int d = 16 * wt + g;
-                        __stcg(a.ypair + (size_t)k * EH + d, w * (acc[0] + acc[1]));
-                        __stcg(a.ypair + (size_t)k * EH + d + 8, w * (acc[2] + acc[3]));
+                        __stcg(a.ypair + (size_t)k * EH + d, acc[0] + acc[1]);
+                        __stcg(a.ypair + (size_t)k * EH + d + 8, acc[2] + acc[3]);
                     }
                 }
             }
@@ -331,13 +378,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         for (int h = 0; h < 2; h++) {
             const int k0 = 1024 * h + 4 * tid;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int rb = 0; rb <= K; rb += 3) {
-                float4 y[3];
+            float4 y[DS_MAXK + 1];   // all rows (and weights) in flight at once; weighted and added in rank order
+            float w[DS_MAXK + 1];
 #pragma unroll
-                for (int u = 0; u < 3; u++) if (rb + u <= K) y[u] = __ldcg(reinterpret_cast<const float4*>(a.ypair + (size_t)(rb + u) * EH + k0));
+            for (int r = 0; r <= DS_MAXK; r++)
+                if (r <= K) { y[r] = __ldcg(reinterpret_cast<const float4*>(a.ypair + (size_t)r * EH + k0)); w[r] = s_wt[r]; }
 #pragma unroll
-                for (int u = 0; u < 3; u++) if (rb + u <= K) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
-            }
+            for (int r = 0; r <= DS_MAXK; r++)
+                if (r <= K) { acc.x += __fmul_rn(w[r], y[r].x); acc.y += __fmul_rn(w[r], y[r].y); acc.z += __fmul_rn(w[r], y[r].z); acc.w += __fmul_rn(w[r], y[r].w); }
             const float4 x = *reinterpret_cast<const float4*>(xres + k0);
             acc.x = x.x + acc.x; acc.y = x.y + acc.y; acc.z = x.z + acc.z; acc.w = x.w + acc.w;
             *reinterpret_cast<float4*>(xres + k0) = acc;

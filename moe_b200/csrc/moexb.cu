@@ -952,7 +952,7 @@ static int decode_stack_launch(moexb_stack* s, void* stream) {
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "decode stack kernel: %s", cudaGetErrorString(attr_err));
     if (per_sm < 1) return fail(MOEXB_ERR_UNSUPPORTED, "decode stack kernel does not fit an SM");
     CUDA_TRY(cudaMemsetAsync(s->dsync, 0, 2 * sizeof(unsigned), S(stream)));
-    DecodeStackArgs a{s->dlayers, s->n_layers, s->n_routed, s->K, s->x_in, s->buf[0], c->logits, c->act_split, c->ypair, nullptr, nullptr, s->dsync, c->err};
+    DecodeStackArgs a{s->dlayers, s->n_layers, s->n_routed, s->K, s->x_in, s->buf[0], c->logits, c->act_split, c->ypair, c->wts, nullptr, nullptr, s->dsync, c->err};
     void* args[] = {&a};
     // cooperative: every CTA is resident, which the grid barrier inside relies on
     CUDA_TRY(cudaLaunchCooperativeKernel((void*)decode_stack_k<FMT, WT, XBF>, dim3(c->sms), dim3(DS_THREADS), args, SMEM, S(stream)));
