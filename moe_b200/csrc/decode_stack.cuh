@@ -15,10 +15,11 @@
 //       warps (one 4.3 KB bulk copy each, issued as soon as P2 is done), partial sums added in shared memory, SiLU * up
 //       -> act[K + 1][2][I] (fp16 hi, lo) in global memory. The warps' down slices (P4) are requested at the same time.
 //                                                                                              -- grid barrier --
-//   P4  down: (expert, row tile of 16 rows) units, one slice per warp; the expert's act row comes from L2
-//       -> ypair[K + 1][H] in global memory.                                                   -- grid barrier --
-//   P5  every CTA: x += sum of the K + 1 weighted rows in rank order (the products and the order of the down kernel +
-//       reduce_residual_norm_k), rmsnorm and split for the next layer, all in shared memory.
+//   P4  down: a CTA takes a 16-row tile for all K + 1 experts (warp k the routed expert k; the shared expert's slice one
+//       input group per warp), the experts' act rows come from L2; the tile's rows of x += sum of the weighted rows in
+//       rank order (the products and the order of the down kernel + reduce_residual_norm_k) -> xnew[H] in global memory.
+//                                                                                              -- grid barrier --
+//   P5  every CTA: the new row from L2 (8 KB), rmsnorm and split for the next layer, all in shared memory.
 // The grid barrier is a monotonic counter in global memory (zeroed by the host before the launch): one thread per CTA adds
 // 1 and polls until the counter reaches (barriers so far) x grid. Every poll loop is bounded; a time-out sets the error
 // word and an abort flag that all other loops watch, and the CTAs leave after waiting (bounded) for their copies in flight.
@@ -45,7 +46,7 @@ struct DecodeStackArgs {
     float* x_out;            // [H]
     float* logits;           // [E + 1]
     uint16_t* act;           // [K + 1][2][I] fp16 hi, lo in split_pos order
-    float* ypair;            // [K + 1][H], not yet multiplied by the routing weights
+    float* ypair;            // [H] the new residual row, written tile by tile in P4
     float* wts;              // [K + 1] routing weights of the selected experts, then the shared expert's gate
     int* idx_out;            // optional [n_layers][K]
     float* w_out;            // optional [n_layers][K]
@@ -64,17 +65,18 @@ constexpr int DS_ERR_BARRIER = 5, DS_ERR_COPY = 6;
 
 template <int FMT> constexpr int ds_smem_bytes() {
     return DS_WARPS * DS_D * tl_slice_bytes<FMT>() + 2 * DS_XCOL + DS_WARPS * 2 * DS_ACOL + 2 * EH * 4 /* xres, xn */ +
-           2 * 4 * 16 * 2 * 4 /* partial sums */ + DS_WARPS * DS_D * 8 + 2 * EH * 4 /* router rows */ + (256 + 1) * 8 + 8 /* slot table */ + 256;
+           2 * 4 * 16 * 2 * 4 /* partial sums */ + DS_WARPS * DS_D * 8 + 2 * EH * 4 /* router rows */ + (256 + 1) * 8 + 8 /* slot table */ +
+           tl_slice_bytes<FMT>() + 2 * DS_ACOL /* the shared expert's down slice and act row */ + 2 * DS_WARPS * 16 * 4 /* down results */ + 256;
 }
 
 // 8 groups of one slice against the lane's two activation columns (bp: the lane's column pointer, already offset to the
 // slice's first input); acc[0..1] += row g, acc[2..3] += row g + 8 (columns 2t, 2t + 1).
 template <int FMT>
-__device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4]) {
+__device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4], int G0 = 0, int G1 = 8) {
     constexpr int GB = tl_group_bytes<FMT>();
     const int g = lane >> 2;
 #pragma unroll 4
-    for (int G = 0; G < 8; G++) {
+    for (int G = G0; G < G1; G++) {
         const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
         const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
         uint32_t Pa[2][4], Pb[2][4];
@@ -112,6 +114,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     uint64_t* bars = reinterpret_cast<uint64_t*>(part + 2 * 4 * 16 * 2);    // [warp][DS_D]
     uint8_t* rrow = reinterpret_cast<uint8_t*>(bars + DS_WARPS * DS_D);     // this CTA's (at most two) router rows of the coming layer
     const uint8_t** table = reinterpret_cast<const uint8_t**>(rrow + 2 * EH * 4);   // the coming layer's E + 1 blob pointers
+    uint8_t* shbuf = reinterpret_cast<uint8_t*>(table) + (256 + 1) * 8 + 8;         // the shared expert's down slice of this CTA's row tile
+    uint8_t* shcol = shbuf + SB;                                                    // the shared expert's act row (hi, lo)
+    float* yrt = reinterpret_cast<float*>(shcol + 2 * DS_ACOL);                     // [warp][16] a routed expert's 16 down rows
+    float* ysh = yrt + DS_WARPS * 16;                                               // [warp][16] the shared expert's, one input group per warp
+    __shared__ __align__(8) uint64_t shbar;
     __shared__ int s_idx[DS_MAXK];
     __shared__ float s_w[DS_MAXK];
     __shared__ const uint8_t* s_slot[DS_MAXK + 1];
@@ -124,6 +131,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int grid = gridDim.x, b = blockIdx.x, E = a.E, K = a.K, O = E + 1;
     if (tid < DS_WARPS * DS_D) mbar_init(smem_u32(bars + tid), 1);
+    if (tid == 0) mbar_init(smem_u32(&shbar), 1);
     if (tid == 0) { s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
     for (int i = tid; i < a.n_layers; i += DS_THREADS) s_layers[i] = a.layers[i];
     // the token: residual row, rmsnorm, split (every CTA its own copy)
@@ -199,8 +207,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     const bool weights_cta = b == grid - 1;
     const int wgrid = grid > 1 ? grid - 1 : 1;
     const bool worker = grid == 1 || !weights_cta;
-    const int U3 = (K + 1) * 64, U4 = (K + 1) * 128;
-    const int n3 = (U3 + 2 * wgrid - 1) / (2 * wgrid), n4 = (U4 + DS_WARPS * wgrid - 1) / (DS_WARPS * wgrid), nS = n3 + n4;
+    const int U3 = (K + 1) * 64, U4 = EH / 16;   // gate/up units; down row tiles (a CTA takes a tile for all K + 1 experts)
+    const int n3 = (U3 + 2 * wgrid - 1) / (2 * wgrid), n4 = (U4 + wgrid - 1) / wgrid, nS = n3 + n4;
     uint8_t* myring = ring + warp * DS_D * SB;
     uint64_t* mybars = bars + warp * DS_D;
     long long S0 = 0;        // slices (list entries) of this warp in earlier layers
@@ -212,9 +220,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             if (u >= U3) return nullptr;
             return s_slot[u >> 6] + (size_t)((u & 63) * 4 + (warp & 3)) * SB;
         }
-        const int u = ((s - n3) * wgrid + b) * DS_WARPS + warp;
-        if (u >= U4) return nullptr;
-        return s_slot[u >> 7] + (size_t)(256 + (u & 127)) * SB;
+        const int tt = (s - n3) * wgrid + b;   // down: routed expert `warp`, row tile tt
+        if (tt >= U4 || warp >= K) return nullptr;
+        return s_slot[warp] + (size_t)(256 + tt) * SB;
     };
     auto issue = [&](int s) {   // lane 0
         const uint8_t* src = slice_src(s);
@@ -223,6 +231,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         const uint32_t bar = smem_u32(mybars + S % DS_D);
         mbar_arrive_expect_tx(bar, SB);
         bulk_g2s(smem_u32(myring + (S % DS_D) * SB), src, SB, bar);
+    };
+    uint32_t sh_phase = 0;   // parity of the next completion of the shared expert's slice barrier
+    bool sh_inflight = false;   // a copy into shbuf was requested and not yet waited for (every thread keeps track)
+    auto issue_shared = [&](int pass) {   // thread 0: the shared expert's down slice of this CTA's row tile of the pass
+        const int tt = pass * wgrid + b;
+        if (!worker || tt >= U4) return;
+        mbar_arrive_expect_tx(smem_u32(&shbar), SB);
+        bulk_g2s(smem_u32(shbuf), s_slot[K] + (size_t)(256 + tt) * SB, SB, smem_u32(&shbar));
     };
     uint32_t phase = 0;      // bit j: parity of the next completion of buffer j's barrier (empty list entries skip a buffer)
     auto wait_slice = [&](int s) -> bool {
@@ -306,7 +322,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         if (lane == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the buffers were read by the warp in the layer before
             for (; issued < nS && issued < DS_D; issued++) issue(issued);
+            if (warp == 0) issue_shared(0);
         }
+        sh_inflight = worker && b < U4;
         issued = __shfl_sync(0xffffffffu, issued, 0);
         if (l + 1 < a.n_layers) stage_layer(l + 1);   // lands while the experts stream; waited for at the end of the layer
         for (int pass = 0; pass < n3 && ok; pass++) {
@@ -340,54 +358,62 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             ok = __syncthreads_and(ok);   // also: every warp leaves the loop together when a copy timed out
         }
         if (!ok || !(ok = grid_barrier())) break;
-        // ---- P4: down. The slice is (mostly) in shared memory already; the expert's act row comes from L2 ----
-        // (the routing weights were published before the barrier just passed: one copy per CTA, read in P5)
-        if (!weights_cta && tid <= K) s_wt[tid] = __ldcg(a.wts + tid);
+        // ---- P4: down. A CTA takes a 16-row tile for all K + 1 experts: warp k the routed expert k, and the shared expert's
+        // slice one input group per warp; the slices are (mostly) in shared memory already, the act rows come from L2. The
+        // tile's rows of the new residual row are finished here: x += sum of the weighted rows in rank order ----
+        if (tid <= K) s_wt[tid] = __ldcg(a.wts + tid);   // published by the last CTA before the barrier just passed
         for (int pass = 0; pass < n4 && ok; pass++) {
-            const int u = worker ? (pass * wgrid + b) * DS_WARPS + warp : U4;
-            if (u < U4) {
-                const int k = u >> 7, wt = u & 127;
-                uint8_t* ac = acol + warp * 2 * DS_ACOL;
-                const uint4* src = reinterpret_cast<const uint4*>(a.act + (size_t)k * 2 * EI);   // 2 x 1024 bytes
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int c = lane + 32 * i;   // 16-byte chunk 0..127: column c >> 6, chunk c & 63
-                    *reinterpret_cast<uint4*>(ac + (c >> 6) * DS_ACOL + (c & 63) * 16) = __ldcg(src + c);
-                }
-                __syncwarp();
+            const int tt = worker ? pass * wgrid + b : U4;
+            if (tt < U4) {
+                if (tid < 128) *reinterpret_cast<uint4*>(shcol + (tid >> 6) * DS_ACOL + (tid & 63) * 16) = __ldcg(reinterpret_cast<const uint4*>(a.act + (size_t)K * 2 * EI) + tid);
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                if (!wait_slice(n3 + pass)) ok = false;
-                else {
-                    ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc);
-                    if (t == 0) {
-                        const int d = 16 * wt + g;
-                        __stcg(a.ypair + (size_t)k * EH + d, acc[0] + acc[1]);
-                        __stcg(a.ypair + (size_t)k * EH + d + 8, acc[2] + acc[3]);
+                if (warp < K) {
+                    uint8_t* ac = acol + warp * 2 * DS_ACOL;
+                    const uint4* src = reinterpret_cast<const uint4*>(a.act + (size_t)warp * 2 * EI);   // 2 x 1024 bytes
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int c = lane + 32 * i;   // 16-byte chunk 0..127: column c >> 6, chunk c & 63
+                        *reinterpret_cast<uint4*>(ac + (c >> 6) * DS_ACOL + (c & 63) * 16) = __ldcg(src + c);
                     }
+                    __syncwarp();
+                    if (!wait_slice(n3 + pass)) ok = false;
+                    else ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc);
+                    if (t == 0) { yrt[warp * 16 + g] = acc[0] + acc[1]; yrt[warp * 16 + g + 8] = acc[2] + acc[3]; }
                 }
+                __syncthreads();   // the shared expert's act row is in
+                if (!mbar_wait(smem_u32(&shbar), sh_phase, a.err, DS_ERR_COPY)) { atomicExch(a.sync + 1, 1u); s_abort = 1; ok = false; }
+                else {
+                    float as[4] = {0.f, 0.f, 0.f, 0.f};
+                    ds_slice<FMT>(shbuf, shcol + (g & 1) * DS_ACOL + t * 16, lane, as, warp, warp + 1);
+                    if (t == 0) { ysh[warp * 16 + g] = as[0] + as[1]; ysh[warp * 16 + g + 8] = as[2] + as[3]; }
+                }
+                sh_phase ^= 1u;
+                sh_inflight = false;
             }
             consumed = n3 + pass + 1;
-            __syncwarp();
+            __syncthreads();
+            if (tt < U4 && tid < 16) {
+                float acc = 0.f;
+                for (int r = 0; r < K; r++) acc += __fmul_rn(s_wt[r], yrt[r * 16 + tid]);
+                float sh = 0.f;
+#pragma unroll
+                for (int w = 0; w < DS_WARPS; w++) sh += ysh[w * 16 + tid];
+                acc += __fmul_rn(s_wt[K], sh);
+                __stcg(a.ypair + 16 * tt + tid, xres[16 * tt + tid] + acc);
+            }
             if (lane == 0 && issued < nS) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue(issued); }
             if (issued < nS) issued++;
+            ok = __syncthreads_and(ok);
+            if (tid == 0 && pass + 1 < n4) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue_shared(pass + 1); }
+            if (pass + 1 < n4) sh_inflight = worker && (pass + 1) * wgrid + b < U4;
         }
         S0 += nS;
         if (!__syncthreads_and(ok) || !(ok = grid_barrier())) { ok = false; break; }
-        // ---- P5: x += the K + 1 rows in rank order, rmsnorm + split for the next layer (every CTA) ----
+        // ---- P5: the new residual row (every CTA its own copy), rmsnorm + split for the next layer ----
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int k0 = 1024 * h + 4 * tid;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 y[DS_MAXK + 1];   // all rows (and weights) in flight at once; weighted and added in rank order
-            float w[DS_MAXK + 1];
-#pragma unroll
-            for (int r = 0; r <= DS_MAXK; r++)
-                if (r <= K) { y[r] = __ldcg(reinterpret_cast<const float4*>(a.ypair + (size_t)r * EH + k0)); w[r] = s_wt[r]; }
-#pragma unroll
-            for (int r = 0; r <= DS_MAXK; r++)
-                if (r <= K) { acc.x += __fmul_rn(w[r], y[r].x); acc.y += __fmul_rn(w[r], y[r].y); acc.z += __fmul_rn(w[r], y[r].z); acc.w += __fmul_rn(w[r], y[r].w); }
-            const float4 x = *reinterpret_cast<const float4*>(xres + k0);
-            acc.x = x.x + acc.x; acc.y = x.y + acc.y; acc.z = x.z + acc.z; acc.w = x.w + acc.w;
+            const float4 acc = __ldcg(reinterpret_cast<const float4*>(a.ypair + k0));
             *reinterpret_cast<float4*>(xres + k0) = acc;
             v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
         }
@@ -400,6 +426,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     if (!ok) {
         for (int s = consumed; s < issued; s++)
             if (slice_src(s)) wait_slice(s);
+        if (sh_inflight) mbar_wait(smem_u32(&shbar), sh_phase, a.err, DS_ERR_COPY);
         return;
     }
     if (b == 0) {
