@@ -113,6 +113,7 @@ struct moexb_ctx {
     uint16_t *xs = nullptr, *act_split = nullptr;       // activations / act as 16-bit hi + lo halves, permuted
     moexb_pair_item* subs = nullptr;                    // sub-items of at most 8 pairs
     int *nsub = nullptr, *err = nullptr;
+    moexb_pair_item* subs2 = nullptr; int* nsub2 = nullptr;   // second sub-item list (the down tiles of the tensor-core path)
     int* route_done = nullptr;                          // per token tile: blocks of the routing kernel that have finished (returns to zero)
     int sms = 0, path = 0;                              // path: 0 = streaming kernels, 1 = fp32 SIMT kernels
     int fused_decode = 1;                               // one-token residual stacks run as one cooperative launch
@@ -413,7 +414,7 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
     A(&c->counts, (size_t)max_experts); A(&c->nitems, 1); A(&c->items, (size_t)max_experts + 1); A(&c->pairs, P);
     A(&c->slots, (size_t)top_k + 1); A(&c->wts, (size_t)top_k + 1);
     A(&c->xs, T * 2 * EH); A(&c->act_split, P * 2 * EI); A(&c->subs, (size_t)max_experts + 1 + P / ST_MAXP + 1);
-    A(&c->nsub, 2); A(&c->err, 1); A(&c->route_done, (size_t)max_tokens); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
+    A(&c->nsub, 2); A(&c->err, 1); A(&c->subs2, (size_t)max_experts + 1 + P / (PF_NMAX / 2) + 1); A(&c->nsub2, 1); A(&c->route_done, (size_t)max_tokens); A(&c->staging, (size_t)STAGING_BLOBS * expert_bytes(FMT_ZP));
     if (rc == MOEXB_OK && cudaMemset(c->err, 0, sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaMemset(c->route_done, 0, (size_t)max_tokens * sizeof(int)) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: memset");
     if (rc == MOEXB_OK && cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = fail(MOEXB_ERR_CUDA, "ctx_create: device attribute");
@@ -645,22 +646,14 @@ static int prefill_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, const
         split8_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(xf, c->xs, EH, parts, n);
         LAUNCHED("split8_rows");
     }
+    // the planner left two tile lists in the context: subs (up to 128 / parts pairs: gate/up) and subs2 (up to 64 pairs: down,
+    // whose act columns are always hi + lo)
     auto run = [&]<int FMT>() {
-        {
-            PROF(c, MOEXB_PROF_GROUP, stream);
-            plan_subitems_k<<<1, 1024, 0, S(stream)>>>(c->items, c->nitems, 0, c->subs, c->nsub, PF_NMAX / parts);
-            LAUNCHED("plan_subitems");
-        }
         PrefillArgs a{c->subs, c->nsub, pairs, c->xs, c->act_split, nullptr, ypair, c->err, parts};
         int rc = prefill_launch_one<FMT, false>(c, a, stream);
         if (rc != MOEXB_OK) return rc;
-        if (parts != 2) {
-            PROF(c, MOEXB_PROF_GROUP, stream);
-            plan_subitems_k<<<1, 1024, 0, S(stream)>>>(c->items, c->nitems, 0, c->subs, c->nsub, PF_NMAX / 2);
-            LAUNCHED("plan_subitems");
-        }
         PrefillArgs d = a;
-        d.xs = c->act_split; d.parts = 2;
+        d.tiles = c->subs2; d.ntiles = c->nsub2; d.xs = c->act_split; d.parts = 2;
         return prefill_launch_one<FMT, true>(c, d, stream);
     };
     if (fmt == FMT_SYM_F16) return run.template operator()<FMT_SYM_F16>();
@@ -756,9 +749,19 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
                                     W, xf, c->logits, EH, E, K, 1, T, c->route_done, o));
                 return MOEXB_OK;
             };
-            // a small batch: 16 outputs x 8 tokens per block, to reach every SM; a prefill chunk has blocks to spare and
-            // re-reads the router weights less with 32 outputs x 16 tokens per block
-            const int rc = T >= 256 ? gemm.template operator()<4, 16>() : gemm.template operator()<2, 8>();
+            // a small batch: 16 outputs x 8 tokens per block, to reach every SM; a prefill chunk goes to the register-tiled
+            // kernel (32 tokens x 16 outputs per block, FMA-bound)
+            auto gemm2 = [&]() -> int {
+                constexpr int SMEM = 2 * rg2_stage_bytes<WT>();
+                static std::once_flag once;
+                static cudaError_t attr_err = cudaSuccess;
+                std::call_once(once, [] { attr_err = cudaFuncSetAttribute(route_gemm2_k<WT, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+                if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
+                CUDA_TRY(launch_dep(route_gemm2_k<WT, NJ>, dim3((E + 1 + RG2_TN - 1) / RG2_TN, (T + RG2_TM - 1) / RG2_TM), 256, SMEM, S(stream),
+                                    W, xf, c->logits, E, K, 1, T, c->route_done, o));
+                return MOEXB_OK;
+            };
+            const int rc = T >= 256 ? gemm2() : gemm.template operator()<2, 8>();
             if (rc != MOEXB_OK) return rc;
         }
         LAUNCHED("route");
@@ -825,12 +828,10 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
     } else {
         {
             PROF(c, MOEXB_PROF_GROUP, stream);
-            if (tiled && !prefill && tiled_maxp(c, L->fmt, T) == 8)
-                CUDA_TRY(launch_dep(group_plan_k<8>, (E + 7) / 8, 256, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                    shared ? c->logits + E : nullptr, ld, sh0, sh1));
-            else
-                CUDA_TRY(launch_dep(group_plan_k<ST_MAXP>, (E + 7) / 8, 256, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub,
-                                    shared ? c->logits + E : nullptr, ld, sh0, sh1));
+            const int parts = (x_bf16 && !block) ? 1 : 2;
+            const int maxp = prefill ? PF_NMAX / parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
+            CUDA_TRY(launch_dep(group_plan1_k, 1, 1024, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
+                                prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1));
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
             // reduction skips them by expert id

@@ -313,6 +313,91 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
     for (int r = warp; r < TR && r0 + r < T; r += WARPS) topk_token<NJ, true>(y + (size_t)(r0 + r) * O, r0 + r, E, K, norm, lane, o);
 }
 
+// The same for a prefill chunk, register-tiled. A block of 8 warps owns 32 tokens x 16 outputs; warp (wm, wn) the 8 tokens
+// 8*wm.. and the 8 outputs 8*wn.., every lane the same 4 of each 128 inputs as in gemv_rows_k, so a lane holds 64 partial
+// sums and each (token, output) sum is formed in the pinned order. Token rows and weight rows come through shared memory in
+// chunks of 512 inputs (cp.async, two stages): per 128 inputs a warp reads 16 x 16 bytes per lane and does 256 fused
+// multiply-adds, which makes the kernel FMA-bound where route_gemm_k is bound by re-reading the weights from L2. The last
+// block of a token tile selects the experts of its 32 tokens. grid (ceil((E + 1) / 16), ceil(T / 32)); I = 2048.
+constexpr int RG2_TM = 32, RG2_TN = 16, RG2_KC = 512;
+template <typename WT> constexpr int rg2_stage_bytes() { return RG2_TM * RG2_KC * 4 + RG2_TN * RG2_KC * (int)sizeof(WT); }
+template <typename WT, int NJ>
+__global__ void __launch_bounds__(256) route_gemm2_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int E, int K,
+                                                     int norm, int T, int* __restrict__ done, const TopkOut o) {
+    constexpr int I = EH, NCH = I / RG2_KC, STAGE = rg2_stage_bytes<WT>();
+    extern __shared__ __align__(16) uint8_t rsm[];   // 2 stages x ([32 tokens][512] f32 | [16 outputs][512] WT)
+    const int O = E + 1, r0 = blockIdx.y * RG2_TM, o0 = blockIdx.x * RG2_TN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+    auto fill_w = [&](int ch) {
+        uint8_t* ws = rsm + (ch & 1) * STAGE + RG2_TM * RG2_KC * 4;
+        constexpr int PER_ROW = RG2_KC * (int)sizeof(WT) / 16;   // 16-byte pieces per row chunk
+        for (int i = tid; i < RG2_TN * PER_ROW; i += 256) {
+            const int r = i / PER_ROW, c = i % PER_ROW;
+            cp_async16(smem_u32(ws + (size_t)i * 16), reinterpret_cast<const uint8_t*>(W + (size_t)min(o0 + r, O - 1) * I + ch * RG2_KC) + c * 16);
+        }
+    };
+    auto fill_x = [&](int ch) {
+        uint8_t* xs = rsm + (ch & 1) * STAGE;
+        constexpr int PER_ROW = RG2_KC * 4 / 16;
+        for (int i = tid; i < RG2_TM * PER_ROW; i += 256) {
+            const int r = i / PER_ROW, c = i % PER_ROW;
+            cp_async16(smem_u32(xs + (size_t)i * 16), reinterpret_cast<const uint8_t*>(x + (size_t)min(r0 + r, T - 1) * I + ch * RG2_KC) + c * 16);
+        }
+    };
+    fill_w(0);   // weights do not depend on the kernel before this one
+    pdl_wait();
+    pdl_trigger();
+    fill_x(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+    for (int ch = 0; ch < NCH; ch++) {
+        if (ch + 1 < NCH) { fill_w(ch + 1); fill_x(ch + 1); }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const float* xs = reinterpret_cast<const float*>(rsm + (ch & 1) * STAGE) + (size_t)(8 * wm) * RG2_KC;
+        const WT* ws = reinterpret_cast<const WT*>(rsm + (ch & 1) * STAGE + RG2_TM * RG2_KC * 4) + (size_t)(8 * wn) * RG2_KC;
+#pragma unroll
+        for (int c = 0; c < RG2_KC / 128; c++) {
+            float4 wv[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if constexpr (sizeof(WT) == 4) wv[j] = *reinterpret_cast<const float4*>(ws + (size_t)j * RG2_KC + 128 * c + 4 * lane);
+                else {
+                    const uint2 h = *reinterpret_cast<const uint2*>(ws + (size_t)j * RG2_KC + 128 * c + 4 * lane);
+                    const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), q = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+                    wv[j] = make_float4(p.x, p.y, q.x, q.y);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)i * RG2_KC + 128 * c + 4 * lane);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float a = acc[i][j];
+                    a = fmaf(wv[j].x, v.x, a); a = fmaf(wv[j].y, v.y, a); a = fmaf(wv[j].z, v.z, a); a = fmaf(wv[j].w, v.w, a);
+                    acc[i][j] = a;
+                }
+            }
+        }
+        __syncthreads();   // the stage is refilled by the copies of chunk ch + 2
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float sum = warp_sum(acc[i][j]);
+            const int r = r0 + 8 * wm + i, oo = o0 + 8 * wn + j;
+            if (lane == 0 && r < T && oo < O) y[(size_t)r * O + oo] = sum;
+        }
+    if (!last_block_done(done + blockIdx.y, gridDim.x)) return;
+    for (int r = warp; r < RG2_TM && r0 + r < T; r += 8) topk_token<NJ, true>(y + (size_t)(r0 + r) * O, r0 + r, E, K, norm, lane, o);
+}
+
 // ---- pair grouping: bucket the T*K (token, rank) pairs by expert (moex.cu:1466-1486; kernels.cuh:1030-1045) ----------
 
 // counts[e] = number of pairs that selected expert e. One warp per expert.
@@ -367,106 +452,6 @@ __global__ void __launch_bounds__(WARPS * 32) group_scatter_k(const int* __restr
             for (int t = threadIdx.x; t < T; t += blockDim.x)
                 pairs[s_np + t] = {t, n + t, 1.f / (1.f + expf(-gate_logits[(size_t)t * gl_stride]))};
         } else if (threadIdx.x == 0) *nitems = s_ni;
-    }
-}
-
-// Exclusive prefix sums of N per-thread values over a block of 256 threads; totals returned through tot[].
-template <int N>
-__device__ __forceinline__ void block_scan_256(int (&v)[N], int (&tot)[N]) {
-    __shared__ int ws[N][8];
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    int inc[N];
-#pragma unroll
-    for (int i = 0; i < N; i++) {
-        inc[i] = v[i];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, inc[i], o); if (lane >= o) inc[i] += u; }
-        if (lane == 31) ws[i][w] = inc[i];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < N; i++) {
-        int before = 0, all = 0;
-#pragma unroll
-        for (int j = 0; j < 8; j++) { const int x = ws[i][j]; all += x; if (j < w) before += x; }
-        v[i] = inc[i] - v[i] + before;
-        tot[i] = all;
-    }
-}
-
-// Grouping and planning in one launch (the work of group_count_k + group_scatter_k, plus the sub-items of at most MAXP
-// pairs that the streaming kernels walk). Every block builds the per-expert histogram of the T*K pairs in shared memory
-// and scans it; then one warp per expert writes that expert's item, its sub-items and its pairs in token order.
-// Sub-items of more than MAXP / 2 pairs ("wide") come first in subs[], the others after them, and nsub[1] receives the
-// number of wide ones: a pass over a wide sub-item costs the streaming kernels more, and with the two kinds apart a kernel
-// can split the work evenly from nsub[0] and nsub[1] alone. (An expert's sub-items are all wide except possibly its last.)
-// Optional shared expert as in group_scatter_k, for the tokens [sh0, sh1). E <= 1024; 256 threads; grid ceil(E / 8).
-__host__ __device__ constexpr int plan_wide(int c, int maxp) { return c / maxp + (c % maxp > maxp / 2); }
-__host__ __device__ constexpr int plan_narrow(int c, int maxp) { return c % maxp > 0 && c % maxp <= maxp / 2; }
-template <int MAXP>
-__global__ void __launch_bounds__(256) group_plan_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
-                                                    const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
-                                                    moexb_pair* __restrict__ pairs, int* __restrict__ nitems, moexb_pair_item* __restrict__ subs,
-                                                    int* __restrict__ nsub, const float* __restrict__ gate_logits, int gl_stride,
-                                                    int sh0, int sh1) {
-    __shared__ int cnt[1024], start[1024], item_of[1024], wide_at[1024], narrow_at[1024];
-    __shared__ int s_tot[4];
-    const int n = T * K, tid = threadIdx.x, lane = tid & 31;
-    for (int e = tid; e < E; e += 256) cnt[e] = 0;
-    __syncthreads();
-    pdl_wait();
-    pdl_trigger();
-    for (int p = tid; p < n; p += 256) atomicAdd(&cnt[__ldg(idx + p)], 1);
-    __syncthreads();
-    {
-        const int per = (E + 255) / 256, e0 = tid * per;
-        int c[4], v[4] = {0, 0, 0, 0}, tot[4];
-        for (int i = 0; i < per; i++) {
-            const int e = e0 + i;
-            c[i] = (e < E && slot_table[e]) ? cnt[e] : 0;
-            v[0] += c[i]; v[1] += c[i] != 0; v[2] += plan_wide(c[i], MAXP); v[3] += plan_narrow(c[i], MAXP);
-        }
-        block_scan_256<4>(v, tot);
-        for (int i = 0; i < per; i++) {
-            const int e = e0 + i;
-            if (e < E) {
-                start[e] = v[0]; item_of[e] = c[i] ? v[1] : -1; wide_at[e] = v[2]; narrow_at[e] = v[3];
-                cnt[e] = c[i];
-            }
-            v[0] += c[i]; v[1] += c[i] != 0; v[2] += plan_wide(c[i], MAXP); v[3] += plan_narrow(c[i], MAXP);
-        }
-        if (tid == 0) { s_tot[0] = tot[0]; s_tot[1] = tot[1]; s_tot[2] = tot[2]; s_tot[3] = tot[3]; }
-    }
-    __syncthreads();
-    const bool with_shared = gate_logits && slot_table[E] && sh1 > sh0;
-    const int Ts = with_shared ? sh1 - sh0 : 0;
-    const int nw = s_tot[2] + plan_wide(Ts, MAXP);   // all wide sub-items: the routed experts', then the shared expert's
-    const int e = blockIdx.x * 8 + (tid >> 5);
-    if (e < E && item_of[e] >= 0) {
-        const uint8_t* slot = slot_table[e];
-        int at = start[e];
-        const int c = cnt[e], cw = plan_wide(c, MAXP);
-        if (lane == 0) items[item_of[e]] = {slot, at, c};
-        for (int j = lane; j * MAXP < c; j += 32)
-            subs[j < cw ? wide_at[e] + j : nw + narrow_at[e]] = {slot, at + j * MAXP, min(MAXP, c - j * MAXP)};
-        for (int p0 = 0; p0 < n; p0 += 32) {
-            const int p = p0 + lane;
-            const bool hit = p < n && __ldg(idx + p) == e;
-            const unsigned b = __ballot_sync(0xffffffffu, hit);
-            if (hit) pairs[at + __popc(b & ((1u << lane) - 1))] = {p / K, p, __ldg(w + p)};
-            at += __popc(b);
-        }
-    }
-    if (blockIdx.x == 0) {
-        const int np = s_tot[0], ni = s_tot[1], ns = nw + s_tot[3];  // ns: where the shared expert's narrow sub-item goes
-        if (with_shared) {
-            // the shared expert for tokens [sh0, sh1) (all of them on one GPU; a slice per rank under expert parallelism)
-            const uint8_t* slot = slot_table[E];
-            const int cw = plan_wide(Ts, MAXP);
-            if (tid == 0) { items[ni] = {slot, np, Ts}; *nitems = ni + 1; nsub[0] = ns + plan_narrow(Ts, MAXP); nsub[1] = nw; }
-            for (int t = tid; t < Ts; t += 256) pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gate_logits[(size_t)(sh0 + t) * gl_stride]))};
-            for (int j = tid; j * MAXP < Ts; j += 256) subs[j < cw ? s_tot[2] + j : ns] = {slot, np + j * MAXP, min(MAXP, Ts - j * MAXP)};
-        } else if (tid == 0) { *nitems = ni; nsub[0] = ns; nsub[1] = nw; }
     }
 }
 

@@ -45,7 +45,6 @@ __host__ __device__ constexpr int split_pos(int k) {
     return G * 64 + w * 32 + t * 8 + (((e & 3) << 1) | (e >> 2));
 }
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -71,12 +70,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -455,6 +448,66 @@ __device__ __forceinline__ int block_scan_1024(int v, int& total) {
     total = __shfl_sync(0xffffffffu, ws, 31);
     const int before = __shfl_sync(0xffffffffu, ws, (w + 31) & 31);
     return inc - v + (w ? before : 0);
+}
+
+// Grouping and planning of a batch in one block of 1024 threads (one expert per thread; E <= 1024): the work of
+// group_plan_k for any batch size, and optionally a second sub-item list with another width (the tensor-core kernels take
+// 128 / parts pairs per tile for gate/up and 64 for down). Histogram of the T*K pairs in shared memory, block scans, then
+// every pair takes the next free place of its expert (an atomic cursor: the order of an expert's pairs is not the token
+// order and may change from run to run - every pair's result is independent of its place). List 1 keeps sub-items of more
+// than maxp / 2 pairs first (nsub[1] = their number); list 2 is in expert order. Shared expert as in group_plan_k.
+__global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
+                                                      const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
+                                                      moexb_pair* __restrict__ pairs, int* __restrict__ nitems,
+                                                      moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int maxp,
+                                                      moexb_pair_item* __restrict__ subs2, int* __restrict__ nsub2, int maxp2,
+                                                      const float* __restrict__ gate_logits, int gl_stride, int sh0, int sh1) {
+    __shared__ int cnt[1024], cur[1024], start[1024];
+    const int n = T * K, e = threadIdx.x;
+    cnt[e] = 0; cur[e] = 0;
+    __syncthreads();
+    pdl_wait();
+    pdl_trigger();
+    for (int p = e; p < n; p += 1024) atomicAdd(&cnt[__ldg(idx + p)], 1);
+    __syncthreads();
+    const uint8_t* slot = e < E ? slot_table[e] : nullptr;
+    const int c = slot ? cnt[e] : 0;   // pairs of experts that are not held here are dropped
+    auto wide = [](int c, int mp) { return c / mp + (c % mp > mp / 2); };
+    auto narrow = [](int c, int mp) { return (int)(c % mp > 0 && c % mp <= mp / 2); };
+    int np, ni, nw, nn, n2 = 0;
+    const int at = block_scan_1024(c, np), item = block_scan_1024(c != 0, ni);
+    const int wat = block_scan_1024(wide(c, maxp), nw), nat = block_scan_1024(narrow(c, maxp), nn);
+    const int at2 = subs2 ? block_scan_1024((c + maxp2 - 1) / maxp2, n2) : 0;
+    start[e] = slot ? at : -1;
+    const bool with_shared = gate_logits && slot_table[E] && sh1 > sh0;
+    const int Ts = with_shared ? sh1 - sh0 : 0;
+    const int all_wide = nw + wide(Ts, maxp);   // the routed experts' wide sub-items, then the shared expert's
+    if (c) {
+        items[item] = {slot, at, c};
+        const int cw = wide(c, maxp);
+        for (int j = 0; j * maxp < c; j++) subs[j < cw ? wat + j : all_wide + nat] = {slot, at + j * maxp, min(maxp, c - j * maxp)};
+        if (subs2) for (int j = 0; j * maxp2 < c; j++) subs2[at2 + j] = {slot, at + j * maxp2, min(maxp2, c - j * maxp2)};
+    }
+    __syncthreads();
+    for (int p = e; p < n; p += 1024) {
+        const int ex = __ldg(idx + p), s0 = start[ex];
+        if (s0 >= 0) pairs[s0 + atomicAdd(&cur[ex], 1)] = {p / K, p, __ldg(w + p)};
+    }
+    if (with_shared) {
+        const uint8_t* sslot = slot_table[E];
+        const int cw = wide(Ts, maxp), ns = all_wide + nn;   // ns: where the shared expert's narrow sub-item goes
+        for (int t = e; t < Ts; t += 1024) pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gate_logits[(size_t)(sh0 + t) * gl_stride]))};
+        for (int j = e; j * maxp < Ts; j += 1024) subs[j < cw ? nw + j : ns] = {sslot, np + j * maxp, min(maxp, Ts - j * maxp)};
+        if (subs2) for (int j = e; j * maxp2 < Ts; j += 1024) subs2[n2 + j] = {sslot, np + j * maxp2, min(maxp2, Ts - j * maxp2)};
+        if (e == 0) {
+            items[ni] = {sslot, np, Ts}; *nitems = ni + 1;
+            nsub[0] = ns + narrow(Ts, maxp); nsub[1] = all_wide;
+            if (subs2) *nsub2 = n2 + (Ts + maxp2 - 1) / maxp2;
+        }
+    } else if (e == 0) {
+        *nitems = ni; nsub[0] = all_wide + nn; nsub[1] = all_wide;
+        if (subs2) *nsub2 = n2;
+    }
 }
 
 // Sub-items of at most maxp pairs from the items of a work list. One block of 1024 threads, one item per thread
