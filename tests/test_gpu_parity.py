@@ -532,15 +532,15 @@ def test_prefill_chunk_of_2048_tokens_both_kernel_families_agree():
     L.close(); c.close()
 
 
-@pytest.mark.parametrize("E,fmt,router", [(256, m.FMT_SYM_F16, np.float32), (64, m.FMT_SYM_F32, np.float16)])
-def test_one_token_stack_as_one_cooperative_launch(E, fmt, router):
+@pytest.mark.parametrize("E,fmt,router,K", [(256, m.FMT_SYM_F16, np.float32, 8), (64, m.FMT_SYM_F32, np.float16, 8), (96, m.FMT_SYM_F16, np.float32, 3)])
+def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
     """A one-token stack of residual blocks runs as a single cooperative kernel (grid barriers inside). Against the graph of
     per-layer kernels on the same layers: the result agrees within the parity bars (the two add the four K slices of a
     gate/up row in a different order), twice in a row (the barrier counter is reset per launch), for f32 and bf16 inputs
     and through host buffers; and against the oracle chain."""
     rng = np.random.default_rng(11)
     NL, T = 5, 1
-    c = m.Context(0, max_tokens=4, max_experts=E, top_k=8)
+    c = m.Context(0, max_tokens=4, max_experts=E, top_k=K)
     layers, hosts, Ws = [], [], []
     for l in range(NL):
         L = m.Layer(c, fmt, E, router_dtype=m.F16 if router == np.float16 else m.F32)
@@ -551,15 +551,15 @@ def test_one_token_stack_as_one_cooperative_launch(E, fmt, router):
     x0 = rng.standard_normal((T, 2048)).astype(np.float32)
     x_ref = x0.copy()
     for l in range(NL):
-        moe, _, _, _ = o.layer_forward(fmt, hosts[l], Ws[l], o.rmsnorm(x_ref), 8)
+        moe, _, _, _ = o.layer_forward(fmt, hosts[l], Ws[l], o.rmsnorm(x_ref), K)
         x_ref = x_ref + moe
     for dt, xin in ((m.F32, torch.from_numpy(x0)), (m.BF16, torch.from_numpy(x0).to(torch.bfloat16))):
         c.set_fused_decode(False)
-        graph = m.Stack(c, layers, T, 8, dt)
+        graph = m.Stack(c, layers, T, K, dt)
         y_graph = graph.run(xin.to(DEV)).cpu().numpy().copy()
         graph.close()
         c.set_fused_decode(True)
-        fused = m.Stack(c, layers, T, 8, dt)
+        fused = m.Stack(c, layers, T, K, dt)
         assert fused.kernel_count == 1
         y1 = fused.run(xin.to(DEV)).cpu().numpy().copy()
         y2 = fused.run(xin.to(DEV)).cpu().numpy().copy()
