@@ -468,7 +468,14 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     __syncthreads();
     pdl_wait();
     pdl_trigger();
-    for (int p = e; p < n; p += 1024) atomicAdd(&cnt[__ldg(idx + p)], 1);
+    constexpr int B = 8;   // pairs per thread in flight: the loops are chains of global loads otherwise
+    for (int p0 = e; p0 < n; p0 += 1024 * B) {
+        int ex[B];
+#pragma unroll
+        for (int u = 0; u < B; u++) ex[u] = p0 + 1024 * u < n ? __ldg(idx + p0 + 1024 * u) : -1;
+#pragma unroll
+        for (int u = 0; u < B; u++) if (ex[u] >= 0) atomicAdd(&cnt[ex[u]], 1);
+    }
     __syncthreads();
     const uint8_t* slot = e < E ? slot_table[e] : nullptr;
     const int c = slot ? cnt[e] : 0;   // pairs of experts that are not held here are dropped
@@ -489,9 +496,15 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
         if (subs2) for (int j = 0; j * maxp2 < c; j++) subs2[at2 + j] = {slot, at + j * maxp2, min(maxp2, c - j * maxp2)};
     }
     __syncthreads();
-    for (int p = e; p < n; p += 1024) {
-        const int ex = __ldg(idx + p), s0 = start[ex];
-        if (s0 >= 0) pairs[s0 + atomicAdd(&cur[ex], 1)] = {p / K, p, __ldg(w + p)};
+    for (int p0 = e; p0 < n; p0 += 1024 * B) {
+        int ex[B]; float wp[B];
+#pragma unroll
+        for (int u = 0; u < B; u++) { const int p = p0 + 1024 * u; ex[u] = p < n ? __ldg(idx + p) : -1; wp[u] = p < n ? __ldg(w + p) : 0.f; }
+#pragma unroll
+        for (int u = 0; u < B; u++) {
+            const int p = p0 + 1024 * u, s0 = ex[u] >= 0 ? start[ex[u]] : -1;
+            if (s0 >= 0) pairs[s0 + atomicAdd(&cur[ex[u]], 1)] = {p / K, p, wp[u]};
+        }
     }
     if (with_shared) {
         const uint8_t* sslot = slot_table[E];
