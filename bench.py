@@ -340,7 +340,7 @@ def main():
         "clocks": clocks,
         "per_layer": {"us": ms_step * 1e3 / NL, "tokens_per_s": tokens_total / (ms_step * 1e-3 / NL)},
     }
-    if T == 1 and world == 1 and fmt != m.FMT_ZP and stack.kernel_count == 1:
+    if T == 1 and world == 1 and stack.kernel_count == 1:
         # the one-token stack is ONE cooperative kernel: its roofline is the whole step
         r = line["roofline"]
         step_bytes = layer_bytes * NL

@@ -74,36 +74,64 @@ template <int FMT> constexpr int ds_smem_bytes() {
 template <int FMT>
 __device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4], int G0 = 0, int G1 = 8) {
     constexpr int GB = tl_group_bytes<FMT>();
-    const int g = lane >> 2;
+    const int g = lane >> 2, t = lane & 3;
 #pragma unroll 4
     for (int G = G0; G < G1; G++) {
         const uint4 qq = *reinterpret_cast<const uint4*>(sl + G * GB + 16 * lane);
         const uint4 B0 = *reinterpret_cast<const uint4*>(bp + G * 128), B1 = *reinterpret_cast<const uint4*>(bp + G * 128 + 64);
         uint32_t Pa[2][4], Pb[2][4];
-        dq_word_h(qq.x, Pa[0]); dq_word_h(qq.y, Pa[1]); dq_word_h(qq.z, Pb[0]); dq_word_h(qq.w, Pb[1]);
-        float sa, sb;
-        if constexpr (FMT == FMT_SYM_F16) {
-            const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(sl + G * GB + 512 + 4 * g));
-            sa = s2.x; sb = s2.y;
+        if constexpr (FMT != FMT_ZP) {
+            dq_word_h(qq.x, Pa[0]); dq_word_h(qq.y, Pa[1]); dq_word_h(qq.z, Pb[0]); dq_word_h(qq.w, Pb[1]);
+            float sa, sb;
+            if constexpr (FMT == FMT_SYM_F16) {
+                const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(sl + G * GB + 512 + 4 * g));
+                sa = s2.x; sb = s2.y;
+            } else {
+                const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
+                sa = s2.x; sb = s2.y;
+            }
+            float c[4];
+            mma_16<true>(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y, true);
+            mma_16<true>(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w, false);
+            mma_16<true>(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y, false);
+            mma_16<true>(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w, false);
+            acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
+            acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
         } else {
-            const float2 s2 = *reinterpret_cast<const float2*>(sl + G * GB + 512 + 8 * g);
-            sa = s2.x; sb = s2.y;
+            // zero point (stream_tiled_k's scheme, bf16 operands): each 32-weight chunk has its own (s, m), w = s*u + m, so a
+            // group is two partial sums s_c * sum(u x) + m_c * sum(x); the chunks are separated by zeroing the other half's
+            // nibbles, sum(x) comes from an all-ones A fragment
+            dq_word<false>(qq.x, Pa[0]); dq_word<false>(qq.y, Pa[1]); dq_word<false>(qq.z, Pb[0]); dq_word<false>(qq.w, Pb[1]);
+            const uint2 cm = *reinterpret_cast<const uint2*>(sl + G * GB + 512 + 8 * g);      // A: sc0 mn0 sc1 mn1 | B: ...
+            const uint4 dd = *reinterpret_cast<const uint4*>(sl + 8 * GB + 16 * g);           // A sb0, A sb1, B sb0, B sb1
+            const uint32_t da = (G >> 2) ? dd.y : dd.x, db = (G >> 2) ? dd.w : dd.z;
+            const float2 dda = __half22float2(*reinterpret_cast<const __half2*>(&da)), ddb = __half22float2(*reinterpret_cast<const __half2*>(&db));
+#pragma unroll
+            for (int hc = 0; hc < 2; hc++) {
+                const bool mine = (t >> 1) == hc;
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t one = mine ? 0x3F803F80u : 0u;
+                mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
+                mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
+                mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
+                mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
+                mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
+                mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                const uint32_t ca = (cm.x >> (16 * hc)) & 0xFFFFu, cb = (cm.y >> (16 * hc)) & 0xFFFFu;
+                const float s_a = dda.x * (float)(ca & 0xFF), m_a = dda.y * (float)(int8_t)(ca >> 8);
+                const float s_b = ddb.x * (float)(cb & 0xFF), m_b = ddb.y * (float)(int8_t)(cb >> 8);
+                acc[0] += fmaf(s_a, c[0], m_a * c1[0]); acc[1] += fmaf(s_a, c[1], m_a * c1[1]);
+                acc[2] += fmaf(s_b, c[2], m_b * c1[2]); acc[3] += fmaf(s_b, c[3], m_b * c1[3]);
+            }
         }
-        float c[4];
-        mma_16<true>(c, Pa[0][0], Pb[0][0], Pa[0][1], Pb[0][1], B0.x, B0.y, true);
-        mma_16<true>(c, Pa[0][2], Pb[0][2], Pa[0][3], Pb[0][3], B0.z, B0.w, false);
-        mma_16<true>(c, Pa[1][0], Pb[1][0], Pa[1][1], Pb[1][1], B1.x, B1.y, false);
-        mma_16<true>(c, Pa[1][2], Pb[1][2], Pa[1][3], Pb[1][3], B1.z, B1.w, false);
-        acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
-        acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
     }
 }
 
-// WT: router weight type; XBF: the input row is bf16. Symmetric formats only (fp16 operands).
+// WT: router weight type; XBF: the input row is bf16. Symmetric formats run on fp16 operands, zero point on bf16.
 template <int FMT, typename WT, bool XBF>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStackArgs a) {
-    static_assert(FMT != FMT_ZP, "zero-point blobs take the multi-launch path");
     constexpr int SB = tl_slice_bytes<FMT>();
+    constexpr bool F16 = FMT != FMT_ZP;   // element type of the split activations
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                               // [warp][DS_D][SB]
     uint8_t* xcol = ring + DS_WARPS * DS_D * SB;                        // token hi, lo columns (fp16, split_pos order)
@@ -156,7 +184,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             *reinterpret_cast<float4*>(xres + 1024 * h + 4 * tid) = make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
     }
     __syncthreads();
-    norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
+    norm_split_row<F16>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
     __syncthreads();
 
     // The router rows this CTA owns and the slot table of layer l: requested (cp.async) while the layer before still streams
@@ -350,7 +378,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
                 for (int ks = 0; ks < 4; ks++) { G += p[ks * 32]; U += p[ks * 32 + 1]; }
                 const float val = G / (1.f + expf(-G)) * U;
                 uint16_t hi, lo;
-                split_hi_lo<true>(val, hi, lo);
+                split_hi_lo<F16>(val, hi, lo);
                 const int k = u >> 6, row = 8 * (u & 63) + lane;
                 uint16_t* dst = a.act + (size_t)k * 2 * EI + split_pos(row);
                 __stcg(dst, hi); __stcg(dst + EI, lo);
@@ -418,7 +446,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
         }
         __syncthreads();   // part[] of norm_split_row and xn / xcol are free: every warp is past P1 and P3 of this layer
-        if (l + 1 < a.n_layers) norm_split_row<true>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
+        if (l + 1 < a.n_layers) norm_split_row<F16>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
         asm volatile("cp.async.wait_all;" ::: "memory");   // the next layer's router rows and slot table
         __syncthreads();
     }

@@ -967,7 +967,7 @@ static int decode_stack_run(moexb_stack* s, void* stream) {
     auto by_w = [&]<int FMT>() {
         return s->router_dtype == MOEXB_F32 ? by_x.template operator()<FMT, float>() : by_x.template operator()<FMT, __half>();
     };
-    return s->fmt == FMT_SYM_F16 ? by_w.template operator()<FMT_SYM_F16>() : by_w.template operator()<FMT_SYM_F32>();
+    return s->fmt == FMT_SYM_F16 ? by_w.template operator()<FMT_SYM_F16>() : s->fmt == FMT_ZP ? by_w.template operator()<FMT_ZP>() : by_w.template operator()<FMT_SYM_F32>();
 }
 extern "C" {
 
@@ -992,7 +992,7 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     if (e != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_NOMEM, "stack_create: %s", cudaGetErrorString(e)); }
     // one token through residual blocks of resident symmetric-format experts: one cooperative launch for the whole stack
     // (a CTA of the cooperative kernel owns at most two router rows, so E + 1 <= 2 x SMs)
-    bool fused = c->fused_decode && T == 1 && residual && K <= DS_MAXK && n_layers <= DS_MAXLAYERS && layers[0]->n_routed + 1 <= 2 * c->sms && layers[0]->layout == MOEXB_LAYOUT_TILED && layers[0]->fmt != FMT_ZP;
+    bool fused = c->fused_decode && T == 1 && residual && K <= DS_MAXK && n_layers <= DS_MAXLAYERS && layers[0]->n_routed + 1 <= 2 * c->sms && layers[0]->layout == MOEXB_LAYOUT_TILED;
     for (int l = 0; l < n_layers && fused; l++)
         fused = layers[l]->n_local == layers[l]->n_routed && layers[l]->n_routed == layers[0]->n_routed && layers[l]->n_routed <= 256 &&
                 layers[l]->n_routed % 32 == 0 && layers[l]->router_dtype == layers[0]->router_dtype;

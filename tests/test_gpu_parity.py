@@ -532,7 +532,8 @@ def test_prefill_chunk_of_2048_tokens_both_kernel_families_agree():
     L.close(); c.close()
 
 
-@pytest.mark.parametrize("E,fmt,router,K", [(256, m.FMT_SYM_F16, np.float32, 8), (64, m.FMT_SYM_F32, np.float16, 8), (96, m.FMT_SYM_F16, np.float32, 3)])
+@pytest.mark.parametrize("E,fmt,router,K", [(256, m.FMT_SYM_F16, np.float32, 8), (64, m.FMT_SYM_F32, np.float16, 8), (96, m.FMT_SYM_F16, np.float32, 3),
+                                              (32, m.FMT_ZP, np.float16, 8)])
 def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
     """A one-token stack of residual blocks runs as a single cooperative kernel (grid barriers inside). Against the graph of
     per-layer kernels on the same layers: the result agrees within the parity bars (the two add the four K slices of a
