@@ -186,8 +186,9 @@ int moexb_ctx_set_pairs_per_pass(moexb_ctx* ctx, int pairs);
  * cooperative launch that walks all layers with grid barriers inside (default on); 0 = the graph of per-layer kernels.
  * Read when a stack is created. */
 int moexb_ctx_set_fused_decode(moexb_ctx* ctx, int on);
-/* Waits for the device and reads the error word of the streaming kernels: 0 = none; 1 / 2 = a consumer warp / the producer
- * warp gave up waiting on a pipeline barrier (every device-side wait is bounded). The word is cleared. */
+/* Waits for the device and reads the error word of the kernels: 0 = none; 1 / 2 = a consumer warp / the producer warp of a
+ * streaming kernel gave up waiting on a pipeline barrier, 3 = the same in the tensor-core grouped GEMM, 5 / 6 = the one-token
+ * stack kernel gave up at a grid barrier / on a weight copy (every device-side wait is bounded). The word is cleared. */
 int moexb_ctx_status(moexb_ctx* ctx, int* status);
 
 /* Allocates the image of one layer: n_routed experts (ids 0..n_routed-1) and the shared expert (id n_routed), each a

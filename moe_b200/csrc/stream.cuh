@@ -450,12 +450,14 @@ __device__ __forceinline__ int block_scan_1024(int v, int& total) {
     return inc - v + (w ? before : 0);
 }
 
-// Grouping and planning of a batch in one block of 1024 threads (one expert per thread; E <= 1024): the work of
-// group_plan_k for any batch size, and optionally a second sub-item list with another width (the tensor-core kernels take
-// 128 / parts pairs per tile for gate/up and 64 for down). Histogram of the T*K pairs in shared memory, block scans, then
+// Grouping and planning of a batch in one block of 1024 threads (one expert per thread; E <= 1024): the (token, rank) pairs
+// bucketed by expert (the host loop of moex.cu:1466-1486), the sub-items of at most maxp pairs that the streaming kernels
+// walk, and optionally a second sub-item list with another width (the tensor-core kernels take 128 / parts pairs per tile
+// for gate/up and 64 for down). Histogram of the T*K pairs in shared memory, block scans, then
 // every pair takes the next free place of its expert (an atomic cursor: the order of an expert's pairs is not the token
 // order and may change from run to run - every pair's result is independent of its place). List 1 keeps sub-items of more
-// than maxp / 2 pairs first (nsub[1] = their number); list 2 is in expert order. Shared expert as in group_plan_k.
+// than maxp / 2 pairs first (nsub[1] = their number); list 2 is in expert order. The shared expert (slot_table[E], when
+// gate_logits is given) gets the tokens [sh0, sh1) with weight sigmoid(gate logit), as the last item.
 __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
                                                       const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
                                                       moexb_pair* __restrict__ pairs, int* __restrict__ nitems,
