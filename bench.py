@@ -106,11 +106,18 @@ class ClockSampler:
 
 def cpu_block(o, blobs, W, X, threads, use_ref, fmt):
     """One residual MoE block on the CPU: router / top-k / grouping / combine from the C port (the reference has no CPU
-    code for them), expert math by the reference's CpuExperts::run_pairs (fp32) when oracle/_ref exists."""
+    code for them), expert math by the compiled reference when oracle/_ref exists: CpuExperts::run (its decode path, int8
+    activations) for one token, CpuExperts::run_pairs (fp32) for a batch."""
     T = X.shape[0]
     xn = o.rmsnorm(X)
     logits = o.router_logits(W, xn, T)
     idx, w = o.router_topk(logits, E, K, True, T, E + 1)
+    if use_ref and T == 1:
+        gate1 = 1.0 / (1.0 + np.exp(-logits[0, E]))
+        # run() takes at most 8 experts per call (its member scratch, cpu_expert.h:266): the routed 8, then the shared one
+        y = o.ref_run([blobs[e] for e in idx[0]], w[0], xn[0], zp=(fmt == o.FMT_ZP), threads=threads)
+        y = y + o.ref_run([blobs[E]], np.array([gate1], np.float32), xn[0], zp=(fmt == o.FMT_ZP), threads=threads)
+        return X + y[None, :]
     items, pt, pp, pw = o.group_pairs(idx, w, E)
     jobs = [(blobs[e], pt[s:s + c], pp[s:s + c], pw[s:s + c]) for e, s, c in items]
     gate = 1.0 / (1.0 + np.exp(-logits[:, E]))
@@ -148,7 +155,7 @@ def cpu_arm(workload, sample_layers, reps):
     per_layer = float(np.median(times[1:])) / nl
     return {"value": T / (per_layer * NL), "unit": "tokens/s", "cores": cores, "kind": "reference" if use_ref else "port",
             "sample": f"{nl} of {NL} layers x {T} tokens, median of {reps} passes, {per_layer * 1e3:.2f} ms/layer, "
-                      f"experts by {'CpuExperts::run_pairs (fp32) of the compiled reference' if use_ref else 'the C port'}, "
+                      f"experts by {('CpuExperts::run (int8 activations, the decode path)' if T == 1 else 'CpuExperts::run_pairs (fp32)') + ' of the compiled reference' if use_ref else 'the C port'}, "
                       f"router/top-k/combine by the C port; weights {nl * (E + 1) * o.expert_bytes(fmt) / 1e6:.0f} MB > L3"}, per_layer
 
 
@@ -173,8 +180,10 @@ def config_of(workload, n_gpus):
     T, NL, fmtname, xdt = WORKLOADS[workload]
     return {"workload": workload, "tokens": T, "layers": NL, "experts": f"{E} routed + 1 shared, top-{K}", "hidden": EH, "intermediate": EI,
             "expert_format": {"sym_f16": "i4_gs64 (fp16 group scales)", "zp": "GGUF Q4_K as zero-point blobs"}[fmtname],
-            "input_dtype": xdt, "router": "fp32", "l2": "weights of one step (%.1f GB) exceed L2; no flush needed" % (NL * (E + 1) * 1.671168e-3)
-            if NL > 1 else "429 MB of layer weights exceed L2",
+            "input_dtype": xdt, "router": "fp32",
+            # expert weights a step reads: the experts its tokens select (at least K + 1 per layer), far more than the 126 MB of L2
+            "l2": ("a step reads at least %.0f MB of expert weights from %.1f GB resident, more than L2; no flush needed"
+                   % (NL * (K + 1) * 1.671168, NL * (E + 1) * 1.671168e-3)) if NL > 1 else "429 MB of layer weights exceed L2",
             "parallelism": "single GPU" if n_gpus == 1 else f"expert parallel over {n_gpus} GPUs: {E // n_gpus} routed experts per rank, router and "
                            "shared expert replicated, one NCCL all-reduce of the partial outputs per layer"}
 
