@@ -409,23 +409,21 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
     for (int h = 0; h < 2; h++) {
         const int k0 = 1024 * h + 4 * threadIdx.x;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int rb = 0; rb < K; rb += 4) {  // four rows in flight, added in rank order
-            float4 y[4];
+        // the shared expert's row and the residual row are requested with the first batch of pair rows: one round trip
+        float4 ye = make_float4(0.f, 0.f, 0.f, 0.f), yx = ye;
+        if (extra) ye = *reinterpret_cast<const float4*>(extra + t * EH + k0);
+        if (x) yx = *reinterpret_cast<const float4*>(x + t * EH + k0);
+        for (int rb = 0; rb < K; rb += 8) {  // eight rows in flight, added in rank order
+            float4 y[8];
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < 8; u++)
                 if (rb + u < K && (have >> (rb + u) & 1)) y[u] = *reinterpret_cast<const float4*>(ypair + (t * K + rb + u) * EH + k0);
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < 8; u++)
                 if (rb + u < K && (have >> (rb + u) & 1)) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
         }
-        if (extra) {
-            const float4 y = *reinterpret_cast<const float4*>(extra + t * EH + k0);
-            acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
-        }
-        if (x) {
-            const float4 y = *reinterpret_cast<const float4*>(x + t * EH + k0);
-            acc.x = y.x + acc.x; acc.y = y.y + acc.y; acc.z = y.z + acc.z; acc.w = y.w + acc.w;
-        }
+        if (extra) { acc.x += ye.x; acc.y += ye.y; acc.z += ye.z; acc.w += ye.w; }
+        if (x) { acc.x = yx.x + acc.x; acc.y = yx.y + acc.y; acc.z = yx.z + acc.z; acc.w = yx.w + acc.w; }
         *reinterpret_cast<float4*>(out + t * EH + k0) = acc;
         v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
     }
