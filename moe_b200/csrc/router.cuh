@@ -253,9 +253,9 @@ template <typename WT, int WARPS, int TO, int TR, int NJ>
 __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int I,
                                                            int E, int K, int norm, int T, int* __restrict__ done, const TopkOut o) {
     extern __shared__ __align__(16) float xsm[];  // [TR][I]
-    // steps per batch of weights: the small tile takes all 16 steps of I = 2048 at once - requested before the wait, they
-    // arrive while the kernel before this one still runs
-    constexpr int U = TO <= 2 ? 16 : 4;
+    // steps per batch of weights: the small tile takes 8 (half of I = 2048) - the first batch, requested before the wait,
+    // arrives while the kernel before this one still runs
+    constexpr int U = TO <= 2 ? 8 : 4;
     const int O = E + 1, r0 = blockIdx.y * TR, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int o0 = (blockIdx.x * WARPS + warp) * TO;
     const WT* wr[TO];
