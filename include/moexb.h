@@ -243,11 +243,16 @@ typedef struct moexb_stack moexb_stack;
  * the reference's decoder block around its MoE, moex.cu:1082, 1092) for a fixed token count T and captures the whole
  * sequence of launches in one CUDA graph, as the reference captures its per-step graph (moex.cu:1165-1181).
  * Input [T][H] of x_dtype, output x_{n_layers} [T][H] f32. residual = 0 chains the plain layers instead,
- * x_{l+1} = moe_l(x_l) (one layer: exactly moexb_layer_forward). The layers must outlive the stack. */
+ * x_{l+1} = moe_l(x_l) (one layer: exactly moexb_layer_forward). The layers must outlive the stack.
+ * A residual stack for T = 1 is not a graph but one cooperative kernel over all layers (moexb_ctx_set_fused_decode):
+ * moexb_stack_run then issues a cudaMemsetAsync and a cooperative launch, which takes every SM of the device - launch it
+ * outside stream capture, and do not expect other kernels to run beside it. A context's stacks and layers share its
+ * workspace: their calls must not overlap on the GPU. */
 int moexb_stack_create(moexb_ctx* ctx, moexb_layer* const* layers, int n_layers, int T, int K, int x_dtype, int residual,
                        moexb_stack** out);
 int moexb_stack_destroy(moexb_stack* stack);
-/* Device buffers: copies X in, replays the graph, copies the result to out; all on `stream`, no synchronisation. */
+/* Device buffers: copies X in, replays the graph (or launches the one-token kernel), copies the result to out; all on
+ * `stream`, no synchronisation. */
 int moexb_stack_run(moexb_stack* stack, const void* X, float* out, void* stream);
 /* Host buffers (pinned memory recommended): host->device copy of X, the graph, device->host copy of the result, then
  * waits for the stream. This is the call an engine that keeps activations on the host makes once per step. */
