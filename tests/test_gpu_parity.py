@@ -575,3 +575,57 @@ def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
     for L in layers:
         L.close()
     c.close()
+
+
+def test_full_size_stacks_of_40_layers():
+    """BASELINE's full sizes: 40 layers x 257 experts (17 GB resident). The 64-token graph replays to exactly what 40 chained
+    layer calls give (bit for bit: the same kernels, and the graph adds only launch overlap); its first layer matches the
+    oracle (ids identical, outputs inside the bars); the one-token stack as a cooperative kernel agrees with the graph of
+    per-layer kernels inside the bars; nothing sets the error word."""
+    E, K, NL = 256, 8, 40
+    rng = np.random.default_rng(40)
+    c = m.Context(0, max_tokens=64, max_experts=E, top_k=K)
+    layers, Ws = [], []
+    for l in range(NL):
+        L = m.Layer(c, m.FMT_SYM_F16, E)
+        L.fill_synth(0, l)
+        W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
+        L.set_router(W)
+        layers.append(L); Ws.append(W)
+    X = rng.standard_normal((64, 2048)).astype(np.float32)
+    # 64 tokens: graph == chained calls
+    stack = m.Stack(c, layers, 64, K, m.F32)
+    y_graph = stack.run(dev(X)).cpu().numpy().copy()
+    stack.close()
+    x = dev(X)
+    bufs = [torch.empty(64, 2048, device=DEV), torch.empty(64, 2048, device=DEV)]
+    idx0 = torch.empty(64, K, dtype=torch.int32, device=DEV)
+    first = None
+    for l, L in enumerate(layers):
+        x = L.forward(x, 64, K, out=bufs[l & 1], idx=idx0 if l == 0 else None, flags=2)
+        if l == 0:
+            first = x.cpu().numpy().copy()
+    assert c.status() == 0
+    assert np.isfinite(y_graph).all()
+    assert np.array_equal(y_graph, x.cpu().numpy())
+    # the first block against the oracle
+    host0 = [m.synth_expert_host(m.FMT_SYM_F16, 0, 0, e) for e in range(E + 1)]
+    moe, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, host0, Ws[0], o.rmsnorm(X), K)
+    assert np.array_equal(idx0.cpu().numpy(), ri)
+    check_ffn(first, X + moe, m.FMT_SYM_F16, "first of 40 blocks, 64 tokens")
+    # one token: cooperative kernel against the graph of per-layer kernels
+    x1 = X[:1]
+    c.set_fused_decode(False)
+    g = m.Stack(c, layers, 1, K, m.F32)
+    y_g = g.run(dev(x1)).cpu().numpy().copy()
+    g.close()
+    c.set_fused_decode(True)
+    f = m.Stack(c, layers, 1, K, m.F32)
+    assert f.kernel_count == 1
+    y_f = f.run(dev(x1)).cpu().numpy().copy()
+    f.close()
+    assert c.status() == 0
+    check_ffn(y_f, y_g, m.FMT_SYM_F16, "one token x 40 layers, cooperative kernel against the graph")
+    for L in layers:
+        L.close()
+    c.close()
