@@ -7,8 +7,8 @@
 // being passed through global memory. Per layer:
 //   P1  router logits: CTA b computes rows b and b + grid of W . xn (one warp per row, the pinned summation order of
 //       gemv_rows_k; the rows were copied into shared memory during the layer before) -> logits[E + 1] in global memory.                                        -- grid barrier --
-//   P2  every CTA: which K experts - thread i ranks logit i among all of them (how many are larger, ties to the lower
-//       index; 256 threads, no sequential rounds) and the K with rank < K are the selection, in rank order. The softmax
+//   P2  every CTA: which K experts - the logits that reach the K-th largest warp maximum (a few dozen) are compacted and
+//       ranked among themselves (how many are larger, ties to the lower index; no sequential rounds); rank < K = selected. The softmax
 //       weights are off this path: the last CTA takes no expert work and instead runs topk_token on the same logits
 //       (the same experts by construction) and publishes the K + 1 weights, which are first needed in P5.
 //   P3  gate/up: (expert, row tile of 8 gate + 8 up rows) units, two per CTA pass, the four K slices of a unit on four
@@ -152,7 +152,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     __shared__ const uint8_t* s_slot[DS_MAXK + 1];
     __shared__ float s_wt[DS_MAXK + 1];
     __shared__ int s_abort;
-    __shared__ __align__(16) unsigned s_keys[DS_THREADS];   // the logits as ordered integer keys (0 beyond E)
+    __shared__ unsigned s_keys[DS_THREADS];   // the candidates' logits as ordered integer keys
+    __shared__ int s_cidx[DS_THREADS];        // and their expert ids
+    __shared__ unsigned s_wmax[DS_WARPS];
+    __shared__ int s_wcnt[DS_WARPS];
     __shared__ int s_idx2[DS_MAXK];
     __shared__ const uint8_t* s_slot2[DS_MAXK + 1];
     __shared__ DecodeLayer s_layers[DS_MAXLAYERS];   // the layer descriptors: no global round trip when a layer is staged
@@ -301,37 +304,42 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             if (lane == 0) __stcg(a.logits + r, acc);
         }
         if (!(ok = grid_barrier())) break;
-        // ---- P2: selection (every CTA): the rank of logit i = how many logits come before it (larger, or equal with a lower
-        // index - the order of topk_token's rounds); warp w compares with >= against the blocks of 32 below it, with > against
-        // those above, and index by index inside its own ----
+        // ---- P2: selection (every CTA). No sequential rounds: (1) a threshold that at least K logits reach - the K-th largest of
+        // the warps' maxima; (2) the logits at or above it (a few dozen) are compacted into a list; (3) list entry j counts the
+        // entries that come before it (larger, or equal with a lower expert id - the order of topk_token's rounds): those with
+        // fewer than K before them are the selection, the count is their rank ----
         {
+            const int nw = E >> 5;   // warps that hold logits
             unsigned key = 0u;
             if (tid < E) { const float x = __ldcg(a.logits + tid); key = f2key(x != x ? -INFINITY : x); }
-            s_keys[tid] = key;
+            const unsigned wmax = __reduce_max_sync(0xffffffffu, key);
+            if (lane == 0) s_wmax[warp] = wmax;
             __syncthreads();
-            if (tid < E) {
-                const uint4* kv = reinterpret_cast<const uint4*>(s_keys);
+            unsigned tau = 0u;   // fewer warps than K: every logit is a candidate
+            if (nw >= K) {
+                for (int w2 = 0; w2 < nw; w2++) {   // the warp maximum with exactly K - 1 maxima before it
+                    const unsigned m2 = s_wmax[w2];
+                    int before = 0;
+                    for (int w3 = 0; w3 < nw; w3++) before += s_wmax[w3] > m2 || (s_wmax[w3] == m2 && w3 < w2);
+                    if (before == K - 1) tau = m2;
+                }
+            }
+            const bool cand = tid < E && key >= tau;
+            const unsigned mask = __ballot_sync(0xffffffffu, cand);
+            if (lane == 0) s_wcnt[warp] = __popc(mask);
+            __syncthreads();
+            int off = 0, C = 0;
+            for (int w2 = 0; w2 < DS_WARPS; w2++) { const int c2 = s_wcnt[w2]; if (w2 < warp) off += c2; C += c2; }
+            if (cand) { const int at = off + __popc(mask & ((1u << lane) - 1)); s_keys[at] = key; s_cidx[at] = tid; }
+            __syncthreads();
+            if (tid < C) {   // entries are in ascending expert order, so "lower expert id" is "earlier in the list"
+                const unsigned kj = s_keys[tid];
                 int cnt = 0;
-                for (int blk = 0; blk < DS_THREADS / 32; blk++) {
-                    if (blk == warp) continue;
-                    const bool below = blk < warp;
-#pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        const uint4 k4 = kv[blk * 8 + q];
-                        if (below) cnt += (k4.x >= key) + (k4.y >= key) + (k4.z >= key) + (k4.w >= key);
-                        else cnt += (k4.x > key) + (k4.y > key) + (k4.z > key) + (k4.w > key);
-                    }
-                }
-#pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    const uint4 k4 = kv[warp * 8 + q];
-                    const int j = 4 * q;   // lanes j .. j + 3 of this warp
-                    cnt += (k4.x > key || (k4.x == key && j < lane)) + (k4.y > key || (k4.y == key && j + 1 < lane)) +
-                           (k4.z > key || (k4.z == key && j + 2 < lane)) + (k4.w > key || (k4.w == key && j + 3 < lane));
-                }
+                for (int c2 = 0; c2 < C; c2++) { const unsigned k2 = s_keys[c2]; cnt += k2 > kj || (k2 == kj && c2 < tid); }
                 if (cnt < K) {
-                    s_idx[cnt] = tid; s_slot[cnt] = table[tid];
-                    if (b == 0 && a.idx_out) a.idx_out[(size_t)l * K + cnt] = tid;
+                    const int e = s_cidx[tid];
+                    s_idx[cnt] = e; s_slot[cnt] = table[e];
+                    if (b == 0 && a.idx_out) a.idx_out[(size_t)l * K + cnt] = e;
                 }
             }
             if (tid == 0) s_slot[K] = table[E];
