@@ -182,7 +182,7 @@ int moexb_ctx_set_prefill_min_tokens(moexb_ctx* ctx, int tokens);
  * symmetric formats): 8 (default; an expert with 5-8 pairs is unpacked once) or 4. Smaller batches and zero-point blobs
  * always take 4. */
 int moexb_ctx_set_pairs_per_pass(moexb_ctx* ctx, int pairs);
-/* A stack of residual blocks for ONE token (TILED layers, symmetric formats, every expert held here) runs as a single
+/* A stack of residual blocks for ONE token (TILED layers, every expert held here) runs as a single
  * cooperative launch that walks all layers with grid barriers inside (default on); 0 = the graph of per-layer kernels.
  * Read when a stack is created. */
 int moexb_ctx_set_fused_decode(moexb_ctx* ctx, int on);
