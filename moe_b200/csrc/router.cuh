@@ -318,13 +318,13 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
 // The same for a prefill chunk, register-tiled. A block of 8 warps owns 32 tokens x 16 outputs; warp (wm, wn) the 8 tokens
 // 8*wm.. and the 8 outputs 8*wn.., every lane the same 4 of each 128 inputs as in gemv_rows_k, so a lane holds 64 partial
 // sums and each (token, output) sum is formed in the pinned order. Token rows and weight rows come through shared memory in
-// chunks of 512 inputs (cp.async, two stages): per 128 inputs a warp reads 16 x 16 bytes per lane and does 256 fused
+// chunks of 256 inputs (cp.async, two stages; two blocks per SM): per 128 inputs a warp reads 16 x 16 bytes per lane and does 256 fused
 // multiply-adds, which makes the kernel FMA-bound where route_gemm_k is bound by re-reading the weights from L2. The last
 // block of a token tile selects the experts of its 32 tokens. grid (ceil((E + 1) / 16), ceil(T / 32)); I = 2048.
-constexpr int RG2_TM = 32, RG2_TN = 16, RG2_KC = 512;
+constexpr int RG2_TM = 32, RG2_TN = 16, RG2_KC = 256;
 template <typename WT> constexpr int rg2_stage_bytes() { return RG2_TM * RG2_KC * 4 + RG2_TN * RG2_KC * (int)sizeof(WT); }
 template <typename WT, int NJ>
-__global__ void __launch_bounds__(256) route_gemm2_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int E, int K,
+__global__ void __launch_bounds__(256, 2) route_gemm2_k(const WT* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int E, int K,
                                                      int norm, int T, int* __restrict__ done, const TopkOut o) {
     constexpr int I = EH, NCH = I / RG2_KC, STAGE = rg2_stage_bytes<WT>();
     extern __shared__ __align__(16) uint8_t rsm[];   // 2 stages x ([32 tokens][512] f32 | [16 outputs][512] WT)
