@@ -372,6 +372,10 @@ def main():
         r["down"].update({"achieved": flops_dn / (per_launch_us["down"] * 1e-6) / 1e12, "algorithmic_flops_per_launch": flops_dn})
         r["whole_layer"].update({"flops": 1.5 * flops_gu + 2.0 * T * (E + 1) * EH,
                                  "tflops": (1.5 * flops_gu + 2.0 * T * (E + 1) * EH) / (ms_step * 1e-3 / NL) / 1e12})
+    # the same fraction against the nominal figures (HBM3e 8 TB/s, dense bf16 2,250 TFLOP/s), for context
+    r_ = line["roofline"]
+    r_["nominal_peak"] = 2250.0 if r_["unit"] == "TFLOP/s" else 8000.0
+    r_["frac_of_nominal"] = r_["achieved"] / r_["nominal_peak"]
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_arm(args.workload, 2 if T <= 64 else 1, 3)
     if rank == 0:
