@@ -214,6 +214,32 @@ void* moexb_layer_router(moexb_layer* layer);
 /* Fills all held experts with synthetic weights (moexb_synth_experts with this layer's format). */
 int moexb_layer_fill_synth(moexb_layer* layer, unsigned seed, int layer_index, void* stream);
 
+/* ---- GGUF ingest ------------------------------------------------------------------------------------------------------ */
+
+/* A GGUF model file (versions 2 and 3), mapped read-only with its tensor directory parsed; needs no GPU. Stands where
+ * the reference's importer opens the file (gguf.h:345-462, struct Gguf: magic, version, metadata, general.alignment,
+ * tensor directory, every length checked against the file size). A file that is truncated, corrupt or not GGUF gives
+ * MOEXB_ERR_ARG with the reason in moexb_last_error(). */
+typedef struct moexb_gguf moexb_gguf;
+int moexb_gguf_open(const char* path, moexb_gguf** out);
+int moexb_gguf_close(moexb_gguf* g);
+int moexb_gguf_tensor_count(const moexb_gguf* g);
+const char* moexb_gguf_tensor_name(const moexb_gguf* g, int i); /* null when i is out of range */
+/* One tensor by name (Gguf::at, gguf.h:373-377): ggml type, dimensions ne[0..3] (ne[0] = row length, unused ones 1),
+ * a pointer into the mapping and the tensor's size in bytes (null / 0 for a ggml type whose block size is not known
+ * here). Any out pointer may be null. */
+int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_dims, long long* ne, const void** data,
+                      long long* nbytes);
+/* Fills a MOEXB_FMT_ZP layer from block `block` of the file: blk.N.ffn_{gate,up,down}_exps.weight (Q4_K, shapes
+ * [H, I, E], [H, I, E], [I, H, E] with E = the layer's n_routed) for the routed experts the layer holds, re-packed on
+ * the device exactly as moexb_q4k_to_zp does; the role of gg_experts (gguf.h:666-694) without the pass through a
+ * container on disk. Also, when present: the shared expert from blk.N.ffn_{gate,up,down}_shexp.weight if all three
+ * are Q4_K, the router rows from blk.N.ffn_gate_inp.weight and the shared expert's gate vector from
+ * blk.N.ffn_gate_inp_shexp.weight (F32, F16 or BF16, converted to the layer's router dtype). *loaded (may be null)
+ * receives a bit set: 1 routed experts, 2 shared expert, 4 router rows, 8 shared gate vector; what a bit does not
+ * name is left as it was. Expert tensors of another ggml type give MOEXB_ERR_UNSUPPORTED. Synchronous. */
+int moexb_layer_load_gguf(moexb_layer* layer, const moexb_gguf* g, int block, int* loaded);
+
 /* One MoE layer for T tokens: router logits -> top-K softmax (renormalised) -> routed experts -> rank-order combine ->
  * + sigmoid(gate) * shared expert. X [T][H] of x_dtype; out [T][H] f32. The sequence the reference runs at
  * moex.cu:1093-1107 (decode) and moex.cu:1414-1415, 1466-1617 (chunk). Optional outputs (may be null): idx_out [T][K],

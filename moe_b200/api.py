@@ -4,6 +4,7 @@ Every function forwards to the C ABI with raw device pointers on torch's current
 follow the reference functions named in include/moexb.h. Nothing here computes: without the CUDA library these raise.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -184,6 +185,35 @@ class Context:
             self.h = None
 
 
+class Gguf:
+    """moexb_gguf: a GGUF model file mapped read-only, with its tensor directory (the reference's struct Gguf,
+    gguf.h:345-462). Needs no GPU."""
+
+    def __init__(self, path):
+        h = C.c_void_p()
+        check(lib().moexb_gguf_open(os.fsencode(path), C.byref(h)))
+        self.h = h
+
+    def names(self):
+        return [lib().moexb_gguf_tensor_name(self.h, i).decode() for i in range(lib().moexb_gguf_tensor_count(self.h))]
+
+    def tensor(self, name):
+        """(ggml type, shape ne[0..n_dims-1] with ne[0] the row length, bytes as a numpy uint8 view of the mapping or
+        None when the type's block size is unknown). The view is valid until close()."""
+        ty, nd, nb, data = C.c_int(0), C.c_int(0), C.c_longlong(0), C.c_void_p()
+        ne = (C.c_longlong * 4)()
+        check(lib().moexb_gguf_tensor(self.h, name.encode(), C.byref(ty), C.byref(nd), ne, C.byref(data), C.byref(nb)))
+        raw = None
+        if data.value:
+            raw = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(nb.value,))
+        return ty.value, tuple(ne[: nd.value]), raw
+
+    def close(self):
+        if self.h:
+            lib().moexb_gguf_close(self.h)
+            self.h = None
+
+
 class Layer:
     """moexb_layer: one MoE layer resident in HBM (routed experts [first_local, first_local+n_local), shared expert,
     router with the shared gate vector as its last row)."""
@@ -210,6 +240,13 @@ class Layer:
 
     def fill_synth(self, seed, layer_index):
         check(lib().moexb_layer_fill_synth(self.h, seed, layer_index, _stream()))
+
+    def load_gguf(self, gguf, block):
+        """moexb_layer_load_gguf: block `block` of an open Gguf into this MOEXB_FMT_ZP layer. Returns the bit set of
+        what the file provided (1 routed experts, 2 shared expert, 4 router rows, 8 shared gate vector)."""
+        got = C.c_int(0)
+        check(lib().moexb_layer_load_gguf(self.h, gguf.h, block, C.byref(got)))
+        return got.value
 
     def upload_blob(self, e, blob):
         """Copy a host blob (numpy uint8 of expert_bytes(fmt)) into expert e's place."""

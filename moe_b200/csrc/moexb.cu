@@ -8,6 +8,7 @@
 #include "tiled.cuh"
 #include "prefill.cuh"
 #include "decode_stack.cuh"
+#include "gguf_ingest.h"
 
 #include <cmath>
 #include <cstdarg>
@@ -546,6 +547,142 @@ int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void*
         if (rc == MOEXB_OK) rc = to_layer_layout(L, c->staging, L->image + (size_t)i * eb, n, S(stream));
         if (rc != MOEXB_OK) return rc;
     }
+    return MOEXB_OK;
+}
+
+// ---- GGUF ingest ----------------------------------------------------------------------------------------------------------
+
+int moexb_gguf_open(const char* path, moexb_gguf** out) {
+    REQUIRE(path && out, "gguf_open: null pointer");
+    std::string err;
+    moexb_gguf* g = gguf_open(path, err);
+    if (!g) return fail(MOEXB_ERR_ARG, "gguf_open: %s", err.c_str());
+    *out = g;
+    return MOEXB_OK;
+}
+
+int moexb_gguf_close(moexb_gguf* g) {
+    delete g;
+    return MOEXB_OK;
+}
+
+int moexb_gguf_tensor_count(const moexb_gguf* g) { return g ? (int)g->tensors.size() : 0; }
+
+const char* moexb_gguf_tensor_name(const moexb_gguf* g, int i) {
+    return g && i >= 0 && i < (int)g->tensors.size() ? g->tensors[i].name.c_str() : nullptr;
+}
+
+int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_dims, long long* ne, const void** data, long long* nbytes) {
+    REQUIRE(g && name, "gguf_tensor: null pointer");
+    const GgufTensor* t = g->find(name);
+    if (!t) return fail(MOEXB_ERR_ARG, "tensor %s is missing from the GGUF", name);
+    if (type) *type = (int)t->type;
+    if (n_dims) *n_dims = t->n_dims;
+    if (ne) for (int d = 0; d < 4; d++) ne[d] = t->ne[d];
+    if (data) *data = t->data;
+    if (nbytes) *nbytes = t->nbytes;
+    return MOEXB_OK;
+}
+
+}  // extern "C"
+
+// A Q4_K tensor of the block with the shape the path needs, or an error naming what differs.
+static int gguf_expect(const moexb_gguf* g, const std::string& name, std::initializer_list<long long> ne, const GgufTensor** out) {
+    const GgufTensor* t = g->find(name);
+    if (!t) return fail(MOEXB_ERR_ARG, "tensor %s is missing from the GGUF", name.c_str());
+    if (t->type != GGML_Q4_K)
+        return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: %s has ggml type %u; only Q4_K (12) expert tensors are carried over", name.c_str(), t->type);
+    bool same = t->n_dims == (int)ne.size();
+    int d = 0;
+    for (long long v : ne) same = same && t->ne[d++] == v;
+    if (!same) return fail(MOEXB_ERR_ARG, "tensor %s has shape [%lld, %lld, %lld, %lld] (%d dimensions), not the one this layer needs",
+                           name.c_str(), t->ne[0], t->ne[1], t->ne[2], t->ne[3], t->n_dims);
+    *out = t;
+    return MOEXB_OK;
+}
+
+// One router row source (F32, F16 or BF16, `n` values) into the layer's router dtype at dst (host).
+static bool gguf_router_rows(const GgufTensor* t, long long n, int router_dtype, void* dst) {
+    if (t->type != GGML_F32 && t->type != GGML_F16 && t->type != GGML_BF16) return false;
+    for (long long i = 0; i < n; i++) {
+        float v;
+        if (t->type == GGML_F32) memcpy(&v, t->data + 4 * i, 4);
+        else {
+            uint16_t h; memcpy(&h, t->data + 2 * i, 2);
+            if (t->type == GGML_F16) { __half hh; memcpy(&hh, &h, 2); v = __half2float(hh); }
+            else { const uint32_t u = (uint32_t)h << 16; memcpy(&v, &u, 4); }
+        }
+        if (router_dtype == MOEXB_F32) static_cast<float*>(dst)[i] = v;
+        else static_cast<__half*>(dst)[i] = __float2half_rn(v);
+    }
+    return true;
+}
+
+extern "C" {
+
+int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* loaded) {
+    REQUIRE(L && g, "layer_load_gguf: null pointer");
+    REQUIRE(block >= 0, "layer_load_gguf: block %d", block);
+    if (loaded) *loaded = 0;
+    if (L->fmt != FMT_ZP) return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: Q4_K tensors load into a MOEXB_FMT_ZP layer (this one has format %d)", L->fmt);
+    const std::string p = "blk." + std::to_string(block) + ".";
+    const long long E = L->n_routed;
+    const GgufTensor* t[3];
+    int rc = gguf_expect(g, p + "ffn_gate_exps.weight", {EH, EI, E}, &t[0]);
+    if (rc == MOEXB_OK) rc = gguf_expect(g, p + "ffn_up_exps.weight", {EH, EI, E}, &t[1]);
+    if (rc == MOEXB_OK) rc = gguf_expect(g, p + "ffn_down_exps.weight", {EI, EH, E}, &t[2]);
+    if (rc != MOEXB_OK) return rc;
+    moexb_ctx* c = L->ctx;
+    CUDA_TRY(cudaSetDevice(c->device));
+    constexpr size_t PART = (size_t)EH * EI / 256 * 144;  // raw bytes of one expert's gate, up or down
+    const size_t eb = expert_bytes(FMT_ZP);
+    static_assert(3 * PART <= (size_t)Q_BYTES + 2 * CHUNKS + CHUNKS / 8 * 4, "raw Q4_K of one expert fits a staging blob");
+    constexpr int HALF = STAGING_BLOBS / 2;  // raw tensors in the first half of the staging buffer, blobs in the second
+    // src[k] = the three raw tensors of the experts to convert, `n` of them, into the layer from slot `dst0` on
+    auto convert = [&](const uint8_t* const* src, int n, uint8_t* dst) -> int {
+        for (int i = 0; i < n; i++)
+            for (int k = 0; k < 3; k++)
+                CUDA_TRY(cudaMemcpyAsync(c->staging + i * eb + k * PART, src[3 * i + k], PART, cudaMemcpyHostToDevice, nullptr));
+        for (int i = 0; i < n; i++) {
+            const uint8_t* raw = c->staging + i * eb;
+            q4k_to_zp_k<<<(unsigned)((CHUNKS / 8 + 127) / 128), 128>>>(raw, raw + PART, raw + 2 * PART, c->staging + (HALF + i) * eb);
+            LAUNCHED("q4k_to_zp");
+        }
+        return to_layer_layout(L, c->staging + HALF * eb, dst, n, nullptr);
+    };
+    const uint8_t* src[3 * HALF];
+    for (int i = 0; i < L->n_local; i += HALF) {
+        const int n = min(HALF, L->n_local - i);
+        for (int j = 0; j < n; j++)
+            for (int k = 0; k < 3; k++) src[3 * j + k] = t[k]->data + (size_t)(L->first_local + i + j) * PART;
+        rc = convert(src, n, L->image + (size_t)i * eb);
+        if (rc != MOEXB_OK) return rc;
+        CUDA_TRY(cudaStreamSynchronize(nullptr));
+    }
+    int got = L->n_local ? 1 : 0;
+    // the shared expert, when the file holds it as Q4_K too
+    const GgufTensor *sg = g->find(p + "ffn_gate_shexp.weight"), *su = g->find(p + "ffn_up_shexp.weight"), *sd = g->find(p + "ffn_down_shexp.weight");
+    if (sg && su && sd && sg->type == GGML_Q4_K && su->type == GGML_Q4_K && sd->type == GGML_Q4_K && sg->n_dims == 2 && su->n_dims == 2 &&
+        sd->n_dims == 2 && sg->ne[0] == EH && sg->ne[1] == EI && su->ne[0] == EH && su->ne[1] == EI && sd->ne[0] == EI && sd->ne[1] == EH) {
+        src[0] = sg->data; src[1] = su->data; src[2] = sd->data;
+        rc = convert(src, 1, L->image + (size_t)L->n_local * eb);
+        if (rc != MOEXB_OK) return rc;
+        CUDA_TRY(cudaStreamSynchronize(nullptr));
+        got |= 2;
+    }
+    // router rows and the shared expert's gate vector
+    const GgufTensor *rt = g->find(p + "ffn_gate_inp.weight"), *rs = g->find(p + "ffn_gate_inp_shexp.weight");
+    const size_t esz = L->router_dtype == MOEXB_F32 ? 4 : 2;
+    std::vector<uint8_t> rows((size_t)E * EH * esz);
+    if (rt && rt->n_dims == 2 && rt->ne[0] == EH && rt->ne[1] == E && rt->data && gguf_router_rows(rt, E * EH, L->router_dtype, rows.data())) {
+        CUDA_TRY(cudaMemcpy(L->router, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+        got |= 4;
+    }
+    if (rs && rs->ne[0] == EH && rs->nbytes == rs->row_bytes && rs->data && gguf_router_rows(rs, EH, L->router_dtype, rows.data())) {
+        CUDA_TRY(cudaMemcpy(static_cast<uint8_t*>(L->router) + (size_t)E * EH * esz, rows.data(), EH * esz, cudaMemcpyHostToDevice));
+        got |= 8;
+    }
+    if (loaded) *loaded = got;
     return MOEXB_OK;
 }
 

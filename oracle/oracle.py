@@ -206,6 +206,19 @@ def ref_gg_zp_row(gg_type, src, cols):
     return qb, cs, sup
 
 
+def ref_gguf_tensor(path, name):
+    """The reference's own GGUF reader (struct Gguf, gguf.h:345-462) on `path`: (shape, ggml type, file offset of the
+    data or -1, bytes per row) of one tensor; None if absent; raises ValueError with the reader's message if it throws."""
+    ne = (C.c_longlong * 4)(); ty = C.c_uint(0); off = C.c_longlong(0); rb = C.c_longlong(0)
+    err = C.create_string_buffer(256)
+    nd = ref().ref_gguf_tensor(os.fsencode(path), name.encode(), ne, C.byref(ty), C.byref(off), C.byref(rb), err, 256)
+    if nd == -2:
+        return None
+    if nd < 0:
+        raise ValueError(err.value.decode())
+    return tuple(ne[:nd]), ty.value, off.value, rb.value
+
+
 def sym_f16_to_f32(blob):
     """An FMT_SYM_F16 blob re-encoded as FMT_SYM_F32 (same values): the layout the reference's CPU code reads."""
     out = np.empty(Q_BYTES + CHUNKS // 2 * 4, np.uint8)

@@ -63,4 +63,25 @@ void ref_gg_zp_row(unsigned type, const uint8_t* src, int cols, uint8_t* qb, uin
 float ref_gg_zp_at(const uint8_t* qb, const uint8_t* cs, const uint16_t* sup, int i) { return gg_zp_at(qb, cs, sup, i); }
 int ref_has_avxvnni() { return cpu_has_avxvnni() ? 1 : 0; }
 
+// The reference's own GGUF reader (struct Gguf, gguf.h:345-462) on a file: for one tensor its dimensions, ggml type,
+// the offset of its data from the start of the file and the bytes of one row. Returns the number of dimensions, -1
+// when the reader throws (message copied to err), -2 when the tensor is absent. The mapping stays for the process
+// lifetime, as in the reference.
+int ref_gguf_tensor(const char* path, const char* name, long long* ne, unsigned* type, long long* offset, long long* row_bytes,
+                    char* err, int err_len) {
+    try {
+        Gguf g(path);
+        if (!g.has(name)) return -2;
+        const Gguf::Tensor& t = g.at(name);
+        for (size_t d = 0; d < t.ne.size(); d++) ne[d] = t.ne[d];
+        *type = t.type;
+        *offset = t.data ? (long long)(t.data - g.base) : -1;
+        *row_bytes = t.row_bytes;
+        return (int)t.ne.size();
+    } catch (const std::exception& e) {
+        if (err && err_len > 0) { strncpy(err, e.what(), err_len - 1); err[err_len - 1] = 0; }
+        return -1;
+    }
+}
+
 }
