@@ -240,6 +240,32 @@ int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_d
  * name is left as it was. Expert tensors of another ggml type give MOEXB_ERR_UNSUPPORTED. Synchronous. */
 int moexb_layer_load_gguf(moexb_layer* layer, const moexb_gguf* g, int block, int* loaded);
 
+/* ---- safetensors container ingest ---------------------------------------------------------------------------------- */
+
+/* One safetensors file of the reference engine's model container (one per layer), mapped read-only with its JSON
+ * directory parsed; needs no GPU. Stands where the reference indexes and maps the files (st.h:19-111, struct
+ * Container: index(), at(), map()). A malformed header or offsets outside the file give MOEXB_ERR_ARG with the reason
+ * in moexb_last_error() (the reference prints and exits). */
+typedef struct moexb_st moexb_st;
+int moexb_st_open(const char* path, moexb_st** out);
+int moexb_st_close(moexb_st* s);
+int moexb_st_tensor_count(const moexb_st* s);
+const char* moexb_st_tensor_name(const moexb_st* s, int i); /* null when i is out of range */
+/* One tensor by name (Container::at / map, st.h:30-35, 64-84): dtype string (buffer of 8 chars), number of dimensions,
+ * shape (up to 8 values), a pointer into the mapping and the size in bytes. Any out pointer may be null. */
+int moexb_st_tensor(const moexb_st* s, const char* name, char* dtype, int* n_dims, long long* shape, const void** data,
+                    long long* nbytes);
+/* Fills a layer from a container file: for every routed expert e the layer holds, `<prefix>mlp.experts.<e>.merged_weight`
+ * (the packed nibbles) and `<prefix>mlp.experts.<e>.qs` (the scale part) as the engine reads them (moex.cu:933-939), with
+ * prefix = "model.layers.<l>." or "mtp.layers.0."; F32 `qs` for the symmetric formats, U8 `qs` for MOEXB_FMT_ZP
+ * (moex.cu:221-225). A MOEXB_FMT_SYM_F16 layer takes F32 scales only if each of them is an fp16 value (nothing is
+ * rounded on the way in); otherwise, and for a `qs` of the other format, MOEXB_ERR_UNSUPPORTED. Also, when present,
+ * the router rows `<prefix>mlp.gate.weight` [E][H] and the shared expert's gate vector
+ * `<prefix>mlp.shared_expert_gate.weight` [1][H] (F32, F16 or BF16), converted to the layer's router dtype. The
+ * container holds the shared expert as dense matrices (moex.cu:768), not as an expert blob: it is left as it was.
+ * *loaded (may be null): bit 1 routed experts, 4 router rows, 8 shared gate vector. Synchronous. */
+int moexb_layer_load_st(moexb_layer* layer, const moexb_st* s, const char* prefix, int* loaded);
+
 /* One MoE layer for T tokens: router logits -> top-K softmax (renormalised) -> routed experts -> rank-order combine ->
  * + sigmoid(gate) * shared expert. X [T][H] of x_dtype; out [T][H] f32. The sequence the reference runs at
  * moex.cu:1093-1107 (decode) and moex.cu:1414-1415, 1466-1617 (chunk). Optional outputs (may be null): idx_out [T][K],

@@ -76,6 +76,12 @@ SIGNATURES = {
     "moexb_gguf_tensor_name": (C.c_char_p, [_vp, _i]),
     "moexb_gguf_tensor": (_i, [_vp, C.c_char_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll), C.POINTER(_vp), C.POINTER(_ll)]),
     "moexb_layer_load_gguf": (_i, [_vp, _vp, _i, C.POINTER(_i)]),
+    "moexb_st_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "moexb_st_close": (_i, [_vp]),
+    "moexb_st_tensor_count": (_i, [_vp]),
+    "moexb_st_tensor_name": (C.c_char_p, [_vp, _i]),
+    "moexb_st_tensor": (_i, [_vp, C.c_char_p, C.c_char_p, C.POINTER(_i), C.POINTER(_ll), C.POINTER(_vp), C.POINTER(_ll)]),
+    "moexb_layer_load_st": (_i, [_vp, _vp, C.c_char_p, C.POINTER(_i)]),
     "moexb_layer_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
     "moexb_layer_forward_ep": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moexb_ep_residual_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),

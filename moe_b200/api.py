@@ -214,6 +214,35 @@ class Gguf:
             self.h = None
 
 
+class SafeTensors:
+    """moexb_st: one safetensors file of the reference engine's model container, mapped read-only (the reference's
+    struct Container, st.h:19-111). Needs no GPU."""
+
+    def __init__(self, path):
+        h = C.c_void_p()
+        check(lib().moexb_st_open(os.fsencode(path), C.byref(h)))
+        self.h = h
+
+    def names(self):
+        return [lib().moexb_st_tensor_name(self.h, i).decode() for i in range(lib().moexb_st_tensor_count(self.h))]
+
+    def tensor(self, name):
+        """(dtype string, shape, bytes as a numpy uint8 view of the mapping, valid until close())."""
+        dt = C.create_string_buffer(8)
+        nd, nb, data = C.c_int(0), C.c_longlong(0), C.c_void_p()
+        shape = (C.c_longlong * 8)()
+        check(lib().moexb_st_tensor(self.h, name.encode(), dt, C.byref(nd), shape, C.byref(data), C.byref(nb)))
+        raw = np.empty(0, np.uint8)
+        if nb.value:
+            raw = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(nb.value,))
+        return dt.value.decode(), tuple(shape[: nd.value]), raw
+
+    def close(self):
+        if self.h:
+            lib().moexb_st_close(self.h)
+            self.h = None
+
+
 class Layer:
     """moexb_layer: one MoE layer resident in HBM (routed experts [first_local, first_local+n_local), shared expert,
     router with the shared gate vector as its last row)."""
@@ -246,6 +275,13 @@ class Layer:
         what the file provided (1 routed experts, 2 shared expert, 4 router rows, 8 shared gate vector)."""
         got = C.c_int(0)
         check(lib().moexb_layer_load_gguf(self.h, gguf.h, block, C.byref(got)))
+        return got.value
+
+    def load_st(self, st, prefix):
+        """moexb_layer_load_st: the experts and router of `prefix` ("model.layers.<l>.") from an open SafeTensors file.
+        Returns the bit set of what the file provided (1 routed experts, 4 router rows, 8 shared gate vector)."""
+        got = C.c_int(0)
+        check(lib().moexb_layer_load_st(self.h, st.h, prefix.encode(), C.byref(got)))
         return got.value
 
     def upload_blob(self, e, blob):

@@ -9,6 +9,7 @@
 #include "prefill.cuh"
 #include "decode_stack.cuh"
 #include "gguf_ingest.h"
+#include "st_ingest.h"
 
 #include <cmath>
 #include <cstdarg>
@@ -601,15 +602,15 @@ static int gguf_expect(const moexb_gguf* g, const std::string& name, std::initia
     return MOEXB_OK;
 }
 
-// One router row source (F32, F16 or BF16, `n` values) into the layer's router dtype at dst (host).
-static bool gguf_router_rows(const GgufTensor* t, long long n, int router_dtype, void* dst) {
-    if (t->type != GGML_F32 && t->type != GGML_F16 && t->type != GGML_BF16) return false;
+// `n` router values at src (F32, F16 or BF16, by ggml type id) into the layer's router dtype at dst (host).
+static bool router_rows_to(uint32_t type, const uint8_t* src, long long n, int router_dtype, void* dst) {
+    if (type != GGML_F32 && type != GGML_F16 && type != GGML_BF16) return false;
     for (long long i = 0; i < n; i++) {
         float v;
-        if (t->type == GGML_F32) memcpy(&v, t->data + 4 * i, 4);
+        if (type == GGML_F32) memcpy(&v, src + 4 * i, 4);
         else {
-            uint16_t h; memcpy(&h, t->data + 2 * i, 2);
-            if (t->type == GGML_F16) { __half hh; memcpy(&hh, &h, 2); v = __half2float(hh); }
+            uint16_t h; memcpy(&h, src + 2 * i, 2);
+            if (type == GGML_F16) { __half hh; memcpy(&hh, &h, 2); v = __half2float(hh); }
             else { const uint32_t u = (uint32_t)h << 16; memcpy(&v, &u, 4); }
         }
         if (router_dtype == MOEXB_F32) static_cast<float*>(dst)[i] = v;
@@ -674,11 +675,109 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
     const GgufTensor *rt = g->find(p + "ffn_gate_inp.weight"), *rs = g->find(p + "ffn_gate_inp_shexp.weight");
     const size_t esz = L->router_dtype == MOEXB_F32 ? 4 : 2;
     std::vector<uint8_t> rows((size_t)E * EH * esz);
-    if (rt && rt->n_dims == 2 && rt->ne[0] == EH && rt->ne[1] == E && rt->data && gguf_router_rows(rt, E * EH, L->router_dtype, rows.data())) {
+    if (rt && rt->n_dims == 2 && rt->ne[0] == EH && rt->ne[1] == E && rt->data && router_rows_to(rt->type, rt->data, E * EH, L->router_dtype, rows.data())) {
         CUDA_TRY(cudaMemcpy(L->router, rows.data(), rows.size(), cudaMemcpyHostToDevice));
         got |= 4;
     }
-    if (rs && rs->ne[0] == EH && rs->nbytes == rs->row_bytes && rs->data && gguf_router_rows(rs, EH, L->router_dtype, rows.data())) {
+    if (rs && rs->ne[0] == EH && rs->nbytes == rs->row_bytes && rs->data && router_rows_to(rs->type, rs->data, EH, L->router_dtype, rows.data())) {
+        CUDA_TRY(cudaMemcpy(static_cast<uint8_t*>(L->router) + (size_t)E * EH * esz, rows.data(), EH * esz, cudaMemcpyHostToDevice));
+        got |= 8;
+    }
+    if (loaded) *loaded = got;
+    return MOEXB_OK;
+}
+
+// ---- safetensors container ingest ----------------------------------------------------------------------------------------
+
+int moexb_st_open(const char* path, moexb_st** out) {
+    REQUIRE(path && out, "st_open: null pointer");
+    std::string err;
+    moexb_st* s = st_open(path, err);
+    if (!s) return fail(MOEXB_ERR_ARG, "st_open: %s", err.c_str());
+    *out = s;
+    return MOEXB_OK;
+}
+
+int moexb_st_close(moexb_st* s) {
+    delete s;
+    return MOEXB_OK;
+}
+
+int moexb_st_tensor_count(const moexb_st* s) { return s ? (int)s->tensors.size() : 0; }
+
+const char* moexb_st_tensor_name(const moexb_st* s, int i) {
+    return s && i >= 0 && i < (int)s->tensors.size() ? s->tensors[i].name.c_str() : nullptr;
+}
+
+int moexb_st_tensor(const moexb_st* s, const char* name, char* dtype, int* n_dims, long long* shape, const void** data, long long* nbytes) {
+    REQUIRE(s && name, "st_tensor: null pointer");
+    const StTensorInfo* t = s->find(name);
+    if (!t) return fail(MOEXB_ERR_ARG, "missing tensor %s", name);
+    if (dtype) { strncpy(dtype, t->dtype.c_str(), 7); dtype[7] = 0; }
+    if (n_dims) *n_dims = (int)t->shape.size();
+    if (shape) for (size_t d = 0; d < t->shape.size() && d < 8; d++) shape[d] = t->shape[d];
+    if (data) *data = t->data;
+    if (nbytes) *nbytes = t->nbytes;
+    return MOEXB_OK;
+}
+
+int moexb_layer_load_st(moexb_layer* L, const moexb_st* s, const char* prefix, int* loaded) {
+    REQUIRE(L && s && prefix, "layer_load_st: null pointer");
+    if (loaded) *loaded = 0;
+    moexb_ctx* c = L->ctx;
+    CUDA_TRY(cudaSetDevice(c->device));
+    const std::string p(prefix);
+    const size_t eb = expert_bytes(L->fmt), sp = eb - Q_BYTES;  // scale part of the layer's format
+    // the container's scale part: F32 group scales (symmetric) or the zero-point bytes; an fp16-scale layer takes F32
+    // scales only when every one of them is an fp16 value, so that nothing is rounded on the way in
+    const size_t sp_file = L->fmt == FMT_ZP ? expert_bytes(FMT_ZP) - Q_BYTES : expert_bytes(FMT_SYM_F32) - Q_BYTES;
+    const char* want_dtype = L->fmt == FMT_ZP ? "U8" : "F32";
+    std::vector<__half> narrow(L->fmt == FMT_SYM_F16 ? CHUNKS / 2 : 0);
+    for (int i = 0; i < L->n_local; i += STAGING_BLOBS) {
+        const int n = min(STAGING_BLOBS, L->n_local - i);
+        for (int j = 0; j < n; j++) {
+            const std::string ep = p + "mlp.experts." + std::to_string(L->first_local + i + j) + ".";
+            const StTensorInfo *q = s->find(ep + "merged_weight"), *qs = s->find(ep + "qs");
+            if (!q || !qs) return fail(MOEXB_ERR_ARG, "missing tensor %s%s", ep.c_str(), q ? "qs" : "merged_weight");
+            if ((size_t)q->nbytes != Q_BYTES) return fail(MOEXB_ERR_ARG, "%smerged_weight has %lld bytes, not the %zu of this expert shape", ep.c_str(), q->nbytes, (size_t)Q_BYTES);
+            if ((size_t)qs->nbytes != sp_file || qs->dtype != want_dtype)
+                return fail(MOEXB_ERR_UNSUPPORTED, "%sqs (%s, %lld bytes) is not the scale part of this layer's expert format (%s, %zu bytes)",
+                            ep.c_str(), qs->dtype.c_str(), qs->nbytes, want_dtype, sp_file);
+            uint8_t* dst = c->staging + (size_t)j * eb;
+            CUDA_TRY(cudaMemcpyAsync(dst, q->data, Q_BYTES, cudaMemcpyHostToDevice, nullptr));
+            if (L->fmt == FMT_SYM_F16) {
+                for (size_t k = 0; k < CHUNKS / 2; k++) {
+                    float f;
+                    memcpy(&f, qs->data + 4 * k, 4);
+                    narrow[k] = __float2half_rn(f);
+                    if (!(__half2float(narrow[k]) == f))
+                        return fail(MOEXB_ERR_UNSUPPORTED, "%sqs: scale %zu (%.9g) is not an fp16 value; load this container into a MOEXB_FMT_SYM_F32 layer", ep.c_str(), k, f);
+                }
+                CUDA_TRY(cudaMemcpy(dst + Q_BYTES, narrow.data(), sp, cudaMemcpyHostToDevice));  // synchronous: narrow is reused
+            } else {
+                CUDA_TRY(cudaMemcpyAsync(dst + Q_BYTES, qs->data, sp, cudaMemcpyHostToDevice, nullptr));
+            }
+        }
+        const int rc = to_layer_layout(L, c->staging, L->image + (size_t)i * eb, n, nullptr);
+        if (rc != MOEXB_OK) return rc;
+        CUDA_TRY(cudaStreamSynchronize(nullptr));
+    }
+    int got = L->n_local ? 1 : 0;
+    // router rows (mlp.gate.weight [E][H]) and the shared expert's gate vector (mlp.shared_expert_gate.weight [1][H])
+    const size_t esz = L->router_dtype == MOEXB_F32 ? 4 : 2;
+    const long long E = L->n_routed;
+    std::vector<uint8_t> rows((size_t)E * EH * esz);
+    auto ggml_of = [](const std::string& d) { return d == "F32" ? (int)GGML_F32 : d == "F16" ? (int)GGML_F16 : d == "BF16" ? (int)GGML_BF16 : -1; };
+    auto convert = [&](const StTensorInfo* t, long long n) {
+        const int ty = t ? ggml_of(t->dtype) : -1;
+        if (ty < 0 || t->nbytes != n * (ty == (int)GGML_F32 ? 4 : 2)) return false;
+        return router_rows_to((uint32_t)ty, t->data, n, L->router_dtype, rows.data());
+    };
+    if (convert(s->find(p + "mlp.gate.weight"), E * EH)) {
+        CUDA_TRY(cudaMemcpy(L->router, rows.data(), rows.size(), cudaMemcpyHostToDevice));
+        got |= 4;
+    }
+    if (convert(s->find(p + "mlp.shared_expert_gate.weight"), EH)) {
         CUDA_TRY(cudaMemcpy(static_cast<uint8_t*>(L->router) + (size_t)E * EH * esz, rows.data(), EH * esz, cudaMemcpyHostToDevice));
         got |= 8;
     }
