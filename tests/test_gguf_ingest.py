@@ -174,7 +174,7 @@ def test_layer_loaded_from_a_gguf_block_holds_the_converted_bytes(gctx, expert_f
     # the router rows arrive converted to the layer's dtype, the shared gate vector as the last row
     class Mem:
         __cuda_array_interface__ = {"shape": ((E_SMALL + 1) * EH,), "typestr": "<f4", "version": 2,
-                                    "data": (m.lib().moexb_layer_router(L.h), True)}
+                                    "data": (m.lib().moexb_layer_router(L.h), False)}
     assert np.array_equal(torch.as_tensor(Mem(), device="cuda:0").cpu().numpy().reshape(E_SMALL + 1, EH), Wr)
     # and the layer computes what a layer filled by upload does
     X = torch.randn(5, EH, device="cuda:0")

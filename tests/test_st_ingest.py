@@ -96,7 +96,7 @@ def layer_file(path, fmt, scales_f16_exact=True):
         blobs.append(blob)
         p = f"model.layers.{LAYER}.mlp.experts.{e}."
         tensors += [(p + "merged_weight", "U8", (Q_BYTES,), blob[:Q_BYTES].tobytes()),
-                    (p + "qs", qs_dtype, (len(blob) - Q_BYTES) // (1 if qs_dtype == "U8" else 4,), blob[Q_BYTES:].tobytes())]
+                    (p + "qs", qs_dtype, ((len(blob) - Q_BYTES) // (1 if qs_dtype == "U8" else 4),), blob[Q_BYTES:].tobytes())]
     W = (rng.standard_normal((E_SMALL + 1, EH)) * 0.02).astype(np.float16)
     tensors += [(f"model.layers.{LAYER}.mlp.gate.weight", "F16", (E_SMALL, EH), W[:E_SMALL].tobytes()),
                 (f"model.layers.{LAYER}.mlp.shared_expert_gate.weight", "F16", (1, EH), W[E_SMALL:].tobytes())]
