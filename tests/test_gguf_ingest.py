@@ -2,8 +2,6 @@
 reference's own reader compiled into oracle/_ref (struct Gguf, gguf.h:345-462; its test: tests/test_gguf.cpp:37-78 writes
 a tiny file, reads it back, then cuts it short), and the load of a block's Q4_K expert tensors into a resident layer
 (GPU), which must give the very bytes moexb_q4k_to_zp / the reference's gg_zp_row give."""
-import os
-
 import numpy as np
 import pytest
 
@@ -13,7 +11,6 @@ from tests import gguf_file as gf
 
 pytestmark = pytest.mark.usefixtures("lib_built")
 EH, EI = m.EH, m.EI
-PART = EH * EI // 256 * 144  # raw Q4_K bytes of one expert's gate, up or down tensor
 
 
 def small_file(path, version=3, alignment=None, nested=False):
