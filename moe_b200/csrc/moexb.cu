@@ -1066,8 +1066,14 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             PROF(c, MOEXB_PROF_GROUP, stream);
             const int parts = (x_bf16 && !block) ? 1 : 2;
             const int maxp = prefill ? PF_NMAX / parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
-            CUDA_TRY(launch_dep(group_plan1_k, 1, 1024, 0, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
-                                prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1));
+            // room in shared memory for the routed pairs (12 bytes each), so that the list is written out in full lines
+            constexpr int PLAN_STAGE_MAX = 196608;
+            static std::once_flag plan_once;
+            static cudaError_t plan_attr = cudaSuccess;
+            std::call_once(plan_once, [] { plan_attr = cudaFuncSetAttribute(group_plan1_k, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
+            const int stage_pairs = plan_attr == cudaSuccess && (size_t)T * K * 12 <= PLAN_STAGE_MAX ? T * K : 0;
+            CUDA_TRY(launch_dep(group_plan1_k, 1, 1024, (size_t)stage_pairs * 12, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
+                                prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1, stage_pairs));
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
             // reduction skips them by expert id

@@ -461,8 +461,10 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
                                                       moexb_pair* __restrict__ pairs, int* __restrict__ nitems,
                                                       moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int maxp,
                                                       moexb_pair_item* __restrict__ subs2, int* __restrict__ nsub2, int maxp2,
-                                                      const float* __restrict__ gate_logits, int gl_stride, int sh0, int sh1) {
+                                                      const float* __restrict__ gate_logits, int gl_stride, int sh0, int sh1,
+                                                      int stage_pairs) {
     __shared__ int cnt[1024], cur[1024], start[1024];
+    extern __shared__ int stage[];   // stage_pairs pairs of 3 words, when the launch gave the room
     const int n = T * K, e = threadIdx.x;
     cnt[e] = 0; cur[e] = 0;
     __syncthreads();
@@ -486,6 +488,7 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     const int wat = block_scan_1024(wide(c, maxp), nw), nat = block_scan_1024(narrow(c, maxp), nn);
     const int at2 = subs2 ? block_scan_1024((c + maxp2 - 1) / maxp2, n2) : 0;
     start[e] = slot ? at : -1;
+    const bool staged = stage_pairs >= n;
     const bool with_shared = gate_logits && slot_table[E] && sh1 > sh0;
     const int Ts = with_shared ? sh1 - sh0 : 0;
     const int all_wide = nw + wide(Ts, maxp);   // the routed experts' wide sub-items, then the shared expert's
@@ -503,8 +506,17 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
 #pragma unroll
         for (int u = 0; u < B; u++) {
             const int p = p0 + 1024 * u, s0 = ex[u] >= 0 ? start[ex[u]] : -1;
-            if (s0 >= 0) pairs[s0 + atomicAdd(&cur[ex[u]], 1)] = {p / K, p, wp[u]};
+            if (s0 < 0) continue;
+            const int at_p = s0 + atomicAdd(&cur[ex[u]], 1);
+            if (staged) { stage[3 * at_p] = p / K; stage[3 * at_p + 1] = p; stage[3 * at_p + 2] = __float_as_int(wp[u]); }
+            else pairs[at_p] = {p / K, p, wp[u]};
         }
+    }
+    if (staged) {
+        // scattered 12-byte stores from one SM cost a sector each; from shared memory the list leaves as full lines
+        __syncthreads();
+        int* out = reinterpret_cast<int*>(pairs);
+        for (int i = e; i < 3 * np; i += 1024) out[i] = stage[i];
     }
     if (with_shared) {
         const uint8_t* sslot = slot_table[E];
