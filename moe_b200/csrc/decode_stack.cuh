@@ -72,7 +72,8 @@ template <int FMT> constexpr int ds_smem_bytes() {
 // 8 groups of one slice against the lane's two activation columns (bp: the lane's column pointer, already offset to the
 // slice's first input); acc[0..1] += row g, acc[2..3] += row g + 8 (columns 2t, 2t + 1).
 template <int FMT>
-__device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4], int G0 = 0, int G1 = 8) {
+__device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const uint8_t* __restrict__ bp, int lane, float (&acc)[4], int G0 = 0, int G1 = 8,
+                                         const float* __restrict__ sums = nullptr) {
     constexpr int GB = tl_group_bytes<FMT>();
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll 4
@@ -98,9 +99,10 @@ __device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const u
             acc[0] = fmaf(c[0], sa, acc[0]); acc[1] = fmaf(c[1], sa, acc[1]);
             acc[2] = fmaf(c[2], sb, acc[2]); acc[3] = fmaf(c[3], sb, acc[3]);
         } else {
-            // zero point (stream_tiled_k's scheme, bf16 operands): each 32-weight chunk has its own (s, m), w = s*u + m, so a
-            // group is two partial sums s_c * sum(u x) + m_c * sum(x); the chunks are separated by zeroing the other half's
-            // nibbles, sum(x) comes from an all-ones A fragment
+            // zero point (bf16 operands): each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial
+            // sums s_c * sum(u x) + m_c * sum(x). The two chunks of a group are separated by zeroing the other half's
+            // nibbles; sum(x) does not depend on the weight row and comes from `sums` ([group][chunk][hi, lo], made once
+            // per activation row).
             dq_word<false>(qq.x, Pa[0]); dq_word<false>(qq.y, Pa[1]); dq_word<false>(qq.z, Pb[0]); dq_word<false>(qq.w, Pb[1]);
             const uint2 cm = *reinterpret_cast<const uint2*>(sl + G * GB + 512 + 8 * g);      // A: sc0 mn0 sc1 mn1 | B: ...
             const uint4 dd = *reinterpret_cast<const uint4*>(sl + 8 * GB + 16 * g);           // A sb0, A sb1, B sb0, B sb1
@@ -109,14 +111,13 @@ __device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const u
 #pragma unroll
             for (int hc = 0; hc < 2; hc++) {
                 const bool mine = (t >> 1) == hc;
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t one = mine ? 0x3F803F80u : 0u;
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
                 mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
                 mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
                 mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
                 mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
-                mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
-                mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                const float2 sx = *reinterpret_cast<const float2*>(sums + G * 4 + hc * 2);   // the chunk's sum of the hi and of the lo column
+                const float c1[4] = {sx.x, sx.y, sx.x, sx.y};   // columns 2t (hi), 2t + 1 (lo) of rows g and g + 8
                 const uint32_t ca = (cm.x >> (16 * hc)) & 0xFFFFu, cb = (cm.y >> (16 * hc)) & 0xFFFFu;
                 const float s_a = dda.x * (float)(ca & 0xFF), m_a = dda.y * (float)(int8_t)(ca >> 8);
                 const float s_b = ddb.x * (float)(cb & 0xFF), m_b = ddb.y * (float)(int8_t)(cb >> 8);
@@ -125,6 +126,22 @@ __device__ __forceinline__ void ds_slice(const uint8_t* __restrict__ sl, const u
             }
         }
     }
+}
+
+// Sum of the 32 bf16 values of one zero-point chunk of an activation column: chunk hc of a group is bytes
+// [32 hc, 32 hc + 32) and [64 + 32 hc, 96 + 32 hc) of the group's 128 (the k-slots of lanes t = 2 hc, 2 hc + 1).
+__device__ __forceinline__ float ds_chunk_sum(const uint8_t* group, int hc) {
+    float s = 0.f;
+#pragma unroll
+    for (int seg = 0; seg < 2; seg++)
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            const uint4 v = *reinterpret_cast<const uint4*>(group + 64 * seg + 32 * hc + 16 * q);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) s += __uint_as_float(w[i] << 16) + __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    return s;
 }
 
 // WT: router weight type; XBF: the input row is bf16. Symmetric formats run on fp16 operands, zero point on bf16.
@@ -158,6 +175,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     __shared__ int s_wcnt[DS_WARPS];
     __shared__ int s_idx2[DS_MAXK];
     __shared__ const uint8_t* s_slot2[DS_MAXK + 1];
+    // zero point only: sum(x) per 32-input chunk of the token's columns, of each routed expert's act row, of the shared one's
+    __shared__ __align__(16) float s_xsum[4 * 8 * 4], s_asum[DS_WARPS * 8 * 4], s_shsum[DS_WARPS * 4];
     __shared__ DecodeLayer s_layers[DS_MAXLAYERS];   // the layer descriptors: no global round trip when a layer is staged
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int grid = gridDim.x, b = blockIdx.x, E = a.E, K = a.K, O = E + 1;
@@ -189,6 +208,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     __syncthreads();
     norm_split_row<F16>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
     __syncthreads();
+    // [K slice][group][chunk][hi, lo]: thread = (column, K slice, group, chunk); read by P3 after later block barriers
+    auto x_sums = [&]() {
+        if (FMT == FMT_ZP && tid < 128) {
+            const int col = tid >> 6, c = tid & 63;
+            s_xsum[(c >> 1) * 4 + (c & 1) * 2 + col] = ds_chunk_sum(xcol + col * DS_XCOL + (c >> 1) * 128, c & 1);
+        }
+    };
+    x_sums();
 
     // The router rows this CTA owns and the slot table of layer l: requested (cp.async) while the layer before still streams
     // its experts, so that P1 and P2 find them in shared memory.
@@ -368,7 +395,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (u < U3) {
                 if (!wait_slice(pass)) { ok = false; }
-                else ds_slice<FMT>(myring + ((S0 + pass) % DS_D) * SB, xcol + (g & 1) * DS_XCOL + t * 16 + (warp & 3) * 1024, lane, acc);
+                else ds_slice<FMT>(myring + ((S0 + pass) % DS_D) * SB, xcol + (g & 1) * DS_XCOL + t * 16 + (warp & 3) * 1024, lane, acc, 0, 8, s_xsum + (warp & 3) * 32);
             }
             consumed = pass + 1;
             __syncwarp();
@@ -412,15 +439,23 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
                         *reinterpret_cast<uint4*>(ac + (c >> 6) * DS_ACOL + (c & 63) * 16) = __ldcg(src + c);
                     }
                     __syncwarp();
+                    if constexpr (FMT == FMT_ZP) {   // lane = (group, chunk, column)
+                        s_asum[warp * 32 + lane] = ds_chunk_sum(ac + (lane & 1) * DS_ACOL + (lane >> 2) * 128, (lane >> 1) & 1);
+                        __syncwarp();
+                    }
                     if (!wait_slice(n3 + pass)) ok = false;
-                    else ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc);
+                    else ds_slice<FMT>(myring + ((S0 + n3 + pass) % DS_D) * SB, ac + (g & 1) * DS_ACOL + t * 16, lane, acc, 0, 8, s_asum + warp * 32);
                     if (t == 0) { yrt[warp * 16 + g] = acc[0] + acc[1]; yrt[warp * 16 + g + 8] = acc[2] + acc[3]; }
                 }
                 __syncthreads();   // the shared expert's act row is in
                 if (!mbar_wait(smem_u32(&shbar), sh_phase, a.err, DS_ERR_COPY)) { atomicExch(a.sync + 1, 1u); s_abort = 1; ok = false; }
                 else {
                     float as[4] = {0.f, 0.f, 0.f, 0.f};
-                    ds_slice<FMT>(shbuf, shcol + (g & 1) * DS_ACOL + t * 16, lane, as, warp, warp + 1);
+                    if constexpr (FMT == FMT_ZP) {   // this warp's input group of the shared act row: lanes 0-3 = (chunk, column)
+                        if (lane < 4) s_shsum[warp * 4 + lane] = ds_chunk_sum(shcol + (lane & 1) * DS_ACOL + warp * 128, lane >> 1);
+                        __syncwarp();
+                    }
+                    ds_slice<FMT>(shbuf, shcol + (g & 1) * DS_ACOL + t * 16, lane, as, warp, warp + 1, s_shsum);
                     if (t == 0) { ysh[warp * 16 + g] = as[0] + as[1]; ysh[warp * 16 + g + 8] = as[2] + as[3]; }
                 }
                 sh_phase ^= 1u;
@@ -457,6 +492,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
         if (l + 1 < a.n_layers) norm_split_row<F16>(v, xn, reinterpret_cast<uint16_t*>(xcol), 1e-6f, DS_XCOL / 2);
         asm volatile("cp.async.wait_all;" ::: "memory");   // the next layer's router rows and slot table
         __syncthreads();
+        if (l + 1 < a.n_layers) x_sums();
     }
     // leave: no copy may still be in flight into this CTA's shared memory
     if (!ok) {
