@@ -252,7 +252,8 @@ int moexb_st_close(moexb_st* s);
 int moexb_st_tensor_count(const moexb_st* s);
 const char* moexb_st_tensor_name(const moexb_st* s, int i); /* null when i is out of range */
 /* One tensor by name (Container::at / map, st.h:30-35, 64-84): dtype string (buffer of 8 chars), number of dimensions,
- * shape (up to 8 values), a pointer into the mapping and the size in bytes. Any out pointer may be null. */
+ * shape (the first 8 dimensions at most, and n_dims counts only those), a pointer into the mapping and the size in
+ * bytes. Any out pointer may be null. */
 int moexb_st_tensor(const moexb_st* s, const char* name, char* dtype, int* n_dims, long long* shape, const void** data,
                     long long* nbytes);
 /* Fills a layer from a container file: for every routed expert e the layer holds, `<prefix>mlp.experts.<e>.merged_weight`

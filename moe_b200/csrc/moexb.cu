@@ -16,6 +16,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <new>
@@ -714,7 +715,7 @@ int moexb_st_tensor(const moexb_st* s, const char* name, char* dtype, int* n_dim
     const StTensorInfo* t = s->find(name);
     if (!t) return fail(MOEXB_ERR_ARG, "missing tensor %s", name);
     if (dtype) { strncpy(dtype, t->dtype.c_str(), 7); dtype[7] = 0; }
-    if (n_dims) *n_dims = (int)t->shape.size();
+    if (n_dims) *n_dims = (int)std::min<size_t>(t->shape.size(), 8);
     if (shape) for (size_t d = 0; d < t->shape.size() && d < 8; d++) shape[d] = t->shape[d];
     if (data) *data = t->data;
     if (nbytes) *nbytes = t->nbytes;
