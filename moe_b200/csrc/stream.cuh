@@ -467,11 +467,27 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     extern __shared__ int stage[];   // stage_pairs pairs of 3 words, when the launch gave the room
     const int n = T * K, e = threadIdx.x;
     cnt[e] = 0; cur[e] = 0;
+    // what does not come from the kernel before: the blob pointers
+    const uint8_t* slot = e < E ? slot_table[e] : nullptr;
+    const uint8_t* sslot = slot_table[E];
+    const bool with_shared = gate_logits && sslot && sh1 > sh0;
+    const int Ts = with_shared ? sh1 - sh0 : 0;
     __syncthreads();
     pdl_wait();
     pdl_trigger();
-    constexpr int B = 8;   // pairs per thread in flight: the loops are chains of global loads otherwise
-    for (int p0 = e; p0 < n; p0 += 1024 * B) {
+    // Every global load of the first 8192 pairs and of the first 1024 gate logits is issued here, in one round trip; the
+    // values stay in registers for the histogram and for the scatter.
+    constexpr int B = 8;   // pairs per thread in flight
+    int ex0[B]; float wp0[B];
+#pragma unroll
+    for (int u = 0; u < B; u++) {
+        const int p = e + 1024 * u;
+        ex0[u] = p < n ? __ldg(idx + p) : -1; wp0[u] = p < n ? __ldg(w + p) : 0.f;
+    }
+    const float gl0 = e < Ts ? gate_logits[(size_t)(sh0 + e) * gl_stride] : 0.f;
+#pragma unroll
+    for (int u = 0; u < B; u++) if (ex0[u] >= 0) atomicAdd(&cnt[ex0[u]], 1);
+    for (int p0 = e + 1024 * B; p0 < n; p0 += 1024 * B) {
         int ex[B];
 #pragma unroll
         for (int u = 0; u < B; u++) ex[u] = p0 + 1024 * u < n ? __ldg(idx + p0 + 1024 * u) : -1;
@@ -479,7 +495,6 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
         for (int u = 0; u < B; u++) if (ex[u] >= 0) atomicAdd(&cnt[ex[u]], 1);
     }
     __syncthreads();
-    const uint8_t* slot = e < E ? slot_table[e] : nullptr;
     const int c = slot ? cnt[e] : 0;   // pairs of experts that are not held here are dropped
     auto wide = [](int c, int mp) { return c / mp + (c % mp > mp / 2); };
     auto narrow = [](int c, int mp) { return (int)(c % mp > 0 && c % mp <= mp / 2); };
@@ -489,8 +504,6 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     const int at2 = subs2 ? block_scan_1024((c + maxp2 - 1) / maxp2, n2) : 0;
     start[e] = slot ? at : -1;
     const bool staged = stage_pairs >= n;
-    const bool with_shared = gate_logits && slot_table[E] && sh1 > sh0;
-    const int Ts = with_shared ? sh1 - sh0 : 0;
     const int all_wide = nw + wide(Ts, maxp);   // the routed experts' wide sub-items, then the shared expert's
     if (c) {
         items[item] = {slot, at, c};
@@ -499,18 +512,21 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
         if (subs2) for (int j = 0; j * maxp2 < c; j++) subs2[at2 + j] = {slot, at + j * maxp2, min(maxp2, c - j * maxp2)};
     }
     __syncthreads();
-    for (int p0 = e; p0 < n; p0 += 1024 * B) {
+    auto place = [&](int p, int ex, float wp) {
+        const int s0 = ex >= 0 ? start[ex] : -1;
+        if (s0 < 0) return;
+        const int at_p = s0 + atomicAdd(&cur[ex], 1);
+        if (staged) { stage[3 * at_p] = p / K; stage[3 * at_p + 1] = p; stage[3 * at_p + 2] = __float_as_int(wp); }
+        else pairs[at_p] = {p / K, p, wp};
+    };
+#pragma unroll
+    for (int u = 0; u < B; u++) place(e + 1024 * u, ex0[u], wp0[u]);
+    for (int p0 = e + 1024 * B; p0 < n; p0 += 1024 * B) {
         int ex[B]; float wp[B];
 #pragma unroll
         for (int u = 0; u < B; u++) { const int p = p0 + 1024 * u; ex[u] = p < n ? __ldg(idx + p) : -1; wp[u] = p < n ? __ldg(w + p) : 0.f; }
 #pragma unroll
-        for (int u = 0; u < B; u++) {
-            const int p = p0 + 1024 * u, s0 = ex[u] >= 0 ? start[ex[u]] : -1;
-            if (s0 < 0) continue;
-            const int at_p = s0 + atomicAdd(&cur[ex[u]], 1);
-            if (staged) { stage[3 * at_p] = p / K; stage[3 * at_p + 1] = p; stage[3 * at_p + 2] = __float_as_int(wp[u]); }
-            else pairs[at_p] = {p / K, p, wp[u]};
-        }
+        for (int u = 0; u < B; u++) place(p0 + 1024 * u, ex[u], wp[u]);
     }
     if (staged) {
         // scattered 12-byte stores from one SM cost a sector each; from shared memory the list leaves as full lines
@@ -519,9 +535,11 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
         for (int i = e; i < 3 * np; i += 1024) out[i] = stage[i];
     }
     if (with_shared) {
-        const uint8_t* sslot = slot_table[E];
         const int cw = wide(Ts, maxp), ns = all_wide + nn;   // ns: where the shared expert's narrow sub-item goes
-        for (int t = e; t < Ts; t += 1024) pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gate_logits[(size_t)(sh0 + t) * gl_stride]))};
+        for (int t = e; t < Ts; t += 1024) {
+            const float gl = t == e ? gl0 : gate_logits[(size_t)(sh0 + t) * gl_stride];
+            pairs[np + t] = {sh0 + t, n + sh0 + t, 1.f / (1.f + expf(-gl))};
+        }
         for (int j = e; j * maxp < Ts; j += 1024) subs[j < cw ? nw + j : ns] = {sslot, np + j * maxp, min(maxp, Ts - j * maxp)};
         if (subs2) for (int j = e; j * maxp2 < Ts; j += 1024) subs2[n2 + j] = {sslot, np + j * maxp2, min(maxp2, Ts - j * maxp2)};
         if (e == 0) {
