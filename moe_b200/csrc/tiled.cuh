@@ -112,6 +112,8 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* bsm = smem + NW * D * SB;                                 // 8 * NB activation columns
     uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * NB * BCOL); // full[NW][D]
+    // zero point: the sum of the activations over each 32-input chunk, per column: [K slice][group][chunk][8 columns]
+    __shared__ __align__(16) float csum[Z ? KS * 8 * 2 * 8 : 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
     if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -164,6 +166,25 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncthreads();
+            if constexpr (Z) {
+                // the term m_c * sum(x) of a chunk does not depend on the weight row: sum(x) once per sub-item. Chunk hc of a
+                // group is bytes [32 hc, 32 hc + 32) and [64 + 32 hc, 96 + 32 hc) of the group's 128 (lanes t = 2 hc, 2 hc + 1).
+                for (int i = threadIdx.x; i < KS * 8 * 2 * 8; i += NW * 32) {
+                    const uint8_t* grp = bsm + (i & 7) * BCOL + (i >> 4) * 128 + ((i >> 3) & 1) * 32;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int seg = 0; seg < 2; seg++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(grp + 64 * seg + 16 * h);
+                            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) sum += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xFFFF0000u);
+                        }
+                    csum[i] = sum;
+                }
+                __syncthreads();
+            }
         }
         if (!mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT)) return;
         if (ks == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; acd[0] = acd[1] = acd[2] = acd[3] = 0.f; }
@@ -209,7 +230,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
                 // zero point: each 32-weight chunk has its own (s, m), w = s*u + m, so a group is two partial sums
                 // s_c * sum(u x) + m_c * sum(x). Lanes t = 0,1 hold chunk 0 of the group, lanes t = 2,3 chunk 1, and an MMA
                 // mixes the quad's k-slots, so the chunks are separated by zeroing the other half's nibbles; sum(x)
-                // comes from an all-ones A fragment.
+                // comes from the table made when the columns were loaded.
                 const uint2 cm = *reinterpret_cast<const uint2*>(sl + G * GB + 512 + 8 * g);      // A: sc0 mn0 sc1 mn1 | B: ...
                 const uint4 dd = *reinterpret_cast<const uint4*>(sl + 8 * GB + 16 * g);           // A sb0, A sb1, B sb0, B sb1
                 const uint32_t da = (G >> 2) ? dd.y : dd.x, db = (G >> 2) ? dd.w : dd.z;
@@ -217,14 +238,13 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
 #pragma unroll
                 for (int hc = 0; hc < 2; hc++) {
                     const bool mine = (t >> 1) == hc;
-                    float c[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-                    const uint32_t one = mine ? 0x3F803F80u : 0u;
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_bf16(c, mine ? Pa[0][0] : 0u, mine ? Pb[0][0] : 0u, mine ? Pa[0][1] : 0u, mine ? Pb[0][1] : 0u, B0.x, B0.y);
                     mma_bf16(c, mine ? Pa[0][2] : 0u, mine ? Pb[0][2] : 0u, mine ? Pa[0][3] : 0u, mine ? Pb[0][3] : 0u, B0.z, B0.w);
                     mma_bf16(c, mine ? Pa[1][0] : 0u, mine ? Pb[1][0] : 0u, mine ? Pa[1][1] : 0u, mine ? Pb[1][1] : 0u, B1.x, B1.y);
                     mma_bf16(c, mine ? Pa[1][2] : 0u, mine ? Pb[1][2] : 0u, mine ? Pa[1][3] : 0u, mine ? Pb[1][3] : 0u, B1.z, B1.w);
-                    mma_bf16(c1, one, one, one, one, B0.x, B0.y); mma_bf16(c1, one, one, one, one, B0.z, B0.w);
-                    mma_bf16(c1, one, one, one, one, B1.x, B1.y); mma_bf16(c1, one, one, one, one, B1.z, B1.w);
+                    const float2 sx = *reinterpret_cast<const float2*>(csum + (((ks * 8 + G) * 2 + hc) * 8 + 2 * t));  // columns 2t, 2t + 1
+                    const float c1[4] = {sx.x, sx.y, sx.x, sx.y};
                     const uint32_t ca = (cm.x >> (16 * hc)) & 0xFFFFu, cb = (cm.y >> (16 * hc)) & 0xFFFFu;
                     const float s_a = dda.x * (float)(ca & 0xFF), m_a = dda.y * (float)(int8_t)(ca >> 8);
                     const float s_b = ddb.x * (float)(cb & 0xFF), m_b = ddb.y * (float)(int8_t)(cb >> 8);

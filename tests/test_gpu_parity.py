@@ -319,7 +319,7 @@ def test_layer_forward_zero_point(ctx):
     E = 32
     W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float16)
     host = [m.synth_expert_host(m.FMT_ZP, 1, 0, e) for e in range(E + 1)]
-    for T, path, layout in ((1, 0, m.LAYOUT_TILED), (5, 0, m.LAYOUT_TILED), (1, 0, m.LAYOUT_REFERENCE), (5, 0, m.LAYOUT_REFERENCE),
+    for T, path, layout in ((1, 0, m.LAYOUT_TILED), (5, 0, m.LAYOUT_TILED), (40, 0, m.LAYOUT_TILED), (1, 0, m.LAYOUT_REFERENCE), (5, 0, m.LAYOUT_REFERENCE),
                             (1, 1, m.LAYOUT_REFERENCE), (5, 1, m.LAYOUT_REFERENCE)):
         L = m.Layer(ctx, m.FMT_ZP, E, router_dtype=m.F16, layout=layout)
         L.fill_synth(1, 0)
