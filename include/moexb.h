@@ -81,14 +81,14 @@ int moexb_gemv_f32(const float* W, const float* x, float* y, int I, int O, void*
 /* Softmax over E logits per token, then the K largest (ties -> lower index), in descending order; w = probability,
  * divided by the sum over the selected K when norm != 0. logits [T][ld] with ld >= E (ld lets the shared-expert gate
  * logit ride along as column E, as the reference appends it as router row E, moex.cu:876). Replaces router_topk
- * (kernels.cuh:373-411). E multiple of 32, E <= 1024, K <= 32. */
+ * (kernels.cuh:373-411). E multiple of 32, E <= 1024, K <= 31. */
 int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, float* w, void* stream, int T, int ld);
 
 /* ---- routed experts, one token (decode) ---------------------------------------------------------------------------- */
 
 /* act[k][I] = silu(gate_k x) * (up_k x); out[H] = sum_k w[k] * (down_k act_k), k in rank order. slots: device array of
- * K blob pointers; nh: optional device count of valid entries (<= K; 0 gives zeros). Replaces experts_forward
- * (kernels.cuh:597-673). K <= 16. */
+ * K blob pointers; nh: optional device count of valid entries (0 gives zeros; a count above K is treated as K).
+ * Replaces experts_forward (kernels.cuh:597-673). K <= 16. */
 int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
                           float* out, void* stream, const int* nh);
 
@@ -97,8 +97,11 @@ int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, 
  * reference, which always receives `act` from its caller. The intermediate activations live in a fixed 32 KB array
  * inside the library image, which every GPU that loads the library keeps until the process exits, so there is no
  * `act` argument and K is limited to 16 experts per call (larger K is rejected with MOEXB_ERR_ARG). The function calls
- * no allocator. The first call on each device looks up the array's device address; make that first call outside any
- * stream capture. All calls on a device share the array, which keeps the previous call's values: nothing in it needs
+ * no allocator. The first call on each device looks up the array's device address, and - with CUDA's default lazy module
+ * loading - is also when the driver loads this library's kernels onto that device, which itself needs some device
+ * memory: make one warm-up call per device and expert format at start-up, before the process commits the rest of the
+ * memory and outside any stream capture. nh as in moexb_experts_forward (a count above K is treated as K).
+ * All calls on a device share the array, which keeps the previous call's values: nothing in it needs
  * clearing between calls, but two calls whose kernels overlap on the GPU (different streams) race on it - keep them
  * on one stream or order them with events. */
 int moexb_experts_forward_static(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* out,
@@ -190,6 +193,12 @@ int moexb_ctx_set_fused_decode(moexb_ctx* ctx, int on);
  * streaming kernel gave up waiting on a pipeline barrier, 3 = the same in the tensor-core grouped GEMM, 5 / 6 = the one-token
  * stack kernel gave up at a grid barrier / on a weight copy (every device-side wait is bounded). The word is cleared. */
 int moexb_ctx_status(moexb_ctx* ctx, int* status);
+/* Exercises the time-out path of the bounded waits without touching any data: which = 0 launches one warp that waits on a
+ * pipeline barrier whose bytes never arrive, which = 1 a one-CTA grid at a grid barrier that expects two arrivals; both
+ * give up after `polls` polls (1..2^20) instead of the production limit. *status receives what moexb_ctx_status then
+ * reports (1 and 5) and the word is cleared. The counterpart of the reference's wait_add_k giving up after timeout_ns and
+ * raising its abort word (kernels.cuh:1055-1089). */
+int moexb_ctx_selftest_timeout(moexb_ctx* ctx, int which, int polls, int* status);
 
 /* Allocates the image of one layer: n_routed experts (ids 0..n_routed-1) and the shared expert (id n_routed), each a
  * blob of format fmt, plus the router [n_routed+1][H] (row n_routed = the shared expert's gate vector).

@@ -49,6 +49,7 @@ SIGNATURES = {
     "moexb_ctx_set_pairs_per_pass": (_i, [_vp, _i]),
     "moexb_ctx_set_fused_decode": (_i, [_vp, _i]),
     "moexb_ctx_status": (_i, [_vp, C.POINTER(_i)]),
+    "moexb_ctx_selftest_timeout": (_i, [_vp, _i, _i, C.POINTER(_i)]),
     "moexb_pairs_reduce": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "moexb_gated_add_rows": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "moexb_shared_expert_add": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),

@@ -165,6 +165,13 @@ class Context:
         check(lib().moexb_ctx_status(self.h, C.byref(st)))
         return st.value
 
+    def selftest_timeout(self, which, polls=4096):
+        """moexb_ctx_selftest_timeout: lets one bounded device-side wait run out (0 = pipeline barrier, 1 = grid barrier)
+        and returns the error word it leaves."""
+        st = C.c_int(0)
+        check(lib().moexb_ctx_selftest_timeout(self.h, which, polls, C.byref(st)))
+        return st.value
+
     def pairs_forward_tc(self, fmt, items, n_items, pairs, X, T, npairs, act, ypair):
         """reference pairs_forward_tc (kernels.cuh:955) on the streaming kernels."""
         check(lib().moexb_pairs_forward_tc(self.h, fmt, _ptr(items), n_items, _ptr(pairs), _ptr(X), T, npairs, _ptr(act), _ptr(ypair), _stream()))

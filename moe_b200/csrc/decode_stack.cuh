@@ -60,7 +60,7 @@ constexpr int DS_XCOL = EH * 2 + 64;          // stride between the hi and lo co
 constexpr int DS_ACOL = EI * 2 + 64;          // the same for an expert's act row
 constexpr int DS_MAXK = 8;
 constexpr int DS_MAXLAYERS = 128;
-constexpr int DS_POLL_LIMIT = 1 << 22;
+constexpr int DS_POLL_LIMIT = 1 << 21;       // polls of a grid barrier (an L2 round trip each: a second or two) before a CTA gives up
 constexpr int DS_ERR_BARRIER = 5, DS_ERR_COPY = 6;
 
 template <int FMT> constexpr int ds_smem_bytes() {
@@ -142,6 +142,27 @@ __device__ __forceinline__ float ds_chunk_sum(const uint8_t* group, int hc) {
             for (int i = 0; i < 4; i++) s += __uint_as_float(w[i] << 16) + __uint_as_float(w[i] & 0xFFFF0000u);
         }
     return s;
+}
+
+// One thread per CTA: arrive at the grid barrier (sync[0], a monotonic counter) and poll until `target` arrivals have been
+// counted. False when another CTA raised the abort flag (sync[1]) or after `limit` polls, in which case the error word and
+// the abort flag are set.
+__device__ __forceinline__ bool ds_barrier_arrive_wait(unsigned* sync, unsigned target, int* err, int limit = DS_POLL_LIMIT) {
+    // release: the CTA's writes (ordered before this by the caller's block barrier) are visible to whoever sees the count
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(sync) : "memory");
+    for (int i = 0; i < limit; i++) {
+        unsigned seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sync) : "memory");
+        if (seen >= target) return true;
+        if ((i & 63) == 63) {
+            unsigned ab;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(sync + 1) : "memory");
+            if (ab) return false;
+        }
+    }
+    atomicExch(err, DS_ERR_BARRIER);
+    atomicExch(sync + 1, 1u);
+    return false;
 }
 
 // WT: router weight type; XBF: the input row is bf16. Symmetric formats run on fp16 operands, zero point on bf16.
@@ -237,23 +258,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     // all CTAs have finished the phase before this call; false: time-out or abort
     auto grid_barrier = [&]() -> bool {
         __syncthreads();
-        if (tid == 0) {
-            // release: the CTA's writes (ordered before this by the barrier above) are visible to whoever sees the count
-            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.sync) : "memory");
-            const unsigned target = (barriers + 1) * (unsigned)grid;
-            int i = 0;
-            for (; i < DS_POLL_LIMIT; i++) {
-                unsigned seen;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.sync) : "memory");
-                if (seen >= target) break;
-                if ((i & 63) == 63) {
-                    unsigned ab;
-                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(a.sync + 1) : "memory");
-                    if (ab) { s_abort = 1; break; }
-                }
-            }
-            if (i == DS_POLL_LIMIT) { atomicExch(a.err, DS_ERR_BARRIER); atomicExch(a.sync + 1, 1u); s_abort = 1; }
-        }
+        if (tid == 0 && !ds_barrier_arrive_wait(a.sync, (barriers + 1) * (unsigned)grid, a.err)) s_abort = 1;
         barriers++;
         __syncthreads();
         return !s_abort;
@@ -505,6 +510,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
 #pragma unroll
         for (int h = 0; h < 2; h++) *reinterpret_cast<float4*>(a.x_out + 1024 * h + 4 * tid) = *reinterpret_cast<const float4*>(xres + 1024 * h + 4 * tid);
     }
+}
+
+// Self-test of the grid barrier's time-out: a grid of ONE CTA arrives at a barrier that expects two arrivals.
+__global__ void selftest_grid_barrier_timeout_k(unsigned* sync, int* err, int limit, int* result) {
+    if (threadIdx.x == 0) *result = ds_barrier_arrive_wait(sync, 2u, err, limit) ? 1 : 0;
 }
 
 }  // namespace moexb

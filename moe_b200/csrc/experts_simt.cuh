@@ -55,7 +55,7 @@ template <int FMT, int WARPS, int KMAX>
 __global__ void __launch_bounds__(WARPS * 32) decode_down_k(const uint8_t* const* __restrict__ slots, const float* __restrict__ w, int K,
                                                             const int* __restrict__ nh, const float* __restrict__ act, float* __restrict__ out) {
     extern __shared__ __align__(16) float as[];
-    if (nh) K = *nh;
+    if (nh) K = min(K, max(*nh, 0));   // the launch sized shared memory for K experts: a larger device count is clamped
     const int d = blockIdx.x * WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31, hf = lane >> 4, c = lane & 15;
     uint4 q[KMAX / 2]; float2 sm[KMAX / 2]; float wk[KMAX / 2];
 #pragma unroll

@@ -61,6 +61,25 @@ static cudaError_t launch_dep(void (*kernel)(P...), dim3 grid, dim3 block, size_
     cfg.attrs = at; cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
 }
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory, occupancy figures) belong to one device, so
+// "once" means once per device: keyed by the device that is current in the calling thread, which is the one the launch
+// that follows goes to.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceOnce {
+    std::mutex mu;
+    bool done[MAX_DEVICES] = {};
+    cudaError_t err[MAX_DEVICES] = {};
+    template <class F>
+    cudaError_t run(F&& f) {
+        int dev = -1;
+        const cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) { err[dev] = f(); done[dev] = true; }
+        return err[dev];
+    }
+};
 inline bool fmt_ok(int fmt) { return fmt == FMT_SYM_F32 || fmt == FMT_SYM_F16 || fmt == FMT_ZP; }
 
 // Calls f.template operator()<FMT>() for the run-time format.
@@ -156,6 +175,10 @@ struct moexb_layer {
     void* router = nullptr;                 // [n_routed + 1][H]
     const uint8_t** slot_table = nullptr;   // device, n_routed + 1 pointers
     std::vector<const uint8_t*> slot_host;
+    // per expert id (index n_routed = the shared expert): weights were put there by an upload, a synthetic fill or a file load.
+    // The image starts zeroed, so an expert that was never loaded contributes zeros; the shared expert runs for every token,
+    // so the layer-level calls refuse to run it unloaded instead of silently adding nothing.
+    std::vector<uint8_t> loaded;
 };
 
 extern "C" {
@@ -175,9 +198,8 @@ static int gemv_any(const WT* W, const float* x, float* y, int I, int O, void* s
         constexpr int WARPS = 4, TO = 4, TR = 8;  // 16 outputs x 8 rows per block: 17 x 8 blocks for the 64-token router
         const int smem = TR * I * (int)sizeof(float);
         REQUIRE(smem <= 200 * 1024, "gemv: I=%d is too large for the batched kernel", I);
-        static std::once_flag once;
-        static cudaError_t attr_err = cudaSuccess;
-        std::call_once(once, [] { attr_err = cudaFuncSetAttribute(gemm_rows_k<WT, WARPS, TO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+        static PerDeviceOnce once;
+        const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(gemm_rows_k<WT, WARPS, TO, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
         if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "gemv: shared memory attribute: %s", cudaGetErrorString(attr_err));
         CUDA_TRY(launch_dep(gemm_rows_k<WT, WARPS, TO, TR>, dim3((O + WARPS * TO - 1) / (WARPS * TO), (rows + TR - 1) / TR), WARPS * 32, smem, S(stream), W, x, y, I, O, rows));
     } else {
@@ -457,6 +479,8 @@ int moexb_layer_create(moexb_ctx* ctx, int fmt, int n_routed, int first_local, i
     L->ctx = ctx; L->fmt = fmt; L->n_routed = n_routed; L->first_local = first_local; L->n_local = n_local; L->router_dtype = router_dtype; L->layout = layout;
     const size_t eb = expert_bytes(fmt);
     cudaError_t e = cudaMalloc((void**)&L->image, (size_t)(n_local + 1) * eb);
+    if (e == cudaSuccess) e = cudaMemset(L->image, 0, (size_t)(n_local + 1) * eb);
+    L->loaded.assign(n_routed + 1, 0);
     if (e == cudaSuccess) e = cudaMalloc(&L->router, (size_t)(n_routed + 1) * EH * (router_dtype == MOEXB_F32 ? 4 : 2));
     if (e == cudaSuccess) e = cudaMalloc((void**)&L->slot_table, (size_t)(n_routed + 1) * sizeof(void*));
     if (e == cudaSuccess) {
@@ -509,6 +533,7 @@ int moexb_layer_upload_expert(moexb_layer* L, int e, const uint8_t* blob_host) {
     const int rc = to_layer_layout(L, L->ctx->staging, const_cast<uint8_t*>(L->slot_host[e]), 1, nullptr);
     if (rc != MOEXB_OK) return rc;
     CUDA_TRY(cudaStreamSynchronize(nullptr));
+    L->loaded[e] = 1;
     return MOEXB_OK;
 }
 
@@ -549,6 +574,8 @@ int moexb_layer_fill_synth(moexb_layer* L, unsigned seed, int layer_index, void*
         if (rc == MOEXB_OK) rc = to_layer_layout(L, c->staging, L->image + (size_t)i * eb, n, S(stream));
         if (rc != MOEXB_OK) return rc;
     }
+    for (int i = 0; i < L->n_local; i++) L->loaded[L->first_local + i] = 1;
+    L->loaded[L->n_routed] = 1;
     return MOEXB_OK;
 }
 
@@ -662,6 +689,7 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
         CUDA_TRY(cudaStreamSynchronize(nullptr));
     }
     int got = L->n_local ? 1 : 0;
+    for (int i = 0; i < L->n_local; i++) L->loaded[L->first_local + i] = 1;
     // the shared expert, when the file holds it as Q4_K too
     const GgufTensor *sg = g->find(p + "ffn_gate_shexp.weight"), *su = g->find(p + "ffn_up_shexp.weight"), *sd = g->find(p + "ffn_down_shexp.weight");
     if (sg && su && sd && sg->type == GGML_Q4_K && su->type == GGML_Q4_K && sd->type == GGML_Q4_K && sg->n_dims == 2 && su->n_dims == 2 &&
@@ -671,6 +699,7 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
         if (rc != MOEXB_OK) return rc;
         CUDA_TRY(cudaStreamSynchronize(nullptr));
         got |= 2;
+        L->loaded[L->n_routed] = 1;
     }
     // router rows and the shared expert's gate vector
     const GgufTensor *rt = g->find(p + "ffn_gate_inp.weight"), *rs = g->find(p + "ffn_gate_inp_shexp.weight");
@@ -764,6 +793,7 @@ int moexb_layer_load_st(moexb_layer* L, const moexb_st* s, const char* prefix, i
         CUDA_TRY(cudaStreamSynchronize(nullptr));
     }
     int got = L->n_local ? 1 : 0;
+    for (int i = 0; i < L->n_local; i++) L->loaded[L->first_local + i] = 1;
     // router rows (mlp.gate.weight [E][H]) and the shared expert's gate vector (mlp.shared_expert_gate.weight [1][H])
     const size_t esz = L->router_dtype == MOEXB_F32 ? 4 : 2;
     const long long E = L->n_routed;
@@ -794,9 +824,8 @@ template <int FMT, bool DOWN>
 static int stream_launch_one(moexb_ctx* c, const StreamArgs& a, void* stream) {
     constexpr int NW = 4, STAGES = FMT == FMT_SYM_F16 ? 4 : 3;
     constexpr int SMEM = st_smem_bytes<FMT, DOWN, NW, STAGES>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_k<FMT, DOWN, NW, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(stream_k<FMT, DOWN, NW, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "stream kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
     stream_k<FMT, DOWN, NW, STAGES><<<2 * c->sms, (NW + 1) * 32, SMEM, S(stream)>>>(a);
@@ -821,9 +850,8 @@ template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2>
 static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
     constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D, NB>();
     static_assert(SMEM * CPS <= 227 * 1024, "shared memory of the resident CTAs");
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "tiled stream kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
     CUDA_TRY(launch_dep(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, CPS * c->sms, NW * 32, SMEM, S(stream), a));
@@ -864,9 +892,8 @@ static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* 
 template <int FMT, bool DOWN>
 static int prefill_launch_one(moexb_ctx* c, const PrefillArgs& a, void* stream) {
     constexpr int SMEM = pf_smem_bytes<FMT, DOWN>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(prefill_k<FMT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(prefill_k<FMT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "prefill kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
     prefill_k<FMT, DOWN><<<c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
@@ -956,6 +983,23 @@ extern "C" int moexb_ctx_status(moexb_ctx* c, int* status) {
     return MOEXB_OK;
 }
 
+// Makes one bounded device-side wait run out on purpose and reports what the kernels' error word then holds.
+// which = 0: the mbarrier wait of the streaming / grouped-GEMM pipelines (a barrier that expects bytes nobody sends);
+// which = 1: the grid barrier of the one-token stack kernel (one CTA, two arrivals expected). Both with `polls` polls
+// instead of the production limits. Nothing faults or hangs: the kernel returns, the context stays usable.
+extern "C" int moexb_ctx_selftest_timeout(moexb_ctx* c, int which, int polls, int* status) {
+    REQUIRE(c && status, "ctx_selftest_timeout: null pointer");
+    REQUIRE((which == 0 || which == 1) && polls > 0 && polls <= (1 << 20), "ctx_selftest_timeout: which=%d polls=%d", which, polls);
+    CUDA_TRY(cudaSetDevice(c->device));
+    CUDA_TRY(cudaMemset(c->nsub, 0, 2 * sizeof(int)));   // scratch of the self-test: [0] result of the wait
+    unsigned* sync = reinterpret_cast<unsigned*>(c->counts);       // scratch: barrier counter and abort flag
+    CUDA_TRY(cudaMemset(sync, 0, 2 * sizeof(unsigned)));
+    if (which == 0) selftest_mbar_timeout_k<<<1, 32>>>(c->err, ST_ERR_FULL_WAIT, polls, c->nsub);
+    else selftest_grid_barrier_timeout_k<<<1, 32>>>(sync, c->err, polls, c->nsub);
+    LAUNCHED("selftest_timeout");
+    return moexb_ctx_status(c, status);
+}
+
 extern "C" {
 
 // Router logits (column n_routed = the shared expert's gate logit) and top-K for T tokens, into the context workspace.
@@ -978,9 +1022,8 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
             // the router weights less with 32 outputs per block
             auto gemm = [&]<int TO, int TR>() -> int {
                 constexpr int WARPS = 8, SMEM = TR * EH * (int)sizeof(float);
-                static std::once_flag once;
-                static cudaError_t attr_err = cudaSuccess;
-                std::call_once(once, [] { attr_err = cudaFuncSetAttribute(route_gemm_k<WT, WARPS, TO, TR, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+                static PerDeviceOnce once;
+                const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(route_gemm_k<WT, WARPS, TO, TR, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
                 if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
                 CUDA_TRY(launch_dep(route_gemm_k<WT, WARPS, TO, TR, NJ>, dim3((E + 1 + WARPS * TO - 1) / (WARPS * TO), (T + TR - 1) / TR), WARPS * 32, SMEM, S(stream),
                                     W, xf, c->logits, EH, E, K, 1, T, c->route_done, o));
@@ -990,9 +1033,8 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
             // kernel (32 tokens x 16 outputs per block, FMA-bound)
             auto gemm2 = [&]() -> int {
                 constexpr int SMEM = 2 * rg2_stage_bytes<WT>();
-                static std::once_flag once;
-                static cudaError_t attr_err = cudaSuccess;
-                std::call_once(once, [] { attr_err = cudaFuncSetAttribute(route_gemm2_k<WT, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+                static PerDeviceOnce once;
+                const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(route_gemm2_k<WT, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
                 if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
                 CUDA_TRY(launch_dep(route_gemm2_k<WT, NJ>, dim3((E + 1 + RG2_TN - 1) / RG2_TN, (T + RG2_TM - 1) / RG2_TM), 256, SMEM, S(stream),
                                     W, xf, c->logits, E, K, 1, T, c->route_done, o));
@@ -1069,9 +1111,8 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             const int maxp = prefill ? PF_NMAX / parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
             // room in shared memory for the routed pairs (12 bytes each), so that the list is written out in full lines
             constexpr int PLAN_STAGE_MAX = 196608;
-            static std::once_flag plan_once;
-            static cudaError_t plan_attr = cudaSuccess;
-            std::call_once(plan_once, [] { plan_attr = cudaFuncSetAttribute(group_plan1_k, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
+            static PerDeviceOnce plan_once;
+            const cudaError_t plan_attr = plan_once.run([] { return cudaFuncSetAttribute(group_plan1_k, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
             const int stage_pairs = plan_attr == cudaSuccess && (size_t)T * K * 12 <= PLAN_STAGE_MAX ? T * K : 0;
             CUDA_TRY(launch_dep(group_plan1_k, 1, 1024, (size_t)stage_pairs * 12, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
                                 prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1, stage_pairs));
@@ -1120,6 +1161,7 @@ int moexb_layer_forward(moexb_ctx* c, moexb_layer* L, const void* X, int x_dtype
     REQUIRE(T > 0 && T <= c->max_tokens, "layer_forward: T=%d exceeds the context's max_tokens=%d", T, c->max_tokens);
     REQUIRE(K > 0 && K <= c->top_k, "layer_forward: K=%d exceeds the context's top_k=%d", K, c->top_k);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "layer_forward: x_dtype=%d", x_dtype);
+    REQUIRE((flags & 1) || L->loaded[L->n_routed], "layer_forward: the shared expert of this layer was never loaded (upload it, or pass flags bit 0 to leave it out)");
     const float* xin;
     int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
@@ -1134,6 +1176,7 @@ int moexb_layer_forward_ep(moexb_ctx* c, moexb_layer* L, const void* X, int x_dt
     REQUIRE(K > 0 && K <= c->top_k, "layer_forward_ep: K=%d exceeds the context's top_k=%d", K, c->top_k);
     REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "layer_forward_ep: x_dtype=%d", x_dtype);
     REQUIRE(shared_t0 >= 0 && shared_t0 <= shared_t1 && shared_t1 <= T, "layer_forward_ep: shared token range [%d, %d) outside 0..%d", shared_t0, shared_t1, T);
+    REQUIRE(shared_t0 == shared_t1 || L->loaded[L->n_routed], "layer_forward_ep: the shared expert of this layer was never loaded");
     const float* xin;
     int rc = layer_input(c, X, x_dtype, T, stream, &xin);
     if (rc != MOEXB_OK) return rc;
@@ -1186,15 +1229,15 @@ template <int FMT, typename WT, bool XBF>
 static int decode_stack_launch(moexb_stack* s, void* stream) {
     moexb_ctx* c = s->ctx;
     constexpr int SMEM = ds_smem_bytes<FMT>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    static int per_sm = 0;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(decode_stack_k<FMT, WT, XBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (attr_err == cudaSuccess) attr_err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_k<FMT, WT, XBF>, DS_THREADS, SMEM);
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] {
+        cudaError_t e = cudaFuncSetAttribute(decode_stack_k<FMT, WT, XBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        int per_sm = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_k<FMT, WT, XBF>, DS_THREADS, SMEM);
+        if (e == cudaSuccess && per_sm < 1) e = cudaErrorLaunchOutOfResources;   // the persistent CTA does not fit an SM of this device
+        return e;
     });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "decode stack kernel: %s", cudaGetErrorString(attr_err));
-    if (per_sm < 1) return fail(MOEXB_ERR_UNSUPPORTED, "decode stack kernel does not fit an SM");
     CUDA_TRY(cudaMemsetAsync(s->dsync, 0, 2 * sizeof(unsigned), S(stream)));
     DecodeStackArgs a{s->dlayers, s->n_layers, s->n_routed, s->K, s->x_in, s->buf[0], c->logits, c->act_split, c->ypair, c->wts, nullptr, nullptr, s->dsync, c->err};
     void* args[] = {&a};
@@ -1222,6 +1265,7 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     for (int l = 0; l < n_layers; l++) {
         REQUIRE(layers[l] && layers[l]->ctx == c, "stack_create: layer %d is null or belongs to another context", l);
         REQUIRE(layers[l]->fmt == layers[0]->fmt && layers[l]->layout == layers[0]->layout, "stack_create: layer %d differs from layer 0 in format or layout", l);
+        REQUIRE(layers[l]->loaded[layers[l]->n_routed], "stack_create: the shared expert of layer %d was never loaded", l);
     }
     CUDA_TRY(cudaSetDevice(c->device));
     moexb_stack* s = new (std::nothrow) moexb_stack;

@@ -37,7 +37,7 @@ template <int NW> constexpr int st_pieces() { return 16 * NW; }
 template <int FMT, int NW> constexpr int st_slot_bytes() { return st_pieces<NW>() * (ST_STRIDE + st_scale_bytes<FMT>()); }
 // activation columns in shared memory: 8 columns of K bf16, column stride K*2 + 64 bytes (conflict-free 16-byte reads)
 template <bool DOWN> constexpr int st_bcol_bytes() { return (DOWN ? EI : EH) * 2 + 64; }
-template <int FMT, bool DOWN, int NW, int STAGES> constexpr int st_smem_bytes() { return STAGES * st_slot_bytes<FMT, NW>() + 8 * st_bcol_bytes<DOWN>() + 256; }
+template <int FMT, bool DOWN, int NW, int STAGES> constexpr int st_smem_bytes() { return STAGES * st_slot_bytes<FMT, NW>() + 8 * st_bcol_bytes<DOWN>() + 256 + 8; }
 
 // Position of input k inside a permuted activation row (see the header comment).
 __host__ __device__ constexpr int split_pos(int k) {
@@ -60,9 +60,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ST_WAIT_LIMIT polls, records why, and lets the caller leave the kernel.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-    for (int i = 0; i < ST_WAIT_LIMIT; i++)
+// Bounded wait: gives up after `limit` polls, records why, and lets the caller leave the kernel.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code, int limit = ST_WAIT_LIMIT) {
+    for (int i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     atomicExch(err, code);
     return false;
@@ -166,11 +166,12 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
     constexpr bool Z = FMT == FMT_ZP;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* bsm = smem + STAGES * SLOT;                                     // 8 activation columns
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);            // full[STAGES], empty[STAGES]
-    StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * STAGES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * BCOL);            // full[STAGES], empty[STAGES], consumer barrier
+    StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * STAGES + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(bars + s), 33); mbar_init(smem_u32(bars + STAGES + s), NW); }
+        mbar_init(smem_u32(bars + 2 * STAGES), NW);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -180,13 +181,21 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
     if (warp == NW) {
         // ---- producer: one warp streams the tiles' row pieces and scale bytes into the ring ----
         int s = 0; uint32_t ph = 0;
+        uint32_t armed = 0, armed_ph = 0;   // per stage: a fill was requested, and the parity its full barrier completes with
+        // a wait ran out: wait (bounded) for the fills already requested, so that no copy is in flight into this CTA's
+        // shared memory when the producer leaves; the consumers run out of polls on their side
+        auto give_up = [&]() {
+            for (int i = 0; i < STAGES; i++)
+                if (armed >> i & 1) mbar_wait(smem_u32(bars + i), armed_ph >> i & 1, a.err, ST_ERR_EMPTY_WAIT);
+        };
         for (int tile = tile0; tile <= tile1; tile++) {
             const bool done = tile == tile1;  // one empty stage after the last tile tells the consumers to stop
             const int sub = done ? -1 : tile / TILES, tin = done ? 0 : tile % TILES;
             const uint8_t* slot = done ? nullptr : a.subs[sub].slot;
             for (int ks = 0; ks < (done ? 1 : KS); ks++) {
                 const uint32_t full = smem_u32(bars + s), empty = smem_u32(bars + STAGES + s);
-                if (!mbar_wait(empty, ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) return;
+                if (!mbar_wait(empty, ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) { give_up(); return; }
+                armed |= 1u << s; armed_ph = (armed_ph & ~(1u << s)) | (ph << s);
                 if (lane == 0) {
                     info[s] = {sub, tin, ks, ks == 0};
                     mbar_arrive_expect_tx(full, done ? 0 : PIECES * ST_PIECE);
@@ -223,7 +232,7 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
         }
         // drain: every slot released, so no copy is in flight when the CTA exits
         for (int i = 0; i < STAGES; i++) {
-            if (!mbar_wait(smem_u32(bars + STAGES + s), ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) return;
+            if (!mbar_wait(smem_u32(bars + STAGES + s), ph ^ 1, a.err, ST_ERR_EMPTY_WAIT)) { give_up(); return; }
             if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         return;
@@ -234,8 +243,17 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
     const int ctid = threadIdx.x;  // 0 .. NW*32-1
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int cur_sub = -1, n = 0, start = 0;
-    int s = 0; uint32_t ph = 0;
+    int s = 0; uint32_t ph = 0, cph = 0;
     const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
+    // barrier over the consumer warps as an mbarrier with a bounded wait: a warp that gave up on a stage never arrives,
+    // and the others then run out of polls here instead of waiting for it for ever
+    auto consumer_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bars + 2 * STAGES));
+        const bool ok = mbar_wait(smem_u32(bars + 2 * STAGES), cph, a.err, ST_ERR_FULL_WAIT);
+        cph ^= 1;
+        return ok;
+    };
     while (true) {
         const uint32_t full = smem_u32(bars + s), empty = smem_u32(bars + STAGES + s);
         if (!mbar_wait(full, ph, a.err, ST_ERR_FULL_WAIT)) return;
@@ -246,7 +264,7 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
             cur_sub = inf.sub;
             const moexb_pair_item it = a.subs[cur_sub];
             n = it.count; start = it.start;
-            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");  // everyone is done with the old columns
+            if (!consumer_sync()) return;  // everyone is done with the old columns
             constexpr int CHUNKS16 = KB * 2 / 16;                        // 16-byte chunks per column
             for (int i = ctid; i < 2 * n * CHUNKS16; i += NW * 32) {
                 const int col = i / CHUNKS16, ch = i % CHUNKS16;
@@ -255,7 +273,7 @@ __global__ void __launch_bounds__((NW + 1) * 32) stream_k(const StreamArgs a) {
                 cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (r * 2 + (col & 1)) * KB + ch * 8);
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
-            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+            if (!consumer_sync()) return;
         }
         if (inf.first) acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
         const uint8_t* st = smem + s * SLOT;
@@ -578,6 +596,20 @@ __global__ void plan_decode_k(const uint8_t* const* __restrict__ slots, const fl
     const int k = threadIdx.x, n = nh ? *nh : K;
     if (k < n) { subs[k] = {slots[k], k, 1}; pairs[k] = {0, k, w[k]}; }
     if (k == 0) *nsub = n;
+}
+
+// Self-test of the bounded waits (moexb_ctx_selftest_timeout): one warp waits on an mbarrier that expects 16 bytes which
+// nobody ever sends. Nothing is in flight, nothing faults: the wait runs out of polls, records `code` and the kernel returns.
+__global__ void selftest_mbar_timeout_k(int* err, int code, int limit, int* polls_done) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_arrive_expect_tx(smem_u32(&bar), 16);
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, err, code, limit);
+    if (threadIdx.x == 0) *polls_done = ok ? 0 : limit;
 }
 
 }  // namespace moexb

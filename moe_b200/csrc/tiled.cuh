@@ -114,9 +114,12 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * NB * BCOL); // full[NW][D]
     // zero point: the sum of the activations over each 32-input chunk, per column: [K slice][group][chunk][8 columns]
     __shared__ __align__(16) float csum[Z ? KS * 8 * 2 * 8 : 4];
+    // set by a warp whose wait on a slice ran out: every warp then stops computing, but all of them keep walking the same
+    // sequence of CTA barriers, wait (bounded) for their own copies in flight and leave together
+    __shared__ volatile int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
-    if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (threadIdx.x == 0) { s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
     __syncthreads();
     // Gate/up: the sub-items come from the kernel before this one. Down: they are older (the gate/up kernel read them
     // too), so the weight copies start while gate/up still runs; only the activation columns wait for it.
@@ -148,6 +151,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};  // acd: the second column block
     int cur_sub = -1, n = 0, start = 0;
+    int issued = min(D, Q), landed = 0;   // slices requested / seen complete by this warp (the lanes agree)
     const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
     for (int q = 0; q < Q; q++) {
         const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, ks = q % KS;
@@ -186,7 +190,9 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
                 __syncthreads();
             }
         }
-        if (!mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT)) return;
+        if (s_abort) continue;   // another warp gave up: no more waits, math or copies - only the barriers above
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT))) { s_abort = 1; continue; }
+        landed = q + 1;
         if (ks == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; acd[0] = acd[1] = acd[2] = acd[3] = 0.f; }
         const uint8_t* sl = ring + (q % D) * SB;
         const uint8_t* bp = bcol + ks * 1024;  // 8 groups of 128 bytes per slice
@@ -262,6 +268,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(q + D);
         }
+        if (q + D < Q) issued = q + D + 1;
         if (ks == KS - 1) {
             // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) of column block b belong to pair slot 4b + t
             const int wt = rin * NW + warp;
@@ -286,6 +293,9 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             }
         }
     }
+    // after a time-out: no copy may still be on its way into this CTA's shared memory when the CTA leaves
+    if (s_abort)
+        for (int q = landed; q < issued; q++) mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT);
 }
 
 template <int FMT, bool DOWN, int NW, int D, int NB = 1>

@@ -19,6 +19,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#include <immintrin.h>
+#include <omp.h>
+#include "../moe_b200/csrc/synth.h"   /* the counter-based generator itself: integer arithmetic, no CUDA types */
 
 #define EH 2048 /* kernels.cuh:422 */
 #define EI 512
@@ -401,4 +404,70 @@ void orc_layer_forward(int fmt, const uint8_t* const* blobs, const void* W, int 
     }
     if (logits_out) memcpy(logits_out, logits, (size_t)T * ld * 4);
     free(logits); free(ie); free(is); free(ic); free(pt); free(pp); free(pw); free(held); free(jb); free(ypair);
+}
+
+/* ---- seeded synthetic experts on the host --------------------------------------------------------------------------------
+ * The benchmark's CPU arm needs the same expert bytes as the GPU without loading the product library. The word generator is
+ * shared source (synth.h, plain C); the half-normal quantile tables and the blob assembly are restated here and pinned
+ * bit for bit against the product's host generator in tests/test_oracle_pins.py. */
+
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+
+static uint16_t g_table_s[SYNTH_TABLE_N], g_table_d[SYNTH_TABLE_N];
+static int g_tables_ready = 0;
+
+/* table[i] = fp16 bits of sigma * q_i, q_i the (i + 0.5) / N quantile of |N(0, 1)| by bisection on erf */
+static void synth_table(double sigma, uint16_t* table) {
+    for (int i = 0; i < SYNTH_TABLE_N; i++) {
+        const double p = (i + 0.5) / SYNTH_TABLE_N;
+        double lo = 0, hi = 10;
+        for (int it = 0; it < 80; it++) {
+            const double mid = 0.5 * (lo + hi);
+            if (erf(mid / sqrt(2.0)) < p) lo = mid; else hi = mid;
+        }
+        table[i] = _cvtss_sh((float)(sigma * 0.5 * (lo + hi)), _MM_FROUND_TO_NEAREST_INT);
+    }
+}
+
+static void synth_tables(void) {
+#pragma omp critical(orc_synth_tables)
+    if (!g_tables_ready) { synth_table(0.02, g_table_s); synth_table(0.01, g_table_d); g_tables_ready = 1; }
+}
+
+/* Raw Q4_K tensors of synthetic expert (layer, expert): gate, up [I][H], down [H][I] as 144-byte super-blocks in blob order */
+void orc_synth_q4k(unsigned seed, int layer, int expert, uint8_t* gate, uint8_t* up, uint8_t* down) {
+    synth_tables();
+    const size_t NB = (size_t)EH * EI / 256;
+    for (size_t sb = 0; sb < 3 * NB; sb++) {
+        uint8_t* d = sb < NB ? gate + sb * 144 : sb < 2 * NB ? up + (sb - NB) * 144 : down + (sb - 2 * NB) * 144;
+        for (uint32_t j = 0; j < 36; j++) {
+            const uint32_t w = synth_q4k_word(seed, layer, expert, sb, j, g_table_d);
+            memcpy(d + 4 * j, &w, 4);
+        }
+    }
+}
+
+/* The synthetic expert (layer, expert) as a blob of format fmt */
+int orc_synth_expert(int fmt, unsigned seed, int layer, int expert, uint8_t* dst) {
+    synth_tables();
+    if (fmt == FMT_ZP) {
+        const size_t part = (size_t)EH * EI / 256 * 144;
+        uint8_t* raw = (uint8_t*)malloc(3 * part);
+        if (!raw) return -1;
+        orc_synth_q4k(seed, layer, expert, raw, raw + part, raw + 2 * part);
+        orc_q4k_to_zp(raw, raw + part, raw + 2 * part, dst);
+        free(raw);
+        return 0;
+    }
+    if (fmt != FMT_SYM_F32 && fmt != FMT_SYM_F16) return -1;
+    for (size_t i = 0; i < Q_BYTES / 4; i++) {
+        const uint32_t w = synth_nibble_word(seed, layer, expert, i);
+        memcpy(dst + 4 * i, &w, 4);
+    }
+    for (size_t g = 0; g < CHUNKS / 2; g++) {
+        const uint16_t h = synth_scale_h(seed, layer, expert, g, g_table_s);
+        if (fmt == FMT_SYM_F16) memcpy(dst + Q_BYTES + 2 * g, &h, 2);
+        else { const float f = orc_half(h); memcpy(dst + Q_BYTES + 4 * g, &f, 4); }
+    }
+    return 0;
 }

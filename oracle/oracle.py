@@ -61,6 +61,18 @@ def expert_bytes(fmt):
     return orc().orc_expert_bytes(fmt)
 
 
+def set_threads(n):
+    """Threads of the OpenMP loops in liboracle.so (router logits, expert pairs), whatever OMP_NUM_THREADS says."""
+    orc().orc_set_threads(int(n))
+
+
+def synth_expert(fmt, seed, layer, expert):
+    """The seeded synthetic expert (layer, expert) as a numpy uint8 blob: the same bytes as the product's generator."""
+    out = np.empty(expert_bytes(fmt), np.uint8)
+    assert orc().orc_synth_expert(fmt, C.c_uint(seed), layer, expert, _p(out)) == 0
+    return out
+
+
 def dequant(fmt, blob):
     out = np.empty(3 * EH * EI, np.float32)
     orc().orc_dequant(fmt, _p(blob), _p(out))

@@ -15,6 +15,7 @@ import torch
 
 import moe_b200 as m
 from oracle import oracle as o
+from parity import check_ffn
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("lib_built")]
 DEV = "cuda:0"
@@ -25,15 +26,6 @@ FMTS = [m.FMT_SYM_F32, m.FMT_SYM_F16, m.FMT_ZP]
 
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
-
-
-def check_ffn(got, ref, fmt, what=""):
-    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
-    rel_l2 = np.linalg.norm(got - ref) / (np.linalg.norm(ref) + 1e-30)
-    max_abs = np.abs(got - ref).max()
-    bar = 2e-3 * max(1.0, np.abs(ref).max() / 57.0)
-    assert rel_l2 <= 1e-3 and max_abs <= bar, f"{what}: rel-L2 {rel_l2:.3e} (bar 1e-3), max-abs {max_abs:.3e} (bar {bar:.3e})"
-    return rel_l2, max_abs
 
 
 @pytest.fixture(scope="module")
@@ -503,35 +495,6 @@ def test_fused_routing_matches_the_entry_points(ctx, layer_sym, T):
         L.close(); c.close()
 
 
-def test_prefill_chunk_of_2048_tokens_both_kernel_families_agree():
-    """The full prefill chunk (2048 bf16 tokens, 256 + 1 experts): the tcgen05 grouped GEMM and the streaming kernels are
-    independent implementations; on the same batch they select the same experts and their outputs agree within the parity
-    bars (each against the other as reference), and a sample of tokens is checked against the oracle."""
-    rng = np.random.default_rng(2048)
-    E, T = 256, 2048
-    c = m.Context(0, max_tokens=T, max_experts=E, top_k=8)
-    L = m.Layer(c, m.FMT_SYM_F16, E)
-    L.fill_synth(0, 0)
-    W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
-    L.set_router(W)
-    X = torch.from_numpy(rng.standard_normal((T, 2048)).astype(np.float32)).to(torch.bfloat16)
-    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
-    out_tc = L.forward(X.to(DEV), T, 8, idx=idx).cpu().numpy().copy()
-    assert c.status() == 0
-    c.set_prefill_min_tokens(1 << 20)
-    idx2 = torch.empty(T, 8, dtype=torch.int32, device=DEV)
-    out_st = L.forward(X.to(DEV), T, 8, idx=idx2).cpu().numpy().copy()
-    assert c.status() == 0
-    assert np.array_equal(idx.cpu().numpy(), idx2.cpu().numpy())
-    check_ffn(out_tc, out_st, m.FMT_SYM_F16, "tcgen05 grouped GEMM against the streaming kernels, 2048 tokens")
-    sample = rng.choice(T, 24, replace=False)
-    host = [m.synth_expert_host(m.FMT_SYM_F16, 0, 0, e) for e in range(E + 1)]
-    ref, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X.float().numpy()[sample], 8)
-    assert np.array_equal(idx.cpu().numpy()[sample], ri)
-    check_ffn(out_tc[sample], ref, m.FMT_SYM_F16, "2048-token chunk, sampled tokens against the oracle")
-    L.close(); c.close()
-
-
 @pytest.mark.parametrize("E,fmt,router,K", [(256, m.FMT_SYM_F16, np.float32, 8), (64, m.FMT_SYM_F32, np.float16, 8), (96, m.FMT_SYM_F16, np.float32, 3),
                                               (32, m.FMT_ZP, np.float16, 8)])
 def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
@@ -577,55 +540,21 @@ def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
     c.close()
 
 
-def test_full_size_stacks_of_40_layers():
-    """BASELINE's full sizes: 40 layers x 257 experts (17 GB resident). The 64-token graph replays to exactly what 40 chained
-    layer calls give (bit for bit: the same kernels, and the graph adds only launch overlap); its first layer matches the
-    oracle (ids identical, outputs inside the bars); the one-token stack as a cooperative kernel agrees with the graph of
-    per-layer kernels inside the bars; nothing sets the error word."""
-    E, K, NL = 256, 8, 40
-    rng = np.random.default_rng(40)
-    c = m.Context(0, max_tokens=64, max_experts=E, top_k=K)
-    layers, Ws = [], []
-    for l in range(NL):
-        L = m.Layer(c, m.FMT_SYM_F16, E)
-        L.fill_synth(0, l)
-        W = (rng.standard_normal((E + 1, 2048)) * 0.02).astype(np.float32)
-        L.set_router(W)
-        layers.append(L); Ws.append(W)
-    X = rng.standard_normal((64, 2048)).astype(np.float32)
-    # 64 tokens: graph == chained calls
-    stack = m.Stack(c, layers, 64, K, m.F32)
-    y_graph = stack.run(dev(X)).cpu().numpy().copy()
-    stack.close()
-    x = dev(X)
-    bufs = [torch.empty(64, 2048, device=DEV), torch.empty(64, 2048, device=DEV)]
-    idx0 = torch.empty(64, K, dtype=torch.int32, device=DEV)
-    first = None
-    for l, L in enumerate(layers):
-        x = L.forward(x, 64, K, out=bufs[l & 1], idx=idx0 if l == 0 else None, flags=2)
-        if l == 0:
-            first = x.cpu().numpy().copy()
-    assert c.status() == 0
-    assert np.isfinite(y_graph).all()
-    assert np.array_equal(y_graph, x.cpu().numpy())
-    # the first block against the oracle
-    host0 = [m.synth_expert_host(m.FMT_SYM_F16, 0, 0, e) for e in range(E + 1)]
-    moe, ri, _, _ = o.layer_forward(m.FMT_SYM_F16, host0, Ws[0], o.rmsnorm(X), K)
-    assert np.array_equal(idx0.cpu().numpy(), ri)
-    check_ffn(first, X + moe, m.FMT_SYM_F16, "first of 40 blocks, 64 tokens")
-    # one token: cooperative kernel against the graph of per-layer kernels
-    x1 = X[:1]
-    c.set_fused_decode(False)
-    g = m.Stack(c, layers, 1, K, m.F32)
-    y_g = g.run(dev(x1)).cpu().numpy().copy()
-    g.close()
-    c.set_fused_decode(True)
-    f = m.Stack(c, layers, 1, K, m.F32)
-    assert f.kernel_count == 1
-    y_f = f.run(dev(x1)).cpu().numpy().copy()
-    f.close()
-    assert c.status() == 0
-    check_ffn(y_f, y_g, m.FMT_SYM_F16, "one token x 40 layers, cooperative kernel against the graph")
-    for L in layers:
-        L.close()
-    c.close()
+def test_bounded_waits_run_out_and_report(ctx, layer_sym):
+    """Every device-side wait is bounded. Two of them are made to run out here, without faulting or hanging anything: a
+    pipeline barrier whose bytes never arrive (the wait of the streaming and grouped-GEMM kernels) and a grid barrier that
+    expects an arrival that never comes (the one-token stack kernel). Each leaves its code in the error word, the status
+    call returns it and clears it, and the context computes correctly afterwards."""
+    assert ctx.status() == 0
+    assert ctx.selftest_timeout(0, 4096) == 1      # ST_ERR_FULL_WAIT
+    assert ctx.status() == 0                       # cleared by the read
+    assert ctx.selftest_timeout(1, 4096) == 5      # DS_ERR_BARRIER
+    assert ctx.status() == 0
+    with pytest.raises(m.MoexbError):
+        ctx.selftest_timeout(2, 4096)
+    L, W, host = layer_sym
+    X = np.random.default_rng(77).standard_normal((4, 2048)).astype(np.float32)
+    out = L.forward(dev(X), 4, 8).cpu().numpy()
+    ref, _, _, _ = o.layer_forward(m.FMT_SYM_F16, host, W, X, 8)
+    assert ctx.status() == 0
+    check_ffn(out, ref, m.FMT_SYM_F16, "layer after the time-out self-tests")

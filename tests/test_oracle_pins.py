@@ -147,3 +147,12 @@ def test_layer_against_float64_statement():
             acc += ww * ffn(blobs[e])
         acc += ffn(blobs[E]) / (1 + np.exp(-(W[E].astype(np.float64) @ x)))
         assert relmax(out[t], acc) < 1e-5
+
+
+def test_host_generator_of_the_checker_matches_the_product_generator(lib_built):
+    """The benchmark's CPU arm builds its experts with the checker library alone; the bytes are the product's (whose device
+    generator the GPU tests compare with its host generator)."""
+    import moe_b200 as m
+    for fmt in (o.FMT_SYM_F32, o.FMT_SYM_F16, o.FMT_ZP):
+        for layer, e in ((0, 0), (39, 256), (7, 131)):
+            assert np.array_equal(o.synth_expert(fmt, 5, layer, e), m.synth_expert_host(fmt, 5, layer, e)), (fmt, layer, e)
