@@ -192,19 +192,23 @@ class CpuArm:
 
 
 def cpu_baseline(workload, reps):
-    """cpu_baseline object of a workload: all host cores, and the reference's own default thread count beside it."""
-    arm = CpuArm(workload, 2 if WORKLOADS[workload][0] <= 64 else 1)
-    base = arm.report(arm.timed(arm.cores, 1, reps), arm.cores, reps)
-    dflt = reference_default_threads(arm.cores)
-    if dflt != arm.cores:
-        d = arm.report(arm.timed(dflt, 1, reps), dflt, reps)
-        base["reference_default_threads"] = {"threads": dflt, "value": d["value"], "unit": "tokens/s", "rule": "clamp(cores / 2, 2, 8), moex.cu:173"}
-    return base
+    """cpu_baseline object of a workload: all host cores, and the reference's own default thread count beside it. Timed in a
+    process of its own - the reference arm of this file - because the reference's thread pool spin-waits on every core it
+    was given, and this process's CUDA and torch threads would share those cores with it."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", workload, "--steps", str(reps), "--warmup", "3"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMP_NUM_THREADS")}
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    if r.returncode or not lines:
+        return {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "unavailable", "sample": (r.stderr or r.stdout)[-300:]}
+    return json.loads(lines[-1])["cpu_baseline"]
 
 
 def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
+    # idle OpenMP workers of the C port (router, top-k) must not spin on the cores the reference's own pool is about to use
+    os.environ.setdefault("OMP_WAIT_POLICY", "passive")
     T, NL, fmtname, xdt, _ = WORKLOADS[args.workload]
     arm = CpuArm(args.workload, 2 if T <= 64 else 1)
     # each step of this arm is one pass over the bounded sample, on every host core (the thread count is set explicitly: a

@@ -114,12 +114,9 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * NB * BCOL); // full[NW][D]
     // zero point: the sum of the activations over each 32-input chunk, per column: [K slice][group][chunk][8 columns]
     __shared__ __align__(16) float csum[Z ? KS * 8 * 2 * 8 : 4];
-    // set by a warp whose wait on a slice ran out: every warp then stops computing, but all of them keep walking the same
-    // sequence of CTA barriers, wait (bounded) for their own copies in flight and leave together
-    __shared__ volatile int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
-    if (threadIdx.x == 0) { s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
     // Gate/up: the sub-items come from the kernel before this one. Down: they are older (the gate/up kernel read them
     // too), so the weight copies start while gate/up still runs; only the activation columns wait for it.
@@ -151,7 +148,10 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};  // acd: the second column block
     int cur_sub = -1, n = 0, start = 0;
+    // A warp whose wait on a slice runs out stops computing and requesting, but keeps walking the same sequence of CTA
+    // barriers as the others (so nobody is left waiting for it), then waits (bounded) for its own copies in flight.
     int issued = min(D, Q), landed = 0;   // slices requested / seen complete by this warp (the lanes agree)
+    bool dead = false;
     const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
     for (int q = 0; q < Q; q++) {
         const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, ks = q % KS;
@@ -190,8 +190,8 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
                 __syncthreads();
             }
         }
-        if (s_abort) continue;   // another warp gave up: no more waits, math or copies - only the barriers above
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT))) { s_abort = 1; continue; }
+        if (dead) continue;   // gave up earlier: no more waits, math or copies - only the barriers above
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT))) { dead = true; continue; }
         landed = q + 1;
         if (ks == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; acd[0] = acd[1] = acd[2] = acd[3] = 0.f; }
         const uint8_t* sl = ring + (q % D) * SB;
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
         }
     }
     // after a time-out: no copy may still be on its way into this CTA's shared memory when the CTA leaves
-    if (s_abort)
+    if (dead)
         for (int q = landed; q < issued; q++) mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT);
 }
 
