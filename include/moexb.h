@@ -191,12 +191,14 @@ int moexb_ctx_set_pairs_per_pass(moexb_ctx* ctx, int pairs);
 int moexb_ctx_set_fused_decode(moexb_ctx* ctx, int on);
 /* Waits for the device and reads the error word of the kernels: 0 = none; 1 / 2 = a consumer warp / the producer warp of a
  * streaming kernel gave up waiting on a pipeline barrier, 3 = the same in the tensor-core grouped GEMM, 5 / 6 = the one-token
- * stack kernel gave up at a grid barrier / on a weight copy (every device-side wait is bounded). The word is cleared. */
+ * stack kernel gave up at a grid barrier / on a weight copy, 7 / 8 = an expert-parallel rank gave up waiting for a peer's
+ * dispatch / combine flag (every device-side wait is bounded). The word is cleared. */
 int moexb_ctx_status(moexb_ctx* ctx, int* status);
 /* Exercises the time-out path of the bounded waits without touching any data: which = 0 launches one warp that waits on a
  * pipeline barrier whose bytes never arrive, which = 1 a one-CTA grid at a grid barrier that expects two arrivals; both
- * give up after `polls` polls (1..2^20) instead of the production limit. *status receives what moexb_ctx_status then
- * reports (1 and 5) and the word is cleared. The counterpart of the reference's wait_add_k giving up after timeout_ns and
+ * give up after `polls` polls (1..2^20) instead of the production limit; which = 2 the same for the expert-parallel
+ * kernels' wait on a flag that a peer GPU raises. *status receives what moexb_ctx_status then reports (1, 5 and 8) and the
+ * word is cleared. The counterpart of the reference's wait_add_k giving up after timeout_ns and
  * raising its abort word (kernels.cuh:1055-1089). */
 int moexb_ctx_selftest_timeout(moexb_ctx* ctx, int which, int polls, int* status);
 
@@ -297,6 +299,55 @@ int moexb_layer_forward_ep(moexb_ctx* ctx, moexb_layer* layer, const void* X, in
 int moexb_ep_residual_norm(moexb_ctx* ctx, moexb_layer* next, const float* x, const float* total, float* out, int T,
                            void* stream);
 
+/* ---- expert parallelism with the token all-to-all over peer memory ------------------------------------------------------ */
+
+/* The path the batched configurations use on 2, 4 or 8 GPUs of one NVLink node, one process per GPU. Rank r of `world` holds
+ * the routed experts [r * E / world, (r + 1) * E / world) of every layer (moexb_layer_create's first_local / n_local; router
+ * and shared expert on every rank) and OWNS the tokens [r * T / world, (r + 1) * T / world) (remainders to the first ranks):
+ * it keeps their residual rows, normalises and routes them, runs the shared expert for them and returns their outputs. Per
+ * layer the kernels exchange, by plain stores into the peers' mapped "exchange buffers": each token's ids and weights to
+ * every rank and its normalised activation row to the ranks that hold one of its selected experts (dispatch); and one
+ * partial output row per (token, rank that ran one of its experts) back to the token's owner (combine), who adds the
+ * partial rows in rank order, the shared expert and the residual. Flags in the same buffers order the steps; every wait on
+ * a peer is bounded (moexb_ctx_status reports 7 / 8 when a dispatch / combine flag never came). No NCCL call is made. The
+ * reference has no multi-GPU path; the grouping that is sharded is the host loop at moex.cu:1466-1506, and the bounded
+ * device-side wait follows wait_add_k (kernels.cuh:1055-1089).
+ *
+ * Exchange buffers: every rank allocates one (moexb_ep_buffer_alloc, which also returns a 64-byte handle), passes the handle
+ * to the other processes by any means (the tests and the benchmark use torch.distributed), and maps the others'
+ * (moexb_ep_buffer_open: cudaIpcOpenMemHandle, peer access enabled on demand). In one process (several contexts on one GPU:
+ * how the single-GPU tests drive this path) the pointers are used as they are. */
+typedef struct moexb_ep moexb_ep;
+size_t moexb_ep_buffer_bytes(int max_tokens, int top_k, int world); /* 0 for bad arguments; world <= 8 */
+int moexb_ep_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64 /* may be null */);
+int moexb_ep_buffer_open(const unsigned char* handle64, void** ptr);
+int moexb_ep_buffer_close(void* ptr); /* a pointer from moexb_ep_buffer_open */
+int moexb_ep_buffer_free(void* ptr);  /* a pointer from moexb_ep_buffer_alloc */
+/* bufs[world]: the exchange buffer of every rank as a device pointer valid in this process (bufs[rank] = the local one), each
+ * of moexb_ep_buffer_bytes(T, K, world) bytes. T tokens per step (world <= T <= the context's max_tokens), K experts per
+ * token, n_routed routed experts per layer. While the object exists the context's activation, id and weight workspace lives
+ * in the local exchange buffer: use the context for this path only. */
+int moexb_ep_create(moexb_ctx* ctx, int rank, int world, int T, int K, int n_routed, void* const* bufs, moexb_ep** out);
+int moexb_ep_destroy(moexb_ep* ep);
+int moexb_ep_own_tokens(const moexb_ep* ep, int* first, int* count);
+/* A step = begin_step, then for each layer l = 0.. dispatch(l) and experts(l), then finish. Every rank makes the same calls
+ * in the same order; all are enqueued on `stream` without synchronising and can be captured in a CUDA graph.
+ *   begin_step  advances the step number the flags carry.
+ *   dispatch    l == 0: takes the own rows of X [T][H] (x_dtype; every rank passes the whole batch); l > 0: adds up layer
+ *               l - 1 for the own tokens (waits for the peers' partial rows). Then normalises (residual != 0: the blocks
+ *               x_{l+1} = x_l + moe_l(rmsnorm(x_l)); residual == 0: the plain layer moe(X), single layer only), routes the
+ *               own tokens and sends ids, weights and activation rows.
+ *   experts     waits for all ranks' dispatch of layer l, runs the pairs of the experts held here (and the shared expert for
+ *               the own tokens) and sends the partial rows to the token owners.
+ *   finish      adds up the last layer: out_own [own tokens][H] f32. */
+int moexb_ep_begin_step(moexb_ep* ep, void* stream);
+int moexb_ep_dispatch(moexb_ep* ep, moexb_layer* layer, int l, const void* X, int x_dtype, int residual, void* stream);
+int moexb_ep_experts(moexb_ep* ep, moexb_layer* layer, int l, void* stream);
+int moexb_ep_finish(moexb_ep* ep, int n_layers, int residual, float* out_own, void* stream);
+/* The whole step in one call. */
+int moexb_ep_step(moexb_ep* ep, moexb_layer* const* layers, int n_layers, const void* X, int x_dtype, int residual,
+                  float* out_own, void* stream);
+
 /* ---- a stack of layers as one replayable unit ---------------------------------------------------------------------- */
 
 typedef struct moexb_stack moexb_stack;
@@ -319,6 +370,9 @@ int moexb_stack_run(moexb_stack* stack, const void* X, float* out, void* stream)
 /* Host buffers (pinned memory recommended): host->device copy of X, the graph, device->host copy of the result, then
  * waits for the stream. This is the call an engine that keeps activations on the host makes once per step. */
 int moexb_stack_run_host(moexb_stack* stack, const void* X_host, float* out_host, void* stream);
+/* The expert-parallel step (moexb_ep_step) captured as one CUDA graph: moexb_stack_run / _run_host then take the whole batch
+ * X [T][H] and return this rank's own rows [own tokens][H]. Every rank replays its graph once per step. */
+int moexb_ep_stack_create(moexb_ep* ep, moexb_layer* const* layers, int n_layers, int x_dtype, int residual, struct moexb_stack** out);
 /* Kernel launches of one replay. */
 int moexb_stack_kernel_count(moexb_stack* stack);
 

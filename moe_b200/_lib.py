@@ -86,6 +86,20 @@ SIGNATURES = {
     "moexb_layer_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp]),
     "moexb_layer_forward_ep": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moexb_ep_residual_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "moexb_ep_buffer_bytes": (C.c_size_t, [_i, _i, _i]),
+    "moexb_ep_buffer_alloc": (_i, [C.c_size_t, C.POINTER(_vp), _vp]),
+    "moexb_ep_buffer_open": (_i, [_vp, C.POINTER(_vp)]),
+    "moexb_ep_buffer_close": (_i, [_vp]),
+    "moexb_ep_buffer_free": (_i, [_vp]),
+    "moexb_ep_create": (_i, [_vp, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp)]),
+    "moexb_ep_destroy": (_i, [_vp]),
+    "moexb_ep_own_tokens": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "moexb_ep_begin_step": (_i, [_vp, _vp]),
+    "moexb_ep_dispatch": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp]),
+    "moexb_ep_experts": (_i, [_vp, _vp, _i, _vp]),
+    "moexb_ep_finish": (_i, [_vp, _i, _i, _vp, _vp]),
+    "moexb_ep_step": (_i, [_vp, C.POINTER(_vp), _i, _vp, _i, _i, _vp, _vp]),
+    "moexb_ep_stack_create": (_i, [_vp, C.POINTER(_vp), _i, _i, _i, C.POINTER(_vp)]),
     "moexb_stack_create": (_i, [_vp, C.POINTER(_vp), _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "moexb_stack_destroy": (_i, [_vp]),
     "moexb_stack_run": (_i, [_vp, _vp, _vp, _vp]),

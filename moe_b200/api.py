@@ -329,6 +329,88 @@ def ep_residual_norm(ctx, next_layer, x, total, out, T):
     return out
 
 
+class ExchangeBuffer:
+    """One rank's exchange buffer of the expert-parallel path: device memory that the peers map (moexb_ep_buffer_*)."""
+
+    def __init__(self, max_tokens, top_k, world):
+        self.bytes = lib().moexb_ep_buffer_bytes(max_tokens, top_k, world)
+        p = C.c_void_p()
+        self._handle = (C.c_ubyte * 64)()
+        check(lib().moexb_ep_buffer_alloc(self.bytes, C.byref(p), self._handle))
+        self.ptr, self._opened = p.value, []
+
+    @property
+    def handle(self):
+        """The 64 bytes another process of this node passes to open_peer()."""
+        return bytes(self._handle)
+
+    def open_peer(self, handle):
+        """Maps a peer's buffer from its handle; returns the device pointer (valid until close())."""
+        h = (C.c_ubyte * 64).from_buffer_copy(handle)
+        p = C.c_void_p()
+        check(lib().moexb_ep_buffer_open(h, C.byref(p)))
+        self._opened.append(p.value)
+        return p.value
+
+    def close(self):
+        for p in self._opened:
+            lib().moexb_ep_buffer_close(p)
+        self._opened = []
+        if self.ptr:
+            lib().moexb_ep_buffer_free(self.ptr)
+            self.ptr = None
+
+
+class EP:
+    """moexb_ep: this rank's part of the expert-parallel path. bufs: the exchange buffer of every rank as a device pointer
+    valid here (index = rank). While it exists the context serves this path only."""
+
+    def __init__(self, ctx, rank, world, T, K, n_routed, bufs):
+        arr = (C.c_void_p * world)(*bufs)
+        h = C.c_void_p()
+        check(lib().moexb_ep_create(ctx.h, rank, world, T, K, n_routed, arr, C.byref(h)))
+        self.h, self.ctx, self.rank, self.world, self.T, self.K = h, ctx, rank, world, T, K
+        f, n = C.c_int(0), C.c_int(0)
+        check(lib().moexb_ep_own_tokens(h, C.byref(f), C.byref(n)))
+        self.first_token, self.n_own = f.value, n.value
+
+    def begin_step(self):
+        check(lib().moexb_ep_begin_step(self.h, _stream()))
+
+    def dispatch(self, layer, l, X=None, residual=True):
+        x_dtype = BF16 if (X is not None and X.dtype == torch.bfloat16) else F32
+        check(lib().moexb_ep_dispatch(self.h, layer.h, l, _ptr(X), x_dtype, int(residual), _stream()))
+
+    def experts(self, layer, l):
+        check(lib().moexb_ep_experts(self.h, layer.h, l, _stream()))
+
+    def finish(self, n_layers, out_own, residual=True):
+        check(lib().moexb_ep_finish(self.h, n_layers, int(residual), _ptr(out_own), _stream()))
+        return out_own
+
+    def step(self, layers, X, out_own, residual=True):
+        """moexb_ep_step: the whole step enqueued on the current stream."""
+        arr = (C.c_void_p * len(layers))(*[l.h for l in layers])
+        x_dtype = BF16 if X.dtype == torch.bfloat16 else F32
+        check(lib().moexb_ep_step(self.h, arr, len(layers), _ptr(X), x_dtype, int(residual), _ptr(out_own), _stream()))
+        return out_own
+
+    def stack(self, layers, x_dtype=F32, residual=True):
+        """moexb_ep_stack_create: the step captured as one CUDA graph; run / run_host take the whole batch [T][H] and
+        return this rank's own rows [n_own][H]."""
+        arr = (C.c_void_p * len(layers))(*[l.h for l in layers])
+        h = C.c_void_p()
+        check(lib().moexb_ep_stack_create(self.h, arr, len(layers), x_dtype, int(residual), C.byref(h)))
+        s = Stack.__new__(Stack)
+        s.h, s.T, s.layers, s.x_dtype, s.out_rows = h, self.T, layers, x_dtype, self.n_own
+        return s
+
+    def close(self):
+        if self.h:
+            lib().moexb_ep_destroy(self.h)
+            self.h = None
+
+
 class Stack:
     """moexb_stack: n layers chained as residual blocks for a fixed token count, replayed as one CUDA graph."""
 
@@ -336,14 +418,14 @@ class Stack:
         arr = (C.c_void_p * len(layers))(*[l.h for l in layers])
         h = C.c_void_p()
         check(lib().moexb_stack_create(ctx.h, arr, len(layers), T, K, x_dtype, int(residual), C.byref(h)))
-        self.h, self.T, self.layers, self.x_dtype = h, T, layers, x_dtype
+        self.h, self.T, self.layers, self.x_dtype, self.out_rows = h, T, layers, x_dtype, T
 
     @property
     def kernel_count(self):
         return lib().moexb_stack_kernel_count(self.h)
 
     def run(self, X, out=None):
-        out = torch.empty(self.T, EH, device=X.device, dtype=torch.float32) if out is None else out
+        out = torch.empty(self.out_rows, EH, device=X.device, dtype=torch.float32) if out is None else out
         check(lib().moexb_stack_run(self.h, _ptr(X), _ptr(out), _stream()))
         return out
 

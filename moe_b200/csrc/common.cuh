@@ -33,6 +33,28 @@ __host__ __device__ constexpr size_t expert_bytes(int fmt) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- flags that another GPU raises (expert parallelism, ep.cuh) ----
+constexpr unsigned EP_PHASES = 256;           // a flag holds step * EP_PHASES + layer + 1: layers of a step must stay below this
+constexpr int EP_POLL_LIMIT = 1 << 21;        // polls (a local L2 round trip and a short sleep each: a second or two in all) before a wait gives up
+constexpr int EP_ERR_DISPATCH_WAIT = 7, EP_ERR_COMBINE_WAIT = 8;
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for *flag >= target; false (and the error word set) when it ran out of polls.
+__device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned target, int* err, int code, int limit = EP_POLL_LIMIT) {
+    for (int i = 0; i < limit; i++) {
+        if ((int)(ld_acquire_sys(flag) - target) >= 0) return true;
+        if (i > 64) __nanosleep(200);
+    }
+    atomicExch(err, code);
+    return false;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");

@@ -1,0 +1,196 @@
+// Expert parallelism over the GPUs of one NVLink node: the token all-to-all done by the path's own kernels over peer memory.
+//
+// Rank r of R holds the routed experts [exp0[r], exp0[r+1]) of every layer (router and shared expert replicated) and OWNS
+// the tokens [tok0[r], tok0[r+1]): it alone keeps their residual rows, normalises and routes them, runs the shared expert
+// for them and produces their outputs. Every rank has one "exchange buffer" of the same layout, mapped into all the others
+// (peer pointers), holding for ALL T tokens the normalised activation rows in the 16-bit split form the expert kernels
+// read, the selected expert ids and routing weights, and per source rank one partial output row for each own token.
+// One layer on rank r:
+//   dispatch  r's routing kernel selects the experts of its own tokens; ep_dispatch_push_k then stores each token's ids
+//             and weights into every peer's buffer and its activation row into the buffers of the ranks that hold one of
+//             its selected experts (plain st.global through the peer mapping), and raises r's dispatch flag on every peer;
+//   experts   the planner waits for all R dispatch flags, groups the (token, expert) pairs of the experts held here, the
+//             gate/up and down kernels run as on one GPU (all their reads are local HBM);
+//   combine   ep_partial_push_k adds, per token, the weighted rows of the experts held here in router-rank order and stores
+//             that ONE partial row into the owner's buffer (only where this rank had a selected expert), then raises r's
+//             combine flag on every peer; ep_combine_norm_k on the owner waits for all R combine flags and adds the
+//             partial rows in rank order 0..R-1, the shared expert's row and the residual, normalises, and the next
+//             layer's dispatch follows.
+// A flag is a 32-bit word per source rank holding step * EP_PHASES + layer + 1 of the last completed push (monotonic; the
+// step counter lives in device memory so that a captured graph can be replayed). Writers order data before flag with
+// __threadfence_system() and a release store at system scope; readers poll with acquire loads at system scope and read the
+// peer-written data past L1. Every poll loop is bounded: on a time-out the kernel records EP_ERR_* in the context's error
+// word and carries on with whatever is in the buffer (always valid ids and finite numbers from an earlier layer), so
+// nothing hangs or faults and the host sees the failure in moexb_ctx_status.
+// Why a rank can never overwrite data a peer still reads: each rank waits for ALL ranks' flags in both waits, so a rank is
+// at most one phase ahead of any other; the rows it pushes in phase p+1 are read by the peer's kernels of phase p+1 only,
+// which start after the peer's own phase-p push, which is what this rank waited for.
+#pragma once
+#include "common.cuh"
+#include "stream.cuh"
+
+namespace moexb {
+
+constexpr int EP_MAX_RANKS = 8;
+
+struct EpGeom {
+    int rank, world, T, K, n_own_max;
+    int tok0[EP_MAX_RANKS + 1];   // rank r owns tokens [tok0[r], tok0[r+1])
+    int exp0[EP_MAX_RANKS + 1];   // and holds routed experts [exp0[r], exp0[r+1])
+};
+struct EpLayout { size_t xs, idx, w, part, flag_a, flag_b, bytes; };   // byte offsets inside an exchange buffer
+struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };                        // exchange buffer of every rank, as mapped here
+
+__host__ __device__ inline size_t ep_align(size_t x) { return (x + 255) & ~(size_t)255; }
+__host__ inline EpLayout ep_layout(int T, int K, int world) {
+    EpLayout l;
+    const size_t n_own_max = (T + world - 1) / world;
+    size_t at = 0;
+    l.xs = at; at = ep_align(at + (size_t)T * 2 * EH * 2);
+    l.idx = at; at = ep_align(at + (size_t)T * K * 4);
+    l.w = at; at = ep_align(at + (size_t)T * K * 4);
+    l.part = at; at = ep_align(at + (size_t)world * n_own_max * EH * 4);
+    l.flag_a = at; at = ep_align(at + EP_MAX_RANKS * 4);
+    l.flag_b = at; at = ep_align(at + EP_MAX_RANKS * 4);
+    l.bytes = at;
+    return l;
+}
+
+// The block's peer stores are ordered before the ticket; the last block of the grid then raises this rank's flag
+// (flag_off inside the exchange buffer) on every peer.
+__device__ __forceinline__ void ep_signal_peers(const EpGeom& g, const EpPeers& p, size_t flag_off, unsigned value, int* ticket, int blocks) {
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int got = atomicAdd(ticket, 1);
+        s_last = got == blocks - 1;
+        if (s_last) *ticket = 0;
+    }
+    __syncthreads();
+    if (s_last && (int)threadIdx.x < g.world && (int)threadIdx.x != g.rank) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<unsigned*>(p.base[threadIdx.x] + flag_off) + g.rank, value);
+    }
+}
+
+__global__ void ep_step_k(unsigned* step) { *step += 1; }
+
+// Dispatch. grid (own tokens, world), 256 threads: block (i, dst) sends token tok0[rank] + i to rank dst: ids and weights
+// always (the planner there walks all T tokens), the activation row (row_bytes: 4 or 8 KB) only if dst holds one of the
+// token's selected experts.
+__global__ void __launch_bounds__(256) ep_dispatch_push_k(const EpGeom g, const EpPeers p, const EpLayout lay, int row_bytes,
+                                                          const unsigned* __restrict__ step, unsigned phase, int* ticket) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = g.tok0[g.rank] + blockIdx.x, dst = blockIdx.y, K = g.K;
+    if (dst != g.rank) {
+        const uint8_t* lb = p.base[g.rank];
+        uint8_t* db = p.base[dst];
+        const int* idx = reinterpret_cast<const int*>(lb + lay.idx) + (size_t)t * K;
+        const float* w = reinterpret_cast<const float*>(lb + lay.w) + (size_t)t * K;
+        bool needed = false;
+        for (int r = 0; r < K; r++) { const int e = idx[r]; needed |= e >= g.exp0[dst] && e < g.exp0[dst + 1]; }
+        if ((int)threadIdx.x < K) reinterpret_cast<int*>(db + lay.idx)[(size_t)t * K + threadIdx.x] = idx[threadIdx.x];
+        else if ((int)threadIdx.x < 2 * K) reinterpret_cast<float*>(db + lay.w)[(size_t)t * K + threadIdx.x - K] = w[threadIdx.x - K];
+        if (needed) {
+            const uint4* src = reinterpret_cast<const uint4*>(lb + lay.xs + (size_t)t * row_bytes);
+            uint4* out = reinterpret_cast<uint4*>(db + lay.xs + (size_t)t * row_bytes);
+            for (int i = threadIdx.x; i < row_bytes / 16; i += 256) out[i] = src[i];
+        }
+    }
+    ep_signal_peers(g, p, lay.flag_a, *step * EP_PHASES + phase, ticket, gridDim.x * gridDim.y);
+}
+
+// Combine, sending side. grid T, 256 threads: block t adds the rows ypair[t*K + r] of the ranks r whose expert is held
+// here, in rank order (the sum reduce_residual_norm_k forms for a rank's share), and stores the one partial row into the
+// token owner's buffer at [this rank][token's place among the owner's tokens]. Tokens none of whose experts are held here
+// send nothing; the owner derives the same from the ids.
+__global__ void __launch_bounds__(256) ep_partial_push_k(const EpGeom g, const EpPeers p, const EpLayout lay, const float* __restrict__ ypair,
+                                                         const unsigned* __restrict__ step, unsigned phase, int* ticket) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, K = g.K;
+    const int* idx = reinterpret_cast<const int*>(p.base[g.rank] + lay.idx) + (size_t)t * K;
+    unsigned have = 0;
+    for (int r = 0; r < K; r++) { const int e = __ldcg(idx + r); if (e >= g.exp0[g.rank] && e < g.exp0[g.rank + 1]) have |= 1u << r; }
+    if (have) {
+        int owner = 0;
+        while (t >= g.tok0[owner + 1]) owner++;
+        float* dst = reinterpret_cast<float*>(p.base[owner] + lay.part) + ((size_t)g.rank * g.n_own_max + (t - g.tok0[owner])) * EH;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int k0 = 1024 * h + 4 * threadIdx.x;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int rb = 0; rb < K; rb += 8) {  // eight rows in flight, added in rank order
+                float4 y[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (rb + u < K && (have >> (rb + u) & 1)) y[u] = *reinterpret_cast<const float4*>(ypair + ((size_t)t * K + rb + u) * EH + k0);
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (rb + u < K && (have >> (rb + u) & 1)) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
+            }
+            *reinterpret_cast<float4*>(dst + k0) = acc;
+        }
+    }
+    ep_signal_peers(g, p, lay.flag_b, *step * EP_PHASES + phase, ticket, gridDim.x);
+}
+
+// Combine, owner's side. grid own tokens, 256 threads: waits for the combine flags of all ranks, then for own token i:
+// value = sum over source ranks 0..R-1 (those that hold one of the token's experts) of their partial row, + the shared
+// expert's row, + the residual row x[i] when x is given. x[i] and out[i] receive the value when given. When xn is given the
+// next layer's input is left there (absolute token index): rmsnorm(value) if norm, else the value itself, with its 16-bit
+// split in xs when xs is given.
+template <bool F16>
+__global__ void __launch_bounds__(256) ep_combine_norm_k(const EpGeom g, const uint8_t* __restrict__ local, const EpLayout lay,
+                                                         const float* __restrict__ extra, float* __restrict__ x, float* __restrict__ out,
+                                                         float* __restrict__ xn, uint16_t* __restrict__ xs, int norm, float eps,
+                                                         const unsigned* __restrict__ step, unsigned phase, int* err) {
+    pdl_wait();
+    pdl_trigger();
+    const int i = blockIdx.x, t = g.tok0[g.rank] + i, K = g.K;
+    if ((int)threadIdx.x < g.world && (int)threadIdx.x != g.rank)
+        ep_wait_flag(reinterpret_cast<const unsigned*>(local + lay.flag_b) + threadIdx.x, *step * EP_PHASES + phase, err, EP_ERR_COMBINE_WAIT);
+    __syncthreads();
+    __threadfence_system();
+    // the ids of the layer whose partial rows these are: the routing kernel of the next layer has not run yet
+    const int* idx = reinterpret_cast<const int*>(local + lay.idx) + (size_t)t * K;
+    unsigned need = 0;
+    for (int r = 0; r < K; r++) {
+        const int e = idx[r];
+        for (int s = 0; s < g.world; s++) if (e >= g.exp0[s] && e < g.exp0[s + 1]) need |= 1u << s;
+    }
+    const float* part = reinterpret_cast<const float*>(local + lay.part);
+    float v[8];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int k0 = 1024 * h + 4 * threadIdx.x;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), ye = acc, yx = acc;
+        if (extra) ye = *reinterpret_cast<const float4*>(extra + (size_t)t * EH + k0);
+        if (x) yx = *reinterpret_cast<const float4*>(x + (size_t)i * EH + k0);
+        float4 y[EP_MAX_RANKS];
+#pragma unroll
+        for (int s = 0; s < EP_MAX_RANKS; s++)
+            if (s < g.world && (need >> s & 1)) y[s] = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)s * g.n_own_max + i) * EH + k0));
+#pragma unroll
+        for (int s = 0; s < EP_MAX_RANKS; s++)
+            if (s < g.world && (need >> s & 1)) { acc.x += y[s].x; acc.y += y[s].y; acc.z += y[s].z; acc.w += y[s].w; }
+        if (extra) { acc.x += ye.x; acc.y += ye.y; acc.z += ye.z; acc.w += ye.w; }
+        if (x) { acc.x = yx.x + acc.x; acc.y = yx.y + acc.y; acc.z = yx.z + acc.z; acc.w = yx.w + acc.w; }
+        if (x) *reinterpret_cast<float4*>(x + (size_t)i * EH + k0) = acc;
+        if (out) *reinterpret_cast<float4*>(out + (size_t)i * EH + k0) = acc;
+        v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
+    }
+    if (xn) {
+        const float r = norm ? row_rms_scale(v, eps) : 1.f;
+        scaled_split_row<F16>(v, r, xn + (size_t)t * EH, xs ? xs + (size_t)t * 2 * EH : nullptr);
+    }
+}
+
+// Self-test of the flag wait's time-out: one thread waits for a flag nobody raises.
+__global__ void selftest_ep_wait_timeout_k(const unsigned* flag, int* err, int limit, int* result) {
+    if (threadIdx.x == 0) *result = ep_wait_flag(flag, 1u, err, EP_ERR_COMBINE_WAIT, limit) ? 1 : 0;
+}
+
+}  // namespace moexb

@@ -8,6 +8,7 @@
 #include "tiled.cuh"
 #include "prefill.cuh"
 #include "decode_stack.cuh"
+#include "ep.cuh"
 #include "gguf_ingest.h"
 #include "st_ingest.h"
 
@@ -903,8 +904,9 @@ static int prefill_launch_one(moexb_ctx* c, const PrefillArgs& a, void* stream) 
 
 // Experts of a large batch on the tensor-core grouped GEMM: items/nitems = the grouped work list (tiled blobs), xf = the
 // activations as fp32 [T][H]; parts = 1 when xf holds exact bf16 values, else 2.
-static int prefill_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, const float* xf, int T, int parts, float* ypair, void* stream) {
-    {
+static int prefill_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, const float* xf, int T, int parts, float* ypair, void* stream,
+                           bool pre_split = false) {
+    if (!pre_split) {   // pre_split: the context already holds the fp16 columns (expert parallelism: the token owners made them)
         PROF(c, MOEXB_PROF_OTHER, stream);
         const size_t n = (size_t)T * EH;
         split8_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, S(stream)>>>(xf, c->xs, EH, parts, n);
@@ -985,17 +987,19 @@ extern "C" int moexb_ctx_status(moexb_ctx* c, int* status) {
 
 // Makes one bounded device-side wait run out on purpose and reports what the kernels' error word then holds.
 // which = 0: the mbarrier wait of the streaming / grouped-GEMM pipelines (a barrier that expects bytes nobody sends);
-// which = 1: the grid barrier of the one-token stack kernel (one CTA, two arrivals expected). Both with `polls` polls
-// instead of the production limits. Nothing faults or hangs: the kernel returns, the context stays usable.
+// which = 1: the grid barrier of the one-token stack kernel (one CTA, two arrivals expected); which = 2: the wait of the
+// expert-parallel kernels for a flag that another GPU raises (nobody raises it). All with `polls` polls instead of the
+// production limits. Nothing faults or hangs: the kernel returns, the context stays usable.
 extern "C" int moexb_ctx_selftest_timeout(moexb_ctx* c, int which, int polls, int* status) {
     REQUIRE(c && status, "ctx_selftest_timeout: null pointer");
-    REQUIRE((which == 0 || which == 1) && polls > 0 && polls <= (1 << 20), "ctx_selftest_timeout: which=%d polls=%d", which, polls);
+    REQUIRE(which >= 0 && which <= 2 && polls > 0 && polls <= (1 << 20), "ctx_selftest_timeout: which=%d polls=%d", which, polls);
     CUDA_TRY(cudaSetDevice(c->device));
     CUDA_TRY(cudaMemset(c->nsub, 0, 2 * sizeof(int)));   // scratch of the self-test: [0] result of the wait
     unsigned* sync = reinterpret_cast<unsigned*>(c->counts);       // scratch: barrier counter and abort flag
     CUDA_TRY(cudaMemset(sync, 0, 2 * sizeof(unsigned)));
     if (which == 0) selftest_mbar_timeout_k<<<1, 32>>>(c->err, ST_ERR_FULL_WAIT, polls, c->nsub);
-    else selftest_grid_barrier_timeout_k<<<1, 32>>>(sync, c->err, polls, c->nsub);
+    else if (which == 1) selftest_grid_barrier_timeout_k<<<1, 32>>>(sync, c->err, polls, c->nsub);
+    else selftest_ep_wait_timeout_k<<<1, 32>>>(sync, c->err, polls, c->nsub);
     LAUNCHED("selftest_timeout");
     return moexb_ctx_status(c, status);
 }
@@ -1008,15 +1012,17 @@ extern "C" {
 // Router logits (into the context, [T][E + 1]) and the top-K selection in one launch; decode: also the K + 1 one-pair
 // sub-items of a single token.
 template <typename WT>
-static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode) {
+static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0) {
+    // tok0: the T rows at xf are tokens tok0.. of the batch - their logits, ids and weights go to those rows of the workspace
     const int E = L->n_routed;
     const WT* W = static_cast<const WT*>(L->router);
-    const TopkOut o{c->idx, c->w, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
+    float* logits = c->logits + (size_t)tok0 * (E + 1);
+    const TopkOut o{c->idx + (size_t)tok0 * K, c->w + (size_t)tok0 * K, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
                     decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr};
     auto run = [&]<int NJ>() -> int {
         if (T < 8) {
             constexpr int WARPS = 8;
-            CUDA_TRY(launch_dep(route_gemv_k<WT, WARPS, NJ>, dim3((E + 1 + WARPS - 1) / WARPS, T), WARPS * 32, 0, S(stream), W, xf, c->logits, EH, E, K, 1, c->route_done, o));
+            CUDA_TRY(launch_dep(route_gemv_k<WT, WARPS, NJ>, dim3((E + 1 + WARPS - 1) / WARPS, T), WARPS * 32, 0, S(stream), W, xf, logits, EH, E, K, 1, c->route_done, o));
         } else {
             // 16 outputs per block spread a small batch over more SMs; a prefill chunk has blocks to spare and re-reads
             // the router weights less with 32 outputs per block
@@ -1026,7 +1032,7 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
                 const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(route_gemm_k<WT, WARPS, TO, TR, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
                 if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
                 CUDA_TRY(launch_dep(route_gemm_k<WT, WARPS, TO, TR, NJ>, dim3((E + 1 + WARPS * TO - 1) / (WARPS * TO), (T + TR - 1) / TR), WARPS * 32, SMEM, S(stream),
-                                    W, xf, c->logits, EH, E, K, 1, T, c->route_done, o));
+                                    W, xf, logits, EH, E, K, 1, T, c->route_done, o));
                 return MOEXB_OK;
             };
             // a small batch: 16 outputs x 8 tokens per block, to reach every SM; a prefill chunk goes to the register-tiled
@@ -1037,7 +1043,7 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
                 const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(route_gemm2_k<WT, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
                 if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "router kernel shared memory: %s", cudaGetErrorString(attr_err));
                 CUDA_TRY(launch_dep(route_gemm2_k<WT, NJ>, dim3((E + 1 + RG2_TN - 1) / RG2_TN, (T + RG2_TM - 1) / RG2_TM), 256, SMEM, S(stream),
-                                    W, xf, c->logits, E, K, 1, T, c->route_done, o));
+                                    W, xf, logits, E, K, 1, T, c->route_done, o));
                 return MOEXB_OK;
             };
             const int rc = T >= 256 ? gemm2() : gemm.template operator()<2, 8>();
@@ -1050,9 +1056,9 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
 }
 
 extern "C" {
-static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode) {
+static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0) {
     PROF(c, MOEXB_PROF_ROUTER, stream);
-    return L->router_dtype == MOEXB_F32 ? route_launch<float>(c, L, xf, T, K, stream, decode) : route_launch<__half>(c, L, xf, T, K, stream, decode);
+    return L->router_dtype == MOEXB_F32 ? route_launch<float>(c, L, xf, T, K, stream, decode, tok0) : route_launch<__half>(c, L, xf, T, K, stream, decode, tok0);
 }
 
 // One layer. xin: the layer input as f32 [T][H]. flags as moexb_layer_forward. pre_normed: the context already holds
@@ -1112,10 +1118,11 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             // room in shared memory for the routed pairs (12 bytes each), so that the list is written out in full lines
             constexpr int PLAN_STAGE_MAX = 196608;
             static PerDeviceOnce plan_once;
-            const cudaError_t plan_attr = plan_once.run([] { return cudaFuncSetAttribute(group_plan1_k, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
+            const cudaError_t plan_attr = plan_once.run([] { return cudaFuncSetAttribute(group_plan1_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
             const int stage_pairs = plan_attr == cudaSuccess && (size_t)T * K * 12 <= PLAN_STAGE_MAX ? T * K : 0;
-            CUDA_TRY(launch_dep(group_plan1_k, 1, 1024, (size_t)stage_pairs * 12, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
-                                prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1, stage_pairs));
+            CUDA_TRY(launch_dep(group_plan1_k<false>, 1, 1024, (size_t)stage_pairs * 12, st, c->idx, c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems, c->subs, c->nsub, maxp,
+                                prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, shared ? c->logits + E : nullptr, ld, sh0, sh1, stage_pairs,
+                                (const unsigned*)nullptr, (const unsigned*)nullptr, 0u, 0, 0, (int*)nullptr));
             LAUNCHED("group_plan");
             // pairs of experts that are not held here are never written: the SIMT reduction path needs zeros there, the fused
             // reduction skips them by expert id
@@ -1201,6 +1208,7 @@ int moexb_ep_residual_norm(moexb_ctx* c, moexb_layer* next, const float* x, cons
 struct moexb_stack {
     moexb_ctx* ctx = nullptr;
     int T = 0, K = 0, x_dtype = 0, n_layers = 0, kernels = 0;
+    int out_rows = 0;            // rows of the result: T, or the own tokens of an expert-parallel rank
     void* x_in = nullptr;        // [T][H] of x_dtype
     float* buf[2] = {nullptr, nullptr};
     float* result = nullptr;     // = buf[(n_layers - 1) & 1]
@@ -1270,7 +1278,7 @@ int moexb_stack_create(moexb_ctx* c, moexb_layer* const* layers, int n_layers, i
     CUDA_TRY(cudaSetDevice(c->device));
     moexb_stack* s = new (std::nothrow) moexb_stack;
     if (!s) return fail(MOEXB_ERR_NOMEM, "out of host memory");
-    s->ctx = c; s->T = T; s->K = K; s->x_dtype = x_dtype; s->n_layers = n_layers;
+    s->ctx = c; s->T = T; s->K = K; s->x_dtype = x_dtype; s->n_layers = n_layers; s->out_rows = T;
     const size_t n = (size_t)T * EH;
     cudaError_t e = cudaMalloc(&s->x_in, n * (x_dtype == MOEXB_BF16 ? 2 : 4));
     if (e == cudaSuccess) e = cudaMalloc((void**)&s->buf[0], n * 4);
@@ -1328,7 +1336,7 @@ int moexb_stack_run(moexb_stack* s, const void* X, float* out, void* stream) {
         CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
         g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
     }
-    CUDA_TRY(cudaMemcpyAsync(out, s->result, n * 4, cudaMemcpyDeviceToDevice, S(stream)));
+    CUDA_TRY(cudaMemcpyAsync(out, s->result, (size_t)s->out_rows * EH * 4, cudaMemcpyDeviceToDevice, S(stream)));
     return MOEXB_OK;
 }
 
@@ -1341,8 +1349,288 @@ int moexb_stack_run_host(moexb_stack* s, const void* X_host, float* out_host, vo
         CUDA_TRY(cudaGraphLaunch(s->exec, S(stream)));
         g_launches.fetch_add(s->kernels, std::memory_order_relaxed);
     }
-    CUDA_TRY(cudaMemcpyAsync(out_host, s->result, n * 4, cudaMemcpyDeviceToHost, S(stream)));
+    CUDA_TRY(cudaMemcpyAsync(out_host, s->result, (size_t)s->out_rows * EH * 4, cudaMemcpyDeviceToHost, S(stream)));
     CUDA_TRY(cudaStreamSynchronize(S(stream)));
+    return MOEXB_OK;
+}
+
+// ---- expert parallelism: token all-to-all over peer memory (ep.cuh) -----------------------------------------------------------
+
+struct moexb_ep {
+    moexb_ctx* ctx = nullptr;
+    EpGeom g{};
+    EpPeers peers{};
+    EpLayout lay{};
+    int n_routed = 0;
+    float* x = nullptr;         // [n_own_max][H] residual rows of the own tokens
+    unsigned* step = nullptr;   // device: steps begun so far
+    int* tickets = nullptr;     // device: block counters of the two push kernels (return to zero)
+    // what the context pointed at before its activations, ids and weights moved into the exchange buffer
+    uint16_t* saved_xs = nullptr; int* saved_idx = nullptr; float* saved_w = nullptr;
+    // host-side state of the layer in progress (set by dispatch, used by experts)
+    bool prefill = false; int parts = 2;
+};
+
+size_t moexb_ep_buffer_bytes(int max_tokens, int top_k, int world) {
+    if (max_tokens <= 0 || top_k <= 0 || world <= 0 || world > EP_MAX_RANKS) return 0;
+    return ep_layout(max_tokens, top_k, world).bytes;
+}
+
+int moexb_ep_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle) {
+    REQUIRE(ptr && bytes > 0, "ep_buffer_alloc: bad argument");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return fail(MOEXB_ERR_NOMEM, "ep_buffer_alloc: cudaMalloc of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess && handle) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "an IPC handle is 64 bytes");
+        cudaIpcMemHandle_t h;
+        e = cudaIpcGetMemHandle(&h, p);
+        if (e == cudaSuccess) memcpy(handle, &h, 64);
+    }
+    if (e != cudaSuccess) { cudaFree(p); return fail(MOEXB_ERR_CUDA, "ep_buffer_alloc: %s", cudaGetErrorString(e)); }
+    *ptr = p;
+    return MOEXB_OK;
+}
+
+int moexb_ep_buffer_open(const unsigned char* handle, void** ptr) {
+    REQUIRE(handle && ptr, "ep_buffer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return MOEXB_OK;
+}
+
+int moexb_ep_buffer_close(void* ptr) {
+    if (ptr) CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return MOEXB_OK;
+}
+
+int moexb_ep_buffer_free(void* ptr) {
+    if (ptr) CUDA_TRY(cudaFree(ptr));
+    return MOEXB_OK;
+}
+
+int moexb_ep_create(moexb_ctx* c, int rank, int world, int T, int K, int n_routed, void* const* bufs, moexb_ep** out) {
+    REQUIRE(c && bufs && out, "ep_create: null pointer");
+    REQUIRE(world >= 1 && world <= EP_MAX_RANKS && rank >= 0 && rank < world, "ep_create: rank %d of %d (at most %d ranks)", rank, world, EP_MAX_RANKS);
+    REQUIRE(T >= world && T <= c->max_tokens, "ep_create: T=%d must be at least the number of ranks (%d) and at most the context's max_tokens=%d", T, world, c->max_tokens);
+    REQUIRE(K > 0 && K <= c->top_k, "ep_create: K=%d exceeds the context's top_k=%d", K, c->top_k);
+    REQUIRE(n_routed >= world && n_routed <= c->max_experts, "ep_create: n_routed=%d", n_routed);
+    for (int r = 0; r < world; r++) REQUIRE(bufs[r], "ep_create: the exchange buffer of rank %d is null", r);
+    CUDA_TRY(cudaSetDevice(c->device));
+    moexb_ep* e = new (std::nothrow) moexb_ep;
+    if (!e) return fail(MOEXB_ERR_NOMEM, "out of host memory");
+    e->ctx = c; e->n_routed = n_routed;
+    e->g.rank = rank; e->g.world = world; e->g.T = T; e->g.K = K; e->g.n_own_max = (T + world - 1) / world;
+    for (int r = 0; r <= EP_MAX_RANKS; r++) {
+        const int rr = min(r, world);
+        e->g.tok0[r] = rr * (T / world) + min(rr, T % world);
+        e->g.exp0[r] = rr * (n_routed / world) + min(rr, n_routed % world);
+    }
+    for (int r = 0; r < EP_MAX_RANKS; r++) e->peers.base[r] = r < world ? static_cast<uint8_t*>(bufs[r]) : nullptr;
+    e->lay = ep_layout(T, K, world);
+    cudaError_t err = cudaMalloc((void**)&e->x, (size_t)e->g.n_own_max * EH * sizeof(float));
+    if (err == cudaSuccess) err = cudaMalloc((void**)&e->step, sizeof(unsigned));
+    if (err == cudaSuccess) err = cudaMalloc((void**)&e->tickets, 2 * sizeof(int));
+    if (err == cudaSuccess) err = cudaMemset(e->step, 0, sizeof(unsigned));
+    if (err == cudaSuccess) err = cudaMemset(e->tickets, 0, 2 * sizeof(int));
+    if (err != cudaSuccess) { cudaFree(e->x); cudaFree(e->step); cudaFree(e->tickets); delete e; return fail(MOEXB_ERR_NOMEM, "ep_create: %s", cudaGetErrorString(err)); }
+    // the context's activation columns, ids and weights now live in this rank's exchange buffer, where the peers write them
+    uint8_t* local = e->peers.base[rank];
+    e->saved_xs = c->xs; e->saved_idx = c->idx; e->saved_w = c->w;
+    c->xs = reinterpret_cast<uint16_t*>(local + e->lay.xs);
+    c->idx = reinterpret_cast<int*>(local + e->lay.idx);
+    c->w = reinterpret_cast<float*>(local + e->lay.w);
+    *out = e;
+    return MOEXB_OK;
+}
+
+int moexb_ep_destroy(moexb_ep* e) {
+    if (!e) return MOEXB_OK;
+    e->ctx->xs = e->saved_xs; e->ctx->idx = e->saved_idx; e->ctx->w = e->saved_w;
+    cudaFree(e->x); cudaFree(e->step); cudaFree(e->tickets);
+    delete e;
+    return MOEXB_OK;
+}
+
+int moexb_ep_own_tokens(const moexb_ep* e, int* first, int* count) {
+    REQUIRE(e, "ep_own_tokens: null pointer");
+    if (first) *first = e->g.tok0[e->g.rank];
+    if (count) *count = e->g.tok0[e->g.rank + 1] - e->g.tok0[e->g.rank];
+    return MOEXB_OK;
+}
+
+int moexb_ep_begin_step(moexb_ep* e, void* stream) {
+    REQUIRE(e, "ep_begin_step: null pointer");
+    ep_step_k<<<1, 1, 0, S(stream)>>>(e->step);
+    LAUNCHED("ep_step");
+    return MOEXB_OK;
+}
+
+}  // extern "C"
+
+static int ep_check_layer(const moexb_ep* e, const moexb_layer* L, int l, const char* who) {
+    REQUIRE(e && L, "%s: null pointer", who);
+    REQUIRE(L->ctx == e->ctx, "%s: layer belongs to another context", who);
+    REQUIRE(l >= 0 && l + 1 < (int)EP_PHASES, "%s: layer index %d", who, l);
+    REQUIRE(L->n_routed == e->n_routed && L->first_local == e->g.exp0[e->g.rank] && L->n_local == e->g.exp0[e->g.rank + 1] - e->g.exp0[e->g.rank],
+            "%s: the layer holds experts [%d, %d) of %d, this rank's share is [%d, %d) of %d", who, L->first_local, L->first_local + L->n_local,
+            L->n_routed, e->g.exp0[e->g.rank], e->g.exp0[e->g.rank + 1], e->n_routed);
+    REQUIRE(L->loaded[L->n_routed], "%s: the shared expert of this layer was never loaded", who);
+    return MOEXB_OK;
+}
+
+// The owner's side of the combine of layer `l - 1` (l >= 1), leaving the next layer's input (or, with `out`, the result).
+static int ep_combine(moexb_ep* e, bool f16, bool residual, unsigned phase, float* out, bool next, bool split, void* stream) {
+    moexb_ctx* c = e->ctx;
+    const int n_own = e->g.tok0[e->g.rank + 1] - e->g.tok0[e->g.rank];
+    const float* extra = c->ypair + (size_t)e->g.T * e->g.K * EH;   // the shared expert's rows, by absolute token
+    float* x = residual ? e->x : nullptr;
+    float* xn = next ? c->xn : nullptr;
+    uint16_t* xs = next && split ? c->xs : nullptr;
+    PROF(c, MOEXB_PROF_COMBINE, stream);
+    if (f16) CUDA_TRY(launch_dep(ep_combine_norm_k<true>, n_own, 256, 0, S(stream), e->g, (const uint8_t*)e->peers.base[e->g.rank], e->lay, extra, x, out, xn, xs, residual ? 1 : 0, 1e-6f, (const unsigned*)e->step, phase, c->err));
+    else CUDA_TRY(launch_dep(ep_combine_norm_k<false>, n_own, 256, 0, S(stream), e->g, (const uint8_t*)e->peers.base[e->g.rank], e->lay, extra, x, out, xn, xs, residual ? 1 : 0, 1e-6f, (const unsigned*)e->step, phase, c->err));
+    LAUNCHED("ep_combine_norm");
+    return MOEXB_OK;
+}
+
+extern "C" {
+
+int moexb_ep_dispatch(moexb_ep* e, moexb_layer* L, int l, const void* X, int x_dtype, int residual, void* stream) {
+    int rc = ep_check_layer(e, L, l, "ep_dispatch");
+    if (rc != MOEXB_OK) return rc;
+    REQUIRE(l > 0 || X, "ep_dispatch: layer 0 needs the input");
+    REQUIRE(x_dtype == MOEXB_F32 || x_dtype == MOEXB_BF16, "ep_dispatch: x_dtype=%d", x_dtype);
+    moexb_ctx* c = e->ctx;
+    cudaStream_t st = S(stream);
+    const int T = e->g.T, K = e->g.K, t0 = e->g.tok0[e->g.rank], n_own = e->g.tok0[e->g.rank + 1] - t0;
+    const bool tiled = L->layout == MOEXB_LAYOUT_TILED;
+    REQUIRE(tiled || c->path == 0, "ep_dispatch: expert parallelism runs on the streaming kernels");
+    const bool prefill = tiled && L->fmt == FMT_SYM_F16 && T >= c->prefill_min_tokens;
+    const bool f16 = tiled && L->fmt != FMT_ZP && !prefill;
+    // activation columns per token: the grouped GEMM takes one when the layer input is exactly bf16, else hi + lo
+    const int parts = prefill && x_dtype == MOEXB_BF16 && !residual && l == 0 ? 1 : 2;
+    e->prefill = prefill; e->parts = parts;
+    float* xn_own = c->xn + (size_t)t0 * EH;
+    if (l == 0) {
+        // the own rows of the input as fp32: into the residual rows (blocks) or straight into the layer input (plain layers)
+        float* dst = residual ? e->x : xn_own;
+        const size_t n = (size_t)n_own * EH;
+        PROF(c, MOEXB_PROF_OTHER, stream);
+        if (x_dtype == MOEXB_BF16) {
+            bf16_to_f32_k<<<(unsigned)((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X) + (size_t)t0 * EH, dst, n);
+            LAUNCHED("bf16_to_f32");
+        } else CUDA_TRY(cudaMemcpyAsync(dst, static_cast<const float*>(X) + (size_t)t0 * EH, n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        if (residual && !prefill) {
+            if (f16) rmsnorm_split_k<true><<<n_own, 256, 0, st>>>(e->x, xn_own, c->xs + (size_t)t0 * 2 * EH, 1e-6f);
+            else rmsnorm_split_k<false><<<n_own, 256, 0, st>>>(e->x, xn_own, c->xs + (size_t)t0 * 2 * EH, 1e-6f);
+            LAUNCHED("rmsnorm_split");
+        } else if (residual) {
+            rmsnorm_rows_k<<<n_own, 256, 0, st>>>(e->x, xn_own, EH, 1e-6f);
+            LAUNCHED("rmsnorm_rows");
+        } else if (!prefill) {
+            if (f16) split_rows_k<true><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xn_own, c->xs + (size_t)t0 * 2 * EH, EH, n);
+            else split_rows_k<false><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xn_own, c->xs + (size_t)t0 * 2 * EH, EH, n);
+            LAUNCHED("split_rows");
+        }
+    } else {
+        rc = ep_combine(e, f16, residual != 0, (unsigned)l, nullptr, true, !prefill, stream);
+        if (rc != MOEXB_OK) return rc;
+    }
+    if (prefill) {
+        PROF(c, MOEXB_PROF_OTHER, stream);
+        const size_t n = (size_t)n_own * EH;
+        split8_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xn_own, c->xs + (size_t)t0 * parts * EH, EH, parts, n);
+        LAUNCHED("split8_rows");
+    }
+    rc = layer_route(c, L, xn_own, n_own, K, stream, false, t0);
+    if (rc != MOEXB_OK) return rc;
+    PROF(c, MOEXB_PROF_OTHER, stream);
+    CUDA_TRY(launch_dep(ep_dispatch_push_k, dim3(n_own, e->g.world), 256, 0, st, e->g, e->peers, e->lay, parts * EH * 2, (const unsigned*)e->step, (unsigned)(l + 1), e->tickets));
+    LAUNCHED("ep_dispatch_push");
+    return MOEXB_OK;
+}
+
+int moexb_ep_experts(moexb_ep* e, moexb_layer* L, int l, void* stream) {
+    int rc = ep_check_layer(e, L, l, "ep_experts");
+    if (rc != MOEXB_OK) return rc;
+    moexb_ctx* c = e->ctx;
+    cudaStream_t st = S(stream);
+    const int T = e->g.T, K = e->g.K, E = L->n_routed, t0 = e->g.tok0[e->g.rank], t1 = e->g.tok0[e->g.rank + 1];
+    const bool tiled = L->layout == MOEXB_LAYOUT_TILED, prefill = e->prefill;
+    {
+        PROF(c, MOEXB_PROF_GROUP, stream);
+        const int maxp = prefill ? PF_NMAX / e->parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
+        constexpr int PLAN_STAGE_MAX = 196608;
+        static PerDeviceOnce plan_once;
+        const cudaError_t plan_attr = plan_once.run([] { return cudaFuncSetAttribute(group_plan1_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
+        const int stage_pairs = plan_attr == cudaSuccess && (size_t)T * K * 12 <= PLAN_STAGE_MAX ? T * K : 0;
+        const unsigned* flags = reinterpret_cast<const unsigned*>(e->peers.base[e->g.rank] + e->lay.flag_a);
+        CUDA_TRY(launch_dep(group_plan1_k<true>, 1, 1024, (size_t)stage_pairs * 12, st, (const int*)c->idx, (const float*)c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems,
+                            c->subs, c->nsub, maxp, prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, (const float*)(c->logits + E), E + 1, t0, t1, stage_pairs,
+                            flags, (const unsigned*)e->step, (unsigned)(l + 1), e->g.world, e->g.rank, c->err));
+        LAUNCHED("group_plan");
+    }
+    rc = prefill ? prefill_experts(c, L->fmt, c->pairs, nullptr, T, e->parts, c->ypair, stream, true)
+       : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
+               : stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
+    if (rc != MOEXB_OK) return rc;
+    PROF(c, MOEXB_PROF_COMBINE, stream);
+    CUDA_TRY(launch_dep(ep_partial_push_k, T, 256, 0, st, e->g, e->peers, e->lay, (const float*)c->ypair, (const unsigned*)e->step, (unsigned)(l + 1), e->tickets + 1));
+    LAUNCHED("ep_partial_push");
+    return MOEXB_OK;
+}
+
+int moexb_ep_finish(moexb_ep* e, int n_layers, int residual, float* out_own, void* stream) {
+    REQUIRE(e && out_own, "ep_finish: null pointer");
+    REQUIRE(n_layers >= 1 && n_layers < (int)EP_PHASES, "ep_finish: %d layers", n_layers);
+    return ep_combine(e, true, residual != 0, (unsigned)n_layers, out_own, false, false, stream);
+}
+
+// One whole step on `stream`: begin, per layer dispatch + experts, finish. X [T][H] of x_dtype (every rank passes the whole
+// batch and uses its own rows), out_own [own tokens][H].
+int moexb_ep_step(moexb_ep* e, moexb_layer* const* layers, int n_layers, const void* X, int x_dtype, int residual, float* out_own, void* stream) {
+    REQUIRE(e && layers && X && out_own, "ep_step: null pointer");
+    int rc = moexb_ep_begin_step(e, stream);
+    for (int l = 0; l < n_layers && rc == MOEXB_OK; l++) {
+        rc = moexb_ep_dispatch(e, layers[l], l, X, x_dtype, residual, stream);
+        if (rc == MOEXB_OK) rc = moexb_ep_experts(e, layers[l], l, stream);
+    }
+    if (rc == MOEXB_OK) rc = moexb_ep_finish(e, n_layers, residual, out_own, stream);
+    return rc;
+}
+
+int moexb_ep_stack_create(moexb_ep* e, moexb_layer* const* layers, int n_layers, int x_dtype, int residual, moexb_stack** out) {
+    REQUIRE(e && layers && out, "ep_stack_create: null pointer");
+    REQUIRE(n_layers >= 1 && n_layers < (int)EP_PHASES, "ep_stack_create: %d layers", n_layers);
+    REQUIRE(residual || n_layers == 1, "ep_stack_create: plain (non-residual) layers are chained one at a time");
+    moexb_ctx* c = e->ctx;
+    REQUIRE(!c->profiling, "ep_stack_create: switch profiling off before capturing a graph");
+    CUDA_TRY(cudaSetDevice(c->device));
+    moexb_stack* s = new (std::nothrow) moexb_stack;
+    if (!s) return fail(MOEXB_ERR_NOMEM, "out of host memory");
+    const int T = e->g.T;
+    s->ctx = c; s->T = T; s->K = e->g.K; s->x_dtype = x_dtype; s->n_layers = n_layers;
+    s->out_rows = e->g.tok0[e->g.rank + 1] - e->g.tok0[e->g.rank];
+    const size_t n = (size_t)T * EH;
+    cudaError_t err = cudaMalloc(&s->x_in, n * (x_dtype == MOEXB_BF16 ? 2 : 4));
+    if (err == cudaSuccess) err = cudaMalloc((void**)&s->buf[0], (size_t)e->g.n_own_max * EH * 4);
+    if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&s->cap, cudaStreamNonBlocking);
+    if (err != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_NOMEM, "ep_stack_create: %s", cudaGetErrorString(err)); }
+    const long long before = g_launches.load();
+    err = cudaStreamBeginCapture(s->cap, cudaStreamCaptureModeThreadLocal);
+    if (err != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "ep_stack_create: begin capture: %s", cudaGetErrorString(err)); }
+    const int rc = moexb_ep_step(e, layers, n_layers, s->x_in, x_dtype, residual, s->buf[0], s->cap);
+    err = cudaStreamEndCapture(s->cap, &s->graph);
+    s->kernels = (int)(g_launches.load() - before);
+    g_launches.store(before);
+    if (rc != MOEXB_OK) { moexb_stack_destroy(s); return rc; }
+    if (err == cudaSuccess) err = cudaGraphInstantiate(&s->exec, s->graph, 0);
+    if (err != cudaSuccess) { moexb_stack_destroy(s); return fail(MOEXB_ERR_CUDA, "ep_stack_create: graph: %s", cudaGetErrorString(err)); }
+    s->result = s->buf[0];
+    *out = s;
     return MOEXB_OK;
 }
 

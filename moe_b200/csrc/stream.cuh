@@ -365,8 +365,8 @@ __global__ void split_rows_k(const float* __restrict__ x, uint16_t* __restrict__
 // in the pinned order of rmsnorm_rows_k, then the normalised row as fp32 (for the router) and as bf16 hi + lo in the
 // permuted order (for the streaming kernels).
 // lo_off: distance (elements) from the hi row to the lo row of the split.
-template <bool F16>
-__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, uint16_t* __restrict__ xs, float eps, int lo_off = EH) {
+// 1 / sqrt(mean(v^2) + eps) of the row, the sum of squares in the pinned order (all 256 threads of the block call it).
+__device__ __forceinline__ float row_rms_scale(const float (&v)[8], float eps) {
     __shared__ float part[8];
     float ss = 0.f;
 #pragma unroll
@@ -377,12 +377,17 @@ __device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __res
     float tot = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; i++) tot += part[i];
-    const float r = 1.f / sqrtf(tot / (float)EH + eps);
+    return 1.f / sqrtf(tot / (float)EH + eps);
+}
+// The row times r as fp32 into xn and, when xs is given, as 16-bit hi + lo in the permuted order into xs (hi) and xs + lo_off (lo).
+template <bool F16>
+__device__ __forceinline__ void scaled_split_row(const float (&v)[8], float r, float* __restrict__ xn, uint16_t* __restrict__ xs, int lo_off = EH) {
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int k0 = 1024 * h + 4 * threadIdx.x;
         float4 o = make_float4(v[4 * h] * r, v[4 * h + 1] * r, v[4 * h + 2] * r, v[4 * h + 3] * r);
         *reinterpret_cast<float4*>(xn + k0) = o;
+        if (!xs) continue;
         const float f[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -392,6 +397,10 @@ __device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __res
             xs[pos] = hi; xs[lo_off + pos] = lo;
         }
     }
+}
+template <bool F16>
+__device__ __forceinline__ void norm_split_row(const float (&v)[8], float* __restrict__ xn, uint16_t* __restrict__ xs, float eps, int lo_off = EH) {
+    scaled_split_row<F16>(v, row_rms_scale(v, eps), xn, xs, lo_off);
 }
 
 // xn[t] = rmsnorm(x[t]) and its bf16 split, one block of 256 per row (H = 2048).
@@ -474,13 +483,17 @@ __device__ __forceinline__ int block_scan_1024(int v, int& total) {
 // order and may change from run to run - every pair's result is independent of its place). List 1 keeps sub-items of more
 // than maxp / 2 pairs first (nsub[1] = their number); list 2 is in expert order. The shared expert (slot_table[E], when
 // gate_logits is given) gets the tokens [sh0, sh1) with weight sigmoid(gate logit), as the last item.
+// EP: the ids and weights were stored by other GPUs (ep.cuh): thread s < ep_world first waits (bounded) until rank s's
+// dispatch flag ep_flags[s] has reached *ep_step * EP_PHASES + ep_phase, and the lists are then read past L1.
+template <bool EP>
 __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
                                                       const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
                                                       moexb_pair* __restrict__ pairs, int* __restrict__ nitems,
                                                       moexb_pair_item* __restrict__ subs, int* __restrict__ nsub, int maxp,
                                                       moexb_pair_item* __restrict__ subs2, int* __restrict__ nsub2, int maxp2,
                                                       const float* __restrict__ gate_logits, int gl_stride, int sh0, int sh1,
-                                                      int stage_pairs) {
+                                                      int stage_pairs, const unsigned* ep_flags = nullptr, const unsigned* ep_step = nullptr,
+                                                      unsigned ep_phase = 0, int ep_world = 0, int ep_rank = 0, int* err = nullptr) {
     __shared__ int cnt[1024], cur[1024], start[1024];
     extern __shared__ int stage[];   // stage_pairs pairs of 3 words, when the launch gave the room
     const int n = T * K, e = threadIdx.x;
@@ -493,6 +506,13 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     __syncthreads();
     pdl_wait();
     pdl_trigger();
+    if constexpr (EP) {
+        if (e < ep_world && e != ep_rank) ep_wait_flag(ep_flags + e, *ep_step * EP_PHASES + ep_phase, err, EP_ERR_DISPATCH_WAIT);
+        __syncthreads();
+        __threadfence_system();
+    }
+    auto ld_idx = [&](int p) { return EP ? __ldcg(idx + p) : __ldg(idx + p); };
+    auto ld_w = [&](int p) { return EP ? __ldcg(w + p) : __ldg(w + p); };
     // Every global load of the first 8192 pairs and of the first 1024 gate logits is issued here, in one round trip; the
     // values stay in registers for the histogram and for the scatter.
     constexpr int B = 8;   // pairs per thread in flight
@@ -500,7 +520,7 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
 #pragma unroll
     for (int u = 0; u < B; u++) {
         const int p = e + 1024 * u;
-        ex0[u] = p < n ? __ldg(idx + p) : -1; wp0[u] = p < n ? __ldg(w + p) : 0.f;
+        ex0[u] = p < n ? ld_idx(p) : -1; wp0[u] = p < n ? ld_w(p) : 0.f;
     }
     const float gl0 = e < Ts ? gate_logits[(size_t)(sh0 + e) * gl_stride] : 0.f;
 #pragma unroll
@@ -508,7 +528,7 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     for (int p0 = e + 1024 * B; p0 < n; p0 += 1024 * B) {
         int ex[B];
 #pragma unroll
-        for (int u = 0; u < B; u++) ex[u] = p0 + 1024 * u < n ? __ldg(idx + p0 + 1024 * u) : -1;
+        for (int u = 0; u < B; u++) ex[u] = p0 + 1024 * u < n ? ld_idx(p0 + 1024 * u) : -1;
 #pragma unroll
         for (int u = 0; u < B; u++) if (ex[u] >= 0) atomicAdd(&cnt[ex[u]], 1);
     }
@@ -542,7 +562,7 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     for (int p0 = e + 1024 * B; p0 < n; p0 += 1024 * B) {
         int ex[B]; float wp[B];
 #pragma unroll
-        for (int u = 0; u < B; u++) { const int p = p0 + 1024 * u; ex[u] = p < n ? __ldg(idx + p) : -1; wp[u] = p < n ? __ldg(w + p) : 0.f; }
+        for (int u = 0; u < B; u++) { const int p = p0 + 1024 * u; ex[u] = p < n ? ld_idx(p) : -1; wp[u] = p < n ? ld_w(p) : 0.f; }
 #pragma unroll
         for (int u = 0; u < B; u++) place(p0 + 1024 * u, ex[u], wp[u]);
     }
