@@ -240,8 +240,9 @@ def config_of(workload, n_gpus):
             "parallelism": "single GPU" if n_gpus == 1 else PARALLELISM.format(n=n_gpus, e=E // n_gpus)}
 
 
-PARALLELISM = ("expert parallel over {n} GPUs: {e} routed experts per rank, router and shared expert replicated, "
-               "one NCCL all-reduce of the partial outputs per layer")
+PARALLELISM = ("expert parallel over {n} GPUs: {e} routed experts and 1/{n} of the tokens per rank, router and shared expert "
+               "replicated; per layer a token all-to-all each way (dispatch of activation rows, combine of partial rows) done by "
+               "the library's kernels over peer-mapped memory, no collective call")
 
 
 # ---- GPU arm -----------------------------------------------------------------------------------------------------------------
@@ -303,29 +304,30 @@ def measure(env, workload):
     fmt = m.FMT_ZP if fmtname == "zp" else m.FMT_SYM_F16
     ctx, layers = env.layers("big" if T > 64 else "small", fmt, NL, max(T, 64))
     x_torch_dtype = torch.bfloat16 if xdt == "bf16" else torch.float32
+    eps = None
     if world == 1:
         stack = m.Stack(ctx, layers, T, K, m.BF16 if xdt == "bf16" else m.F32, residual=NL > 1)
-        kernel_count = stack.kernel_count
+        kernel_count, out_rows = stack.kernel_count, T
     else:
-        # expert parallel: every rank sees the same tokens; the step is captured with its all-reduces in one graph
-        eps = env.ep.EPStack(ctx, layers, T, K, x_torch_dtype)
-        kernel_count = 0
+        # expert parallel: every rank gets the whole batch, owns 1/world of the tokens and returns their rows; the step of a
+        # rank (kernels, pushes into the peers' buffers, bounded waits on their flags) is one graph
+        eps = env.ep.EPStack(ctx, layers, T, K, x_torch_dtype, residual=NL > 1)
+        kernel_count, out_rows = eps.kernel_count, eps.n_own
 
         class _S:  # the Stack interface on top of the expert-parallel step
             def run(self, X, out):
-                out.copy_(eps.run(X))
+                eps.stack.run(X, out)
 
             def run_host(self, Xh_, out_h_):
-                out_h_.copy_(eps.run(Xh_), non_blocking=True)
-                torch.cuda.current_stream().synchronize()
+                eps.stack.run_host(Xh_, out_h_)
 
             def close(self):
-                pass
+                eps.close()
         stack = _S()
     Xh = [torch.from_numpy(tokens(T, s % 8)).to(x_torch_dtype).pin_memory() for s in range(8)]
     Xd = [x.to(dev) for x in Xh]
-    out = torch.empty(T, EH, device=dev)
-    out_h = torch.empty(T, EH).pin_memory()
+    out = torch.empty(out_rows, EH, device=dev)
+    out_h = torch.empty(out_rows, EH).pin_memory()
 
     # ---- device-resident throughput: inputs already in HBM ----
     for s in range(args.warmup):
@@ -365,9 +367,13 @@ def measure(env, workload):
             if world == 1:
                 x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2 if NL > 1 else 0)
             else:
-                part = L.forward_ep(x, T, K, bufs[l & 1], sh0, sh1, idx=idx[l])
-                env.dist.all_reduce(part)
-                x = x.float() + part
+                if l == 0:
+                    eps.ep.begin_step()
+                eps.ep.dispatch(L, l, x if l == 0 else None, NL > 1)
+                eps.ep.experts(L, l)
+                eps.ep.read_routing(idx[l])
+                if l == NL - 1:
+                    eps.ep.finish(NL, out, NL > 1)
         if r == 0:
             ctx.profile_read()  # discard the first pass
     prof_ms, prof_n = ctx.profile_read()
@@ -395,7 +401,7 @@ def measure(env, workload):
     res = {
         "config": config_of(workload, world), "value": T / (ms_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step,
         "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Xh[0].numel() * Xh[0].element_size(),
-                "d2h_bytes_per_step": out_h.numel() * 4, "ms_per_step": e2e_ms},
+                "d2h_bytes_per_step": T * EH * 4, "ms_per_step": e2e_ms},
         "gpu_launches": int(launches), "kernels_per_step": kernel_count,
         "roofline": {"bound": "hbm", "kernel": "gate_up (expert gate/up projection + SwiGLU)", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": ratio * bytes_gu if ratio and T > 1 else None,

@@ -330,6 +330,9 @@ int moexb_ep_buffer_free(void* ptr);  /* a pointer from moexb_ep_buffer_alloc */
 int moexb_ep_create(moexb_ctx* ctx, int rank, int world, int T, int K, int n_routed, void* const* bufs, moexb_ep** out);
 int moexb_ep_destroy(moexb_ep* ep);
 int moexb_ep_own_tokens(const moexb_ep* ep, int* first, int* count);
+/* Optional outputs (either may be null): the selected experts and routing weights [T][K] of ALL tokens as this rank holds
+ * them after moexb_ep_experts of a layer (its own tokens' from its router, the others' as the peers sent them). */
+int moexb_ep_read_routing(moexb_ep* ep, int* idx_out, float* w_out, void* stream);
 /* A step = begin_step, then for each layer l = 0.. dispatch(l) and experts(l), then finish. Every rank makes the same calls
  * in the same order; all are enqueued on `stream` without synchronising and can be captured in a CUDA graph.
  *   begin_step  advances the step number the flags carry.

@@ -94,6 +94,7 @@ SIGNATURES = {
     "moexb_ep_create": (_i, [_vp, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp)]),
     "moexb_ep_destroy": (_i, [_vp]),
     "moexb_ep_own_tokens": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "moexb_ep_read_routing": (_i, [_vp, _vp, _vp, _vp]),
     "moexb_ep_begin_step": (_i, [_vp, _vp]),
     "moexb_ep_dispatch": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp]),
     "moexb_ep_experts": (_i, [_vp, _vp, _i, _vp]),

@@ -377,6 +377,10 @@ class EP:
     def begin_step(self):
         check(lib().moexb_ep_begin_step(self.h, _stream()))
 
+    def read_routing(self, idx=None, w=None):
+        """moexb_ep_read_routing: ids / weights [T][K] of all tokens as this rank holds them after experts() of a layer."""
+        check(lib().moexb_ep_read_routing(self.h, _ptr(idx), _ptr(w), _stream()))
+
     def dispatch(self, layer, l, X=None, residual=True):
         x_dtype = BF16 if (X is not None and X.dtype == torch.bfloat16) else F32
         check(lib().moexb_ep_dispatch(self.h, layer.h, l, _ptr(X), x_dtype, int(residual), _stream()))

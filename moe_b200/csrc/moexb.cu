@@ -1461,6 +1461,14 @@ int moexb_ep_own_tokens(const moexb_ep* e, int* first, int* count) {
     return MOEXB_OK;
 }
 
+int moexb_ep_read_routing(moexb_ep* e, int* idx_out, float* w_out, void* stream) {
+    REQUIRE(e, "ep_read_routing: null pointer");
+    const size_t n = (size_t)e->g.T * e->g.K;
+    if (idx_out) CUDA_TRY(cudaMemcpyAsync(idx_out, e->ctx->idx, n * sizeof(int), cudaMemcpyDeviceToDevice, S(stream)));
+    if (w_out) CUDA_TRY(cudaMemcpyAsync(w_out, e->ctx->w, n * sizeof(float), cudaMemcpyDeviceToDevice, S(stream)));
+    return MOEXB_OK;
+}
+
 int moexb_ep_begin_step(moexb_ep* e, void* stream) {
     REQUIRE(e, "ep_begin_step: null pointer");
     ep_step_k<<<1, 1, 0, S(stream)>>>(e->step);

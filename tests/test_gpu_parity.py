@@ -541,17 +541,19 @@ def test_one_token_stack_as_one_cooperative_launch(E, fmt, router, K):
 
 
 def test_bounded_waits_run_out_and_report(ctx, layer_sym):
-    """Every device-side wait is bounded. Two of them are made to run out here, without faulting or hanging anything: a
-    pipeline barrier whose bytes never arrive (the wait of the streaming and grouped-GEMM kernels) and a grid barrier that
-    expects an arrival that never comes (the one-token stack kernel). Each leaves its code in the error word, the status
+    """Every device-side wait is bounded. Three of them are made to run out here, without faulting or hanging anything: a
+    pipeline barrier whose bytes never arrive (the wait of the streaming and grouped-GEMM kernels), a grid barrier that
+    expects an arrival that never comes (the one-token stack kernel) and a flag that no peer raises (expert parallelism). Each leaves its code in the error word, the status
     call returns it and clears it, and the context computes correctly afterwards."""
     assert ctx.status() == 0
     assert ctx.selftest_timeout(0, 4096) == 1      # ST_ERR_FULL_WAIT
     assert ctx.status() == 0                       # cleared by the read
     assert ctx.selftest_timeout(1, 4096) == 5      # DS_ERR_BARRIER
     assert ctx.status() == 0
+    assert ctx.selftest_timeout(2, 4096) == 8      # EP_ERR_COMBINE_WAIT: a flag that a peer GPU would raise
+    assert ctx.status() == 0
     with pytest.raises(m.MoexbError):
-        ctx.selftest_timeout(2, 4096)
+        ctx.selftest_timeout(3, 4096)
     L, W, host = layer_sym
     X = np.random.default_rng(77).standard_normal((4, 2048)).astype(np.float32)
     out = L.forward(dev(X), 4, 8).cpu().numpy()
