@@ -33,7 +33,18 @@ __host__ __device__ constexpr size_t expert_bytes(int fmt) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// ---- flags that another GPU raises (expert parallelism, ep.cuh) ----
+// ---- expert parallelism (ep.cuh): geometry, exchange-buffer layout, flags that another GPU raises ----
+constexpr int EP_MAX_RANKS = 8;
+struct EpGeom {
+    int rank, world, T, K, n_own_max;
+    int tok0[EP_MAX_RANKS + 1];   // rank r owns tokens [tok0[r], tok0[r+1])
+    int exp0[EP_MAX_RANKS + 1];   // and holds routed experts [exp0[r], exp0[r+1])
+};
+// byte offsets inside an exchange buffer: activation rows [T][2][H] 16-bit, ids [T][K], weights [T][K], partial rows
+// [world][n_own_max][H] f32, dispatch flags [T] (one per token), combine flags [world][n_own_max] (one per source rank and own token)
+struct EpLayout { size_t xs, idx, w, part, flag_a, flag_b, bytes; };
+struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };   // exchange buffer of every rank, as mapped in this process
+struct EpDevice { EpGeom g; EpPeers p; EpLayout lay; };
 constexpr unsigned EP_PHASES = 256;           // a flag holds step * EP_PHASES + layer + 1: layers of a step must stay below this
 constexpr int EP_POLL_LIMIT = 1 << 21;        // polls (a local L2 round trip and a short sleep each: a second or two in all) before a wait gives up
 constexpr int EP_ERR_DISPATCH_WAIT = 7, EP_ERR_COMBINE_WAIT = 8;
@@ -44,6 +55,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded wait for *flag >= target; false (and the error word set) when it ran out of polls.
 __device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned target, int* err, int code, int limit = EP_POLL_LIMIT) {

@@ -6,40 +6,34 @@
 // (peer pointers), holding for ALL T tokens the normalised activation rows in the 16-bit split form the expert kernels
 // read, the selected expert ids and routing weights, and per source rank one partial output row for each own token.
 // One layer on rank r:
-//   dispatch  r's routing kernel selects the experts of its own tokens; ep_dispatch_push_k then stores each token's ids
-//             and weights into every peer's buffer and its activation row into the buffers of the ranks that hold one of
-//             its selected experts (plain st.global through the peer mapping), and raises r's dispatch flag on every peer;
-//   experts   the planner waits for all R dispatch flags, groups the (token, expert) pairs of the experts held here, the
+//   dispatch  r's routing kernel selects the experts of its own tokens, and the warp that selected a token's experts stores
+//             the token's ids and weights into every peer's buffer and its activation row into the buffers of the ranks
+//             that hold one of its selected experts (plain st.global through the peer mapping; topk_token in router.cuh);
+//             the block then raises the tokens' dispatch flags on every peer;
+//   experts   the planner waits for the dispatch flags of all T tokens, groups the (token, expert) pairs of the experts held here, the
 //             gate/up and down kernels run as on one GPU (all their reads are local HBM);
 //   combine   ep_partial_push_k adds, per token, the weighted rows of the experts held here in router-rank order and stores
-//             that ONE partial row into the owner's buffer (only where this rank had a selected expert), then raises r's
-//             combine flag on every peer; ep_combine_norm_k on the owner waits for all R combine flags and adds the
+//             that ONE partial row into the owner's buffer (only where this rank had a selected expert), then raises the
+//             token's combine flag there; ep_combine_norm_k on the owner waits for the token's R combine flags and adds the
 //             partial rows in rank order 0..R-1, the shared expert's row and the residual, normalises, and the next
 //             layer's dispatch follows.
-// A flag is a 32-bit word per source rank holding step * EP_PHASES + layer + 1 of the last completed push (monotonic; the
+// A flag is a 32-bit word (dispatch: per token; combine: per source rank and token) holding step * EP_PHASES + layer + 1 of
+// the last completed push (monotonic; the
 // step counter lives in device memory so that a captured graph can be replayed). Writers order data before flag with
 // __threadfence_system() and a release store at system scope; readers poll with acquire loads at system scope and read the
 // peer-written data past L1. Every poll loop is bounded: on a time-out the kernel records EP_ERR_* in the context's error
 // word and carries on with whatever is in the buffer (always valid ids and finite numbers from an earlier layer), so
 // nothing hangs or faults and the host sees the failure in moexb_ctx_status.
-// Why a rank can never overwrite data a peer still reads: each rank waits for ALL ranks' flags in both waits, so a rank is
-// at most one phase ahead of any other; the rows it pushes in phase p+1 are read by the peer's kernels of phase p+1 only,
-// which start after the peer's own phase-p push, which is what this rank waited for.
+// Why a rank can never overwrite data a peer still reads: the owner of a token sends the token's row and ids of layer l+1
+// only after its combine of layer l for that token, which waited for the token's combine flag of EVERY rank (raised whether
+// or not that rank had a row to send), and a rank raises it only after its planner, gate/up, down and partial-sum kernels of
+// layer l are done with the token; the partial rows a rank writes for layer l+1 come after its planner of layer l+1, which
+// waited for every token's dispatch flag, which the owner raises after its combine has read the partial rows of layer l.
 #pragma once
 #include "common.cuh"
 #include "stream.cuh"
 
 namespace moexb {
-
-constexpr int EP_MAX_RANKS = 8;
-
-struct EpGeom {
-    int rank, world, T, K, n_own_max;
-    int tok0[EP_MAX_RANKS + 1];   // rank r owns tokens [tok0[r], tok0[r+1])
-    int exp0[EP_MAX_RANKS + 1];   // and holds routed experts [exp0[r], exp0[r+1])
-};
-struct EpLayout { size_t xs, idx, w, part, flag_a, flag_b, bytes; };   // byte offsets inside an exchange buffer
-struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };                        // exchange buffer of every rank, as mapped here
 
 __host__ __device__ inline size_t ep_align(size_t x) { return (x + 255) & ~(size_t)255; }
 __host__ inline EpLayout ep_layout(int T, int K, int world) {
@@ -50,73 +44,29 @@ __host__ inline EpLayout ep_layout(int T, int K, int world) {
     l.idx = at; at = ep_align(at + (size_t)T * K * 4);
     l.w = at; at = ep_align(at + (size_t)T * K * 4);
     l.part = at; at = ep_align(at + (size_t)world * n_own_max * EH * 4);
-    l.flag_a = at; at = ep_align(at + EP_MAX_RANKS * 4);
-    l.flag_b = at; at = ep_align(at + EP_MAX_RANKS * 4);
+    l.flag_a = at; at = ep_align(at + (size_t)T * 4);
+    l.flag_b = at; at = ep_align(at + (size_t)world * n_own_max * 4);
     l.bytes = at;
     return l;
 }
 
-// The block's peer stores are ordered before the ticket; the last block of the grid then raises this rank's flag
-// (flag_off inside the exchange buffer) on every peer.
-__device__ __forceinline__ void ep_signal_peers(const EpGeom& g, const EpPeers& p, size_t flag_off, unsigned value, int* ticket, int blocks) {
-    __shared__ int s_last;
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int got = atomicAdd(ticket, 1);
-        s_last = got == blocks - 1;
-        if (s_last) *ticket = 0;
-    }
-    __syncthreads();
-    if (s_last && (int)threadIdx.x < g.world && (int)threadIdx.x != g.rank) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<unsigned*>(p.base[threadIdx.x] + flag_off) + g.rank, value);
-    }
-}
-
 __global__ void ep_step_k(unsigned* step) { *step += 1; }
-
-// Dispatch. grid (own tokens, world), 256 threads: block (i, dst) sends token tok0[rank] + i to rank dst: ids and weights
-// always (the planner there walks all T tokens), the activation row (row_bytes: 4 or 8 KB) only if dst holds one of the
-// token's selected experts.
-__global__ void __launch_bounds__(256) ep_dispatch_push_k(const EpGeom g, const EpPeers p, const EpLayout lay, int row_bytes,
-                                                          const unsigned* __restrict__ step, unsigned phase, int* ticket) {
-    pdl_wait();
-    pdl_trigger();
-    const int t = g.tok0[g.rank] + blockIdx.x, dst = blockIdx.y, K = g.K;
-    if (dst != g.rank) {
-        const uint8_t* lb = p.base[g.rank];
-        uint8_t* db = p.base[dst];
-        const int* idx = reinterpret_cast<const int*>(lb + lay.idx) + (size_t)t * K;
-        const float* w = reinterpret_cast<const float*>(lb + lay.w) + (size_t)t * K;
-        bool needed = false;
-        for (int r = 0; r < K; r++) { const int e = idx[r]; needed |= e >= g.exp0[dst] && e < g.exp0[dst + 1]; }
-        if ((int)threadIdx.x < K) reinterpret_cast<int*>(db + lay.idx)[(size_t)t * K + threadIdx.x] = idx[threadIdx.x];
-        else if ((int)threadIdx.x < 2 * K) reinterpret_cast<float*>(db + lay.w)[(size_t)t * K + threadIdx.x - K] = w[threadIdx.x - K];
-        if (needed) {
-            const uint4* src = reinterpret_cast<const uint4*>(lb + lay.xs + (size_t)t * row_bytes);
-            uint4* out = reinterpret_cast<uint4*>(db + lay.xs + (size_t)t * row_bytes);
-            for (int i = threadIdx.x; i < row_bytes / 16; i += 256) out[i] = src[i];
-        }
-    }
-    ep_signal_peers(g, p, lay.flag_a, *step * EP_PHASES + phase, ticket, gridDim.x * gridDim.y);
-}
 
 // Combine, sending side. grid T, 256 threads: block t adds the rows ypair[t*K + r] of the ranks r whose expert is held
 // here, in rank order (the sum reduce_residual_norm_k forms for a rank's share), and stores the one partial row into the
 // token owner's buffer at [this rank][token's place among the owner's tokens]. Tokens none of whose experts are held here
 // send nothing; the owner derives the same from the ids.
 __global__ void __launch_bounds__(256) ep_partial_push_k(const EpGeom g, const EpPeers p, const EpLayout lay, const float* __restrict__ ypair,
-                                                         const unsigned* __restrict__ step, unsigned phase, int* ticket) {
+                                                         const unsigned* __restrict__ step, unsigned phase) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, K = g.K;
     const int* idx = reinterpret_cast<const int*>(p.base[g.rank] + lay.idx) + (size_t)t * K;
     unsigned have = 0;
     for (int r = 0; r < K; r++) { const int e = __ldcg(idx + r); if (e >= g.exp0[g.rank] && e < g.exp0[g.rank + 1]) have |= 1u << r; }
+    int owner = 0;
+    while (t >= g.tok0[owner + 1]) owner++;
     if (have) {
-        int owner = 0;
-        while (t >= g.tok0[owner + 1]) owner++;
         float* dst = reinterpret_cast<float*>(p.base[owner] + lay.part) + ((size_t)g.rank * g.n_own_max + (t - g.tok0[owner])) * EH;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -134,10 +84,19 @@ __global__ void __launch_bounds__(256) ep_partial_push_k(const EpGeom g, const E
             *reinterpret_cast<float4*>(dst + k0) = acc;
         }
     }
-    ep_signal_peers(g, p, lay.flag_b, *step * EP_PHASES + phase, ticket, gridDim.x);
+    // the token's flag on its owner, raised whether or not a row went out: it also tells the owner that this rank is done with
+    // the token's row and ids of this layer. One system-scope fence, by one thread after the block barrier (the barrier orders
+    // the block's stores before it and the fence is cumulative).
+    if (owner != g.rank) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            st_relaxed_sys(reinterpret_cast<unsigned*>(p.base[owner] + lay.flag_b) + (size_t)g.rank * g.n_own_max + (t - g.tok0[owner]), *step * EP_PHASES + phase);
+        }
+    }
 }
 
-// Combine, owner's side. grid own tokens, 256 threads: waits for the combine flags of all ranks, then for own token i:
+// Combine, owner's side. grid own tokens, 256 threads: waits for all ranks' combine flags of own token i, then:
 // value = sum over source ranks 0..R-1 (those that hold one of the token's experts) of their partial row, + the shared
 // expert's row, + the residual row x[i] when x is given. x[i] and out[i] receive the value when given. When xn is given the
 // next layer's input is left there (absolute token index): rmsnorm(value) if norm, else the value itself, with its 16-bit
@@ -151,9 +110,8 @@ __global__ void __launch_bounds__(256) ep_combine_norm_k(const EpGeom g, const u
     pdl_trigger();
     const int i = blockIdx.x, t = g.tok0[g.rank] + i, K = g.K;
     if ((int)threadIdx.x < g.world && (int)threadIdx.x != g.rank)
-        ep_wait_flag(reinterpret_cast<const unsigned*>(local + lay.flag_b) + threadIdx.x, *step * EP_PHASES + phase, err, EP_ERR_COMBINE_WAIT);
-    __syncthreads();
-    __threadfence_system();
+        ep_wait_flag(reinterpret_cast<const unsigned*>(local + lay.flag_b) + (size_t)threadIdx.x * g.n_own_max + i, *step * EP_PHASES + phase, err, EP_ERR_COMBINE_WAIT);
+    __syncthreads();   // the polling threads' acquire loads, then the barrier: the peers' rows are visible to the whole block
     // the ids of the layer whose partial rows these are: the routing kernel of the next layer has not run yet
     const int* idx = reinterpret_cast<const int*>(local + lay.idx) + (size_t)t * K;
     unsigned need = 0;

@@ -847,15 +847,15 @@ static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float*
     });
 }
 
-template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2>
-static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
-    constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D, NB>();
+template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2, bool PLAN = false>
+static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, const PlanArgs& pa, void* stream) {
+    constexpr int SMEM = tl_smem_bytes<FMT, DOWN, NW, D, NB, PLAN>();
     static_assert(SMEM * CPS <= 227 * 1024, "shared memory of the resident CTAs");
     static PerDeviceOnce once;
-    const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
+    const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS, PLAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "tiled stream kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
-    CUDA_TRY(launch_dep(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS>, CPS * c->sms, NW * 32, SMEM, S(stream), a));
+    CUDA_TRY(launch_dep(stream_tiled_k<FMT, DOWN, NW, D, NB, CPS, PLAN>, CPS * c->sms, NW * 32, SMEM, S(stream), a, pa));
     LAUNCHED(DOWN ? "stream_tiled_down" : "stream_tiled_gate_up");
     return MOEXB_OK;
 }
@@ -865,22 +865,33 @@ static int tiled_launch_cfg(moexb_ctx* c, const TiledArgs& a, void* stream) {
 // (CTAs of 8 warps, 2 slices in flight each - the same bytes in flight, twice the issue slots in use).
 // From 8 tokens on the symmetric formats also take sub-items of up to 8 pairs (two column blocks; tiled_maxp below): the
 // gate/up columns of 8 pairs are 66 KB, so that kernel runs as one CTA of 16 warps per SM.
-template <int FMT, bool DOWN>
-static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* stream) {
-    if (T < 8) return tiled_launch_cfg<FMT, DOWN, 4, 4>(c, a, stream);
-    if (FMT == FMT_ZP || c->pairs_per_pass == 4) return tiled_launch_cfg<FMT, DOWN, 8, 2>(c, a, stream);
+// plan: the gate/up kernel makes the work list itself (no planning launch before it).
+template <int FMT, bool DOWN, bool PLAN = false>
+static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* stream, const PlanArgs& pa = PlanArgs{}) {
+    static_assert(!PLAN || FMT == FMT_SYM_F16, "the in-kernel work list fits beside the ring of the fp16-scale format only");
+    if (T < 8) return tiled_launch_cfg<FMT, DOWN, 4, 4, 1, 2, PLAN>(c, a, pa, stream);
+    if (FMT == FMT_ZP || c->pairs_per_pass == 4) return tiled_launch_cfg<FMT, DOWN, 8, 2, 1, 2, PLAN>(c, a, pa, stream);
     if constexpr (FMT == FMT_ZP) return MOEXB_OK;
-    else if constexpr (DOWN) return tiled_launch_cfg<FMT, DOWN, 8, 2, 2, 2>(c, a, stream);
-    else return tiled_launch_cfg<FMT, DOWN, 16, 2, 2, 1>(c, a, stream);
+    else if constexpr (DOWN) return tiled_launch_cfg<FMT, DOWN, 8, 2, 2, 2, PLAN>(c, a, pa, stream);
+    else return tiled_launch_cfg<FMT, DOWN, 16, 2, 2, 1, PLAN>(c, a, pa, stream);
 }
 // Pairs per sub-item that tiled_launch_one's kernels take.
 static int tiled_maxp(const moexb_ctx* c, int fmt, int T) { return (T >= 8 && fmt != FMT_ZP) ? c->pairs_per_pass : 4; }
+// Whether the gate/up kernel can make the work list of this batch itself (tiled.cuh: plan_in_cta).
+// (fp16-scale format: with the wider slices of the other formats the list does not fit beside two CTAs' rings.)
+static bool plan_in_kernel(const moexb_ctx* c, int fmt, int T, int K, int E) {
+    static const bool on = [] { const char* e = getenv("MOEXB_PLAN_IN_KERNEL"); return !(e && e[0] == '0'); }();
+    return on && fmt == FMT_SYM_F16 && T <= PL_MAX_TOKENS && K <= PL_MAX_K && E <= PL_MAX_E;
+}
 
-// The same on blobs in the tiled layout (sub-item slots point into a tiled layer image).
-static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, int T, void* stream) {
+// The same on blobs in the tiled layout (sub-item slots point into a tiled layer image). plan: null = the list is already
+// in the context (subs, nsub, pairs); else the gate/up kernel makes it and leaves it there for the down kernel.
+static int tiled_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, int T, void* stream, const PlanArgs* plan = nullptr) {
     TiledArgs a{c->subs, c->nsub, pairs, c->xs, act32, c->act_split, ypair, c->err};
     return by_fmt(fmt, [&]<int FMT>() {
-        int rc = tiled_launch_one<FMT, false>(c, a, T, stream);
+        int rc;
+        if constexpr (FMT == FMT_SYM_F16) rc = plan ? tiled_launch_one<FMT, false, true>(c, a, T, stream, *plan) : tiled_launch_one<FMT, false>(c, a, T, stream);
+        else rc = tiled_launch_one<FMT, false>(c, a, T, stream);
         if (rc != MOEXB_OK) return rc;
         TiledArgs d = a;
         d.xs = c->act_split;
@@ -1011,14 +1022,16 @@ extern "C" {
 }  // extern "C"
 // Router logits (into the context, [T][E + 1]) and the top-K selection in one launch; decode: also the K + 1 one-pair
 // sub-items of a single token.
+struct RouteEp { const EpDevice* dev; int row_bytes; unsigned phase; const unsigned* step; };
 template <typename WT>
-static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0) {
+static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0, const RouteEp* rep = nullptr) {
     // tok0: the T rows at xf are tokens tok0.. of the batch - their logits, ids and weights go to those rows of the workspace
     const int E = L->n_routed;
     const WT* W = static_cast<const WT*>(L->router);
     float* logits = c->logits + (size_t)tok0 * (E + 1);
-    const TopkOut o{c->idx + (size_t)tok0 * K, c->w + (size_t)tok0 * K, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
-                    decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr};
+    TopkOut o{c->idx + (size_t)tok0 * K, c->w + (size_t)tok0 * K, L->slot_table, decode ? c->slots : nullptr, decode ? c->wts : nullptr,
+              decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr};
+    if (rep) { o.ep = rep->dev; o.ep_row_bytes = rep->row_bytes; o.ep_phase = rep->phase; o.ep_step = rep->step; }
     auto run = [&]<int NJ>() -> int {
         if (T < 8) {
             constexpr int WARPS = 8;
@@ -1056,9 +1069,9 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
 }
 
 extern "C" {
-static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0) {
+static int layer_route(moexb_ctx* c, moexb_layer* L, const float* xf, int T, int K, void* stream, bool decode, int tok0 = 0, const RouteEp* rep = nullptr) {
     PROF(c, MOEXB_PROF_ROUTER, stream);
-    return L->router_dtype == MOEXB_F32 ? route_launch<float>(c, L, xf, T, K, stream, decode, tok0) : route_launch<__half>(c, L, xf, T, K, stream, decode, tok0);
+    return L->router_dtype == MOEXB_F32 ? route_launch<float>(c, L, xf, T, K, stream, decode, tok0, rep) : route_launch<__half>(c, L, xf, T, K, stream, decode, tok0, rep);
 }
 
 // One layer. xin: the layer input as f32 [T][H]. flags as moexb_layer_forward. pre_normed: the context already holds
@@ -1111,10 +1124,12 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
         if (rc != MOEXB_OK) return rc;
         ranks = K + 1;
     } else {
-        {
+        const int parts = (x_bf16 && !block) ? 1 : 2;
+        const int maxp = prefill ? PF_NMAX / parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
+        const bool in_kernel = tiled && !prefill && plan_in_kernel(c, L->fmt, T, K, E);
+        const PlanArgs plan{c->idx, c->w, T, K, E, L->slot_table, L->first_local, L->first_local + L->n_local, shared ? c->logits + E : nullptr, ld, sh0, sh1, maxp, c->subs, c->pairs, c->nsub, nullptr, nullptr, 0u};
+        if (!in_kernel) {
             PROF(c, MOEXB_PROF_GROUP, stream);
-            const int parts = (x_bf16 && !block) ? 1 : 2;
-            const int maxp = prefill ? PF_NMAX / parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
             // room in shared memory for the routed pairs (12 bytes each), so that the list is written out in full lines
             constexpr int PLAN_STAGE_MAX = 196608;
             static PerDeviceOnce plan_once;
@@ -1128,8 +1143,8 @@ static int layer_impl(moexb_ctx* c, moexb_layer* L, const float* xin, int T, int
             // reduction skips them by expert id
             if (!all_local && !streaming) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)T * K * EH * sizeof(float), st));
         }
-        rc = prefill ? prefill_experts(c, L->fmt, c->pairs, xf, T, (x_bf16 && !block) ? 1 : 2, c->ypair, stream)
-           : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
+        rc = prefill ? prefill_experts(c, L->fmt, c->pairs, xf, T, parts, c->ypair, stream)
+           : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream, in_kernel ? &plan : nullptr)
            : streaming ? stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream)
                        : pairs_launch(c, L->fmt, c->items, c->nitems, min(E, T * K) + 1, c->pairs, xf, c->act, c->ypair, stream);
         if (rc != MOEXB_OK) return rc;
@@ -1364,7 +1379,7 @@ struct moexb_ep {
     int n_routed = 0;
     float* x = nullptr;         // [n_own_max][H] residual rows of the own tokens
     unsigned* step = nullptr;   // device: steps begun so far
-    int* tickets = nullptr;     // device: block counters of the two push kernels (return to zero)
+    EpDevice* dev = nullptr;    // device copy of geometry, peer pointers and layout (what the routing kernel's push reads)
     // what the context pointed at before its activations, ids and weights moved into the exchange buffer
     uint16_t* saved_xs = nullptr; int* saved_idx = nullptr; float* saved_w = nullptr;
     // host-side state of the layer in progress (set by dispatch, used by experts)
@@ -1432,10 +1447,10 @@ int moexb_ep_create(moexb_ctx* c, int rank, int world, int T, int K, int n_route
     e->lay = ep_layout(T, K, world);
     cudaError_t err = cudaMalloc((void**)&e->x, (size_t)e->g.n_own_max * EH * sizeof(float));
     if (err == cudaSuccess) err = cudaMalloc((void**)&e->step, sizeof(unsigned));
-    if (err == cudaSuccess) err = cudaMalloc((void**)&e->tickets, 2 * sizeof(int));
+    if (err == cudaSuccess) err = cudaMalloc((void**)&e->dev, sizeof(EpDevice));
     if (err == cudaSuccess) err = cudaMemset(e->step, 0, sizeof(unsigned));
-    if (err == cudaSuccess) err = cudaMemset(e->tickets, 0, 2 * sizeof(int));
-    if (err != cudaSuccess) { cudaFree(e->x); cudaFree(e->step); cudaFree(e->tickets); delete e; return fail(MOEXB_ERR_NOMEM, "ep_create: %s", cudaGetErrorString(err)); }
+    if (err == cudaSuccess) { const EpDevice h{e->g, e->peers, e->lay}; err = cudaMemcpy(e->dev, &h, sizeof h, cudaMemcpyHostToDevice); }
+    if (err != cudaSuccess) { cudaFree(e->x); cudaFree(e->step); cudaFree(e->dev); delete e; return fail(MOEXB_ERR_NOMEM, "ep_create: %s", cudaGetErrorString(err)); }
     // the context's activation columns, ids and weights now live in this rank's exchange buffer, where the peers write them
     uint8_t* local = e->peers.base[rank];
     e->saved_xs = c->xs; e->saved_idx = c->idx; e->saved_w = c->w;
@@ -1449,7 +1464,7 @@ int moexb_ep_create(moexb_ctx* c, int rank, int world, int T, int K, int n_route
 int moexb_ep_destroy(moexb_ep* e) {
     if (!e) return MOEXB_OK;
     e->ctx->xs = e->saved_xs; e->ctx->idx = e->saved_idx; e->ctx->w = e->saved_w;
-    cudaFree(e->x); cudaFree(e->step); cudaFree(e->tickets);
+    cudaFree(e->x); cudaFree(e->step); cudaFree(e->dev);
     delete e;
     return MOEXB_OK;
 }
@@ -1553,12 +1568,9 @@ int moexb_ep_dispatch(moexb_ep* e, moexb_layer* L, int l, const void* X, int x_d
         split8_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xn_own, c->xs + (size_t)t0 * parts * EH, EH, parts, n);
         LAUNCHED("split8_rows");
     }
-    rc = layer_route(c, L, xn_own, n_own, K, stream, false, t0);
-    if (rc != MOEXB_OK) return rc;
-    PROF(c, MOEXB_PROF_OTHER, stream);
-    CUDA_TRY(launch_dep(ep_dispatch_push_k, dim3(n_own, e->g.world), 256, 0, st, e->g, e->peers, e->lay, parts * EH * 2, (const unsigned*)e->step, (unsigned)(l + 1), e->tickets));
-    LAUNCHED("ep_dispatch_push");
-    return MOEXB_OK;
+    // the routing kernel sends each token to the peers as soon as its experts are selected and raises the tokens' flags
+    const RouteEp rep{e->dev, parts * EH * 2, (unsigned)(l + 1), e->step};
+    return layer_route(c, L, xn_own, n_own, K, stream, false, t0, &rep);
 }
 
 int moexb_ep_experts(moexb_ep* e, moexb_layer* L, int l, void* stream) {
@@ -1568,25 +1580,28 @@ int moexb_ep_experts(moexb_ep* e, moexb_layer* L, int l, void* stream) {
     cudaStream_t st = S(stream);
     const int T = e->g.T, K = e->g.K, E = L->n_routed, t0 = e->g.tok0[e->g.rank], t1 = e->g.tok0[e->g.rank + 1];
     const bool tiled = L->layout == MOEXB_LAYOUT_TILED, prefill = e->prefill;
-    {
+    const int maxp = prefill ? PF_NMAX / e->parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
+    const unsigned* flags = reinterpret_cast<const unsigned*>(e->peers.base[e->g.rank] + e->lay.flag_a);
+    const bool in_kernel = tiled && !prefill && plan_in_kernel(c, L->fmt, T, K, E);
+    // the dispatch flags of all tokens are waited for by whoever makes the work list: the gate/up CTAs, or the planning kernel
+    const PlanArgs plan{c->idx, c->w, T, K, E, L->slot_table, L->first_local, L->first_local + L->n_local, c->logits + E, E + 1, t0, t1, maxp, c->subs, c->pairs, c->nsub, flags, e->step, (unsigned)(l + 1)};
+    if (!in_kernel) {
         PROF(c, MOEXB_PROF_GROUP, stream);
-        const int maxp = prefill ? PF_NMAX / e->parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
         constexpr int PLAN_STAGE_MAX = 196608;
         static PerDeviceOnce plan_once;
         const cudaError_t plan_attr = plan_once.run([] { return cudaFuncSetAttribute(group_plan1_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PLAN_STAGE_MAX); });
         const int stage_pairs = plan_attr == cudaSuccess && (size_t)T * K * 12 <= PLAN_STAGE_MAX ? T * K : 0;
-        const unsigned* flags = reinterpret_cast<const unsigned*>(e->peers.base[e->g.rank] + e->lay.flag_a);
         CUDA_TRY(launch_dep(group_plan1_k<true>, 1, 1024, (size_t)stage_pairs * 12, st, (const int*)c->idx, (const float*)c->w, T, K, E, L->slot_table, c->items, c->pairs, c->nitems,
                             c->subs, c->nsub, maxp, prefill ? c->subs2 : nullptr, c->nsub2, PF_NMAX / 2, (const float*)(c->logits + E), E + 1, t0, t1, stage_pairs,
                             flags, (const unsigned*)e->step, (unsigned)(l + 1), e->g.world, e->g.rank, c->err));
         LAUNCHED("group_plan");
     }
     rc = prefill ? prefill_experts(c, L->fmt, c->pairs, nullptr, T, e->parts, c->ypair, stream, true)
-       : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream)
+       : tiled ? tiled_experts(c, L->fmt, c->pairs, nullptr, c->ypair, T, stream, in_kernel ? &plan : nullptr)
                : stream_experts(c, L->fmt, c->pairs, nullptr, c->ypair, stream);
     if (rc != MOEXB_OK) return rc;
     PROF(c, MOEXB_PROF_COMBINE, stream);
-    CUDA_TRY(launch_dep(ep_partial_push_k, T, 256, 0, st, e->g, e->peers, e->lay, (const float*)c->ypair, (const unsigned*)e->step, (unsigned)(l + 1), e->tickets + 1));
+    CUDA_TRY(launch_dep(ep_partial_push_k, T, 256, 0, st, e->g, e->peers, e->lay, (const float*)c->ypair, (const unsigned*)e->step, (unsigned)(l + 1)));
     LAUNCHED("ep_partial_push");
     return MOEXB_OK;
 }

@@ -118,6 +118,10 @@ struct TopkOut {
     int* idx; float* w;
     const uint8_t* const* slot_table; const uint8_t** slots_out; float* wts_out;
     moexb_pair_item* dsubs; moexb_pair* dpairs; int* dnsub;
+    // expert parallelism (ep.cuh): the warp that selected a token's experts also sends the token to the peers - ids and
+    // weights to every rank, the activation row (ep_row_bytes at [token] of the exchange buffer's row area) to the ranks that
+    // hold one of the selected experts - and the block then raises the tokens' dispatch flags
+    const EpDevice* ep = nullptr; int ep_row_bytes = 0; unsigned ep_phase = 0; const unsigned* ep_step = nullptr;
 };
 __device__ __forceinline__ unsigned f2key(float v) { const unsigned u = __float_as_uint(v); return (u & 0x80000000u) ? ~u : (u | 0x80000000u); }
 __device__ __forceinline__ float key2f(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
@@ -173,6 +177,53 @@ __device__ __forceinline__ void topk_token(const float* __restrict__ l, int t, i
         o.wts_out[(size_t)t * (K + 1) + K] = gate;
         if (o.dsubs) { o.dsubs[K] = {o.slot_table[E], K, 1}; o.dpairs[K] = {0, K, gate}; o.dnsub[0] = K + 1; o.dnsub[1] = 0; }
     }
+    if (o.ep) {
+        const EpDevice& ep = *o.ep;
+        const int rank = ep.g.rank, ta = ep.g.tok0[rank] + t;   // t counts from this rank's first token
+        unsigned need = 0;
+        if (lane < K)
+            for (int s = 0; s < ep.g.world; s++) if (mine_i >= ep.g.exp0[s] && mine_i < ep.g.exp0[s + 1]) need = 1u << s;
+        need = __reduce_or_sync(0xffffffffu, need);
+        const float wk = norm ? mine / total : mine;
+        // the row (at most 8 KB = 16 x 16 bytes per lane) is read once, every load in flight before the first store
+        const uint4* src = reinterpret_cast<const uint4*>(ep.p.base[rank] + ep.lay.xs + (size_t)ta * o.ep_row_bytes);
+        const int n16 = o.ep_row_bytes / 16;
+        uint4 v[16];
+        if (need & ~(1u << rank)) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) if (lane + 32 * j < n16) v[j] = src[lane + 32 * j];
+        }
+        for (int d = 0; d < ep.g.world; d++) {
+            if (d == rank) continue;
+            uint8_t* db = ep.p.base[d];
+            if (lane < K) {
+                reinterpret_cast<int*>(db + ep.lay.idx)[(size_t)ta * K + lane] = mine_i;
+                reinterpret_cast<float*>(db + ep.lay.w)[(size_t)ta * K + lane] = wk;
+            }
+            if (need >> d & 1) {
+                uint4* out = reinterpret_cast<uint4*>(db + ep.lay.xs + (size_t)ta * o.ep_row_bytes);
+#pragma unroll
+                for (int j = 0; j < 16; j++) if (lane + 32 * j < n16) out[lane + 32 * j] = v[j];
+            }
+        }
+    }
+}
+
+// After the warps of a block have sent tokens [t_first, t_first + n) of this rank (topk_token with o.ep): one system-scope
+// fence by one thread behind the block barrier, then the tokens' dispatch flags on every peer.
+__device__ __forceinline__ void ep_raise_dispatch_flags(const TopkOut& o, int t_first, int n) {
+    if (!o.ep) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const EpDevice& ep = *o.ep;
+        const unsigned value = *o.ep_step * EP_PHASES + o.ep_phase;
+        __threadfence_system();
+        for (int d = 0; d < ep.g.world; d++) {
+            if (d == ep.g.rank) continue;
+            unsigned* flags = reinterpret_cast<unsigned*>(ep.p.base[d] + ep.lay.flag_a) + ep.g.tok0[ep.g.rank] + t_first;
+            for (int i = 0; i < n; i++) st_relaxed_sys(flags + i, value);
+        }
+    }
 }
 
 // One warp per token.
@@ -189,15 +240,14 @@ __global__ void __launch_bounds__(WARPS * 32) router_topk_k(const float* __restr
 // after its global writes); the last one sees the writes of all the others and resets the counter for the next launch.
 __device__ __forceinline__ bool last_block_done(int* cnt, int expected) {
     __shared__ int s_last;
-    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();   // one fence per block: the barrier orders the block's writes before it, and it is cumulative
         const int ticket = atomicAdd(cnt, 1);
         s_last = ticket == expected - 1;
-        if (s_last) *cnt = 0;
+        if (s_last) { *cnt = 0; __threadfence(); }
     }
     __syncthreads();
-    if (s_last) __threadfence();
     return s_last;
 }
 
@@ -242,6 +292,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemv_k(const WT* __restrict_
     if (lane == 0 && out < O) y[(size_t)t * O + out] = acc;
     if (!last_block_done(done + t, gridDim.x)) return;
     if (threadIdx.x < 32) topk_token<NJ, true>(y + (size_t)t * O, t, E, K, norm, lane, o);
+    ep_raise_dispatch_flags(o, t, 1);
 }
 
 // The same for a batch: gemm_rows_k's tiling (a block stages TR token rows in shared memory, each of its WARPS warps owns
@@ -313,6 +364,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
         }
     if (!last_block_done(done + blockIdx.y, gridDim.x)) return;
     for (int r = warp; r < TR && r0 + r < T; r += WARPS) topk_token<NJ, true>(y + (size_t)(r0 + r) * O, r0 + r, E, K, norm, lane, o);
+    ep_raise_dispatch_flags(o, r0, min(TR, T - r0));
 }
 
 // The same for a prefill chunk, register-tiled. A block of 8 warps owns 32 tokens x 16 outputs; warp (wm, wn) the 8 tokens
@@ -398,6 +450,7 @@ __global__ void __launch_bounds__(256, 2) route_gemm2_k(const WT* __restrict__ W
         }
     if (!last_block_done(done + blockIdx.y, gridDim.x)) return;
     for (int r = warp; r < RG2_TM && r0 + r < T; r += 8) topk_token<NJ, true>(y + (size_t)(r0 + r) * O, r0 + r, E, K, norm, lane, o);
+    ep_raise_dispatch_flags(o, r0, min(RG2_TM, T - r0));
 }
 
 // ---- pair grouping: bucket the T*K (token, rank) pairs by expert (moex.cu:1466-1486; kernels.cuh:1030-1045) ----------

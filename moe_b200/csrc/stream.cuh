@@ -483,8 +483,9 @@ __device__ __forceinline__ int block_scan_1024(int v, int& total) {
 // order and may change from run to run - every pair's result is independent of its place). List 1 keeps sub-items of more
 // than maxp / 2 pairs first (nsub[1] = their number); list 2 is in expert order. The shared expert (slot_table[E], when
 // gate_logits is given) gets the tokens [sh0, sh1) with weight sigmoid(gate logit), as the last item.
-// EP: the ids and weights were stored by other GPUs (ep.cuh): thread s < ep_world first waits (bounded) until rank s's
-// dispatch flag ep_flags[s] has reached *ep_step * EP_PHASES + ep_phase, and the lists are then read past L1.
+// EP: the ids and weights of the tokens outside [sh0, sh1) were stored by other GPUs (ep.cuh): the block first waits (bounded)
+// until every such token's dispatch flag ep_flags[t] has reached *ep_step * EP_PHASES + ep_phase, and the lists are then read
+// past L1.
 template <bool EP>
 __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ idx, const float* __restrict__ w, int T, int K, int E,
                                                       const uint8_t* const* __restrict__ slot_table, moexb_pair_item* __restrict__ items,
@@ -507,9 +508,10 @@ __global__ void __launch_bounds__(1024) group_plan1_k(const int* __restrict__ id
     pdl_wait();
     pdl_trigger();
     if constexpr (EP) {
-        if (e < ep_world && e != ep_rank) ep_wait_flag(ep_flags + e, *ep_step * EP_PHASES + ep_phase, err, EP_ERR_DISPATCH_WAIT);
-        __syncthreads();
-        __threadfence_system();
+        const unsigned target = *ep_step * EP_PHASES + ep_phase;
+        for (int t = e; t < T; t += 1024)
+            if (t < sh0 || t >= sh1) ep_wait_flag(ep_flags + t, target, err, EP_ERR_DISPATCH_WAIT);
+        __syncthreads();   // the polling threads' acquire loads, then the barrier: the peers' lists are visible to the whole block
     }
     auto ld_idx = [&](int p) { return EP ? __ldcg(idx + p) : __ldg(idx + p); };
     auto ld_w = [&](int p) { return EP ? __ldcg(w + p) : __ldg(w + p); };

@@ -78,6 +78,131 @@ __global__ void __launch_bounds__(256) tile_expert_k(const uint8_t* __restrict__
     }
 }
 
+// ---- the work list made inside the gate/up kernel (no planning launch) ------------------------------------------------------
+//
+// For batches of up to PL_MAX_TOKENS tokens every CTA of the gate/up kernel builds the whole work list itself, in shared memory,
+// from the router's ids and weights (at most 512 pairs: two microseconds of redundant work per CTA, against a separate one-block
+// launch that the whole grid would wait for). The list is the one group_plan1_k makes - pairs bucketed by expert, sub-items of
+// at most maxp pairs with the wide ones first, the shared expert's pairs appended for tokens [sh0, sh1) - except that an
+// expert's pairs are in token order here, so every CTA derives the same list: a pair's place is (pairs of its expert in
+// earlier 32-pair chunks) + (its rank among the equal ids of its own chunk, from one warp match). CTA 0 also writes the list
+// to global memory, for the down kernel.
+constexpr int PL_MAX_TOKENS = 64, PL_MAX_K = 8, PL_MAX_PAIRS = PL_MAX_TOKENS * PL_MAX_K, PL_MAX_E = 256;
+constexpr int PL_MAX_SUBS = PL_MAX_E + PL_MAX_PAIRS / 4 + PL_MAX_TOKENS / 4 + 2;
+struct PlanArgs {
+    const int* idx; const float* w; int T, K, E;
+    const uint8_t* const* slot_table;   // E + 1 blob pointers, null = expert not held here
+    int e_lo, e_hi;                     // the routed experts held here are [e_lo, e_hi) (the same fact, without a load per pair)
+    const float* gate_logits; int gl_stride, sh0, sh1, maxp;
+    moexb_pair_item* subs_out; moexb_pair* pairs_out; int* nsub_out;   // the list in global memory (written by CTA 0)
+    const unsigned* ep_flags; const unsigned* ep_step; unsigned ep_phase;   // expert parallelism: per-token dispatch flags to wait for, or null
+};
+// The list as the CTA keeps it (8 KB): a sub-item as (expert id, first pair, pairs), a pair as (p, weight) with the token
+// derived from p (routed pairs p = t * K + rank, the shared expert's p = T * K + t).
+struct PlanSub { uint16_t e, start, count, pad; };
+struct PlanSmem {
+    PlanSub subs[PL_MAX_SUBS];
+    uint2 pairs[PL_MAX_PAIRS + PL_MAX_TOKENS];
+    int nsub[2], npairs, n, K;
+    __device__ __forceinline__ moexb_pair pair_at(int i) const {
+        const uint2 v = pairs[i];
+        const int p = (int)v.x;
+        return {p < n ? p / K : p - n, p, __uint_as_float(v.y)};
+    }
+};
+// Scratch of the planning itself (8 KB): lives where the weight ring will be, whose first copy is requested after planning.
+struct PlanTmp {
+    int cnt[PL_MAX_E], start[PL_MAX_E], wat[PL_MAX_E], nat[PL_MAX_E];
+    uint8_t chunk[PL_MAX_PAIRS / 32][PL_MAX_E];   // pairs of expert e in chunk c; then the exclusive prefix over the chunks
+    int np, nw, nn;
+};
+
+__device__ __forceinline__ void plan_in_cta(PlanSmem& L, PlanTmp& P, const PlanArgs& a, int* err) {
+    const int tid = threadIdx.x, NT = blockDim.x, lane = tid & 31;
+    const int n = a.T * a.K, E = a.E, maxp = a.maxp;
+    if (a.ep_flags) {
+        const unsigned target = *a.ep_step * EP_PHASES + a.ep_phase;
+        for (int t = tid; t < a.T; t += NT)
+            if (t < a.sh0 || t >= a.sh1) ep_wait_flag(a.ep_flags + t, target, err, EP_ERR_DISPATCH_WAIT);
+    }
+    for (int i = tid; i < PL_MAX_E; i += NT) P.cnt[i] = 0;
+    for (int i = tid; i < (int)sizeof(P.chunk) / 4; i += NT) reinterpret_cast<uint32_t*>(P.chunk)[i] = 0;
+    __syncthreads();
+    constexpr int MAXPT = PL_MAX_PAIRS / 128;   // pairs per thread with the smallest CTA (4 warps)
+    int ex[MAXPT], rk[MAXPT];
+    float wv[MAXPT];
+#pragma unroll
+    for (int k = 0; k < MAXPT; k++) {
+        const int p = tid + k * NT;   // a warp's 32 pairs are consecutive: one chunk
+        ex[k] = -1; rk[k] = 0; wv[k] = 0.f;
+        if (k * NT < n) {             // the whole warp takes part in the match
+            int e = p < n ? __ldcg(a.idx + p) : -1;
+            if (e < a.e_lo || e >= a.e_hi) e = -1;   // experts that are not held here are dropped
+            if (p < n) wv[k] = __ldcg(a.w + p);
+            const unsigned m = __match_any_sync(0xffffffffu, e);
+            ex[k] = e; rk[k] = __popc(m & ((1u << lane) - 1));
+            if (e >= 0 && rk[k] == 0) P.chunk[p >> 5][e] = (uint8_t)__popc(m);
+        }
+    }
+    __syncthreads();
+    const int nchunks = (n + 31) >> 5;
+    for (int e = tid; e < E; e += NT) {
+        int c = 0;
+        for (int ch = 0; ch < nchunks; ch++) { const int v = P.chunk[ch][e]; P.chunk[ch][e] = (uint8_t)c; c += v; }
+        P.cnt[e] = c;
+    }
+    __syncthreads();
+    auto wide = [maxp](int c) { return c / maxp + (c % maxp > maxp / 2); };
+    auto narrow = [maxp](int c) { return (int)(c % maxp > 0 && c % maxp <= maxp / 2); };
+    if (tid < 32) {   // exclusive scans over the experts: pairs, wide sub-items, narrow sub-items; a lane takes 8 experts
+        int c[8], sp = 0, sw = 0, sn = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { const int e = lane * 8 + j; c[j] = e < E ? P.cnt[e] : 0; sp += c[j]; sw += wide(c[j]); sn += narrow(c[j]); }
+        int ip = sp, iw = sw, in = sn;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, ip, o), uw = __shfl_up_sync(0xffffffffu, iw, o), un = __shfl_up_sync(0xffffffffu, in, o);
+            if (lane >= o) { ip += up; iw += uw; in += un; }
+        }
+        if (lane == 31) { P.np = ip; P.nw = iw; P.nn = in; }
+        int bp = ip - sp, bw = iw - sw, bn = in - sn;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int e = lane * 8 + j;
+            if (e < E) { P.start[e] = bp; P.wat[e] = bw; P.nat[e] = bn; }
+            bp += c[j]; bw += wide(c[j]); bn += narrow(c[j]);
+        }
+    }
+    __syncthreads();
+    const uint8_t* sslot = a.slot_table[E];
+    const int Ts = (a.gate_logits && sslot && a.sh1 > a.sh0) ? a.sh1 - a.sh0 : 0;
+    const int np = P.np, nw = P.nw, nn = P.nn, all_wide = nw + wide(Ts);
+    for (int e = tid; e < E; e += NT) {
+        const int c = P.cnt[e];
+        if (!c) continue;
+        const int cw = wide(c), at = P.start[e];
+        for (int j = 0; j * maxp < c; j++)
+            L.subs[j < cw ? P.wat[e] + j : all_wide + P.nat[e]] = {(uint16_t)e, (uint16_t)(at + j * maxp), (uint16_t)min(maxp, c - j * maxp), 0};
+    }
+#pragma unroll
+    for (int k = 0; k < MAXPT; k++)
+        if (ex[k] >= 0) {
+            const int p = tid + k * NT;
+            L.pairs[P.start[ex[k]] + P.chunk[p >> 5][ex[k]] + rk[k]] = make_uint2((unsigned)p, __float_as_uint(wv[k]));
+        }
+    if (Ts) {
+        const int cw = wide(Ts), ns = all_wide + nn;
+        for (int t = tid; t < Ts; t += NT) {
+            const float gl = a.gate_logits[(size_t)(a.sh0 + t) * a.gl_stride];
+            L.pairs[np + t] = make_uint2((unsigned)(n + a.sh0 + t), __float_as_uint(1.f / (1.f + expf(-gl))));
+        }
+        for (int j = tid; j * maxp < Ts; j += NT)
+            L.subs[j < cw ? nw + j : ns] = {(uint16_t)E, (uint16_t)(np + j * maxp), (uint16_t)min(maxp, Ts - j * maxp), 0};
+    }
+    if (tid == 0) { L.nsub[0] = all_wide + nn + (Ts ? narrow(Ts) : 0); L.nsub[1] = all_wide; L.npairs = np + Ts; L.n = n; L.K = a.K; }
+    __syncthreads();   // also: the scratch is free for the first weight copies
+}
+
 struct TiledArgs {
     const moexb_pair_item* subs;  // sub-items: at most 4 * NB pairs each, slot = tiled blob
     const int* nsub;
@@ -99,9 +224,11 @@ struct TiledArgs {
 // DOWN = true : row tile = 16 down rows, 1 slice (K = 512); ypair = w * (down . act).
 // NB = 8-column blocks of activations per sub-item (1: up to 4 pairs, 2: up to 8 pairs - the weights of an expert with 5-8
 // pairs are then unpacked once instead of twice); CPS = CTAs per SM the launch is sized for.
-template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2>
-__global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a) {
+// PLAN (gate/up only): the CTA makes the work list itself (plan_in_cta) from pa instead of reading a.subs / a.pairs / a.nsub.
+template <int FMT, bool DOWN, int NW, int D, int NB = 1, int CPS = 2, bool PLAN = false>
+__global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a, const PlanArgs pa) {
     static_assert(NB == 1 || FMT != FMT_ZP, "two column blocks are built for the symmetric formats only");
+    static_assert(!PLAN || !DOWN, "the down kernel reads the list the gate/up kernel left in global memory");
     constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
     constexpr int KS = DOWN ? 1 : 4;                       // slices per row tile
     constexpr int RPS = (DOWN ? 128 : 64) / NW;            // rounds per sub-item
@@ -112,6 +239,8 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* bsm = smem + NW * D * SB;                                 // 8 * NB activation columns
     uint64_t* bars = reinterpret_cast<uint64_t*>(bsm + 8 * NB * BCOL); // full[NW][D]
+    PlanSmem& P = *reinterpret_cast<PlanSmem*>(bars + NW * D + 8);      // PLAN only (the launch adds the room)
+    static_assert(!PLAN || sizeof(PlanTmp) <= NW * D * SB, "the planning scratch fits where the ring will be");
     // zero point: the sum of the activations over each 32-input chunk, per column: [K slice][group][chunk][8 columns]
     __shared__ __align__(16) float csum[Z ? KS * 8 * 2 * 8 : 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -122,11 +251,32 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     // too), so the weight copies start while gate/up still runs; only the activation columns wait for it.
     // The trigger comes after the wait so that the down kernel, which reads the sub-items before its own wait, cannot
     // start before the kernel that writes them has finished.
-    if (!DOWN) { pdl_wait(); pdl_trigger(); }
+    if constexpr (PLAN) {
+        pdl_wait();
+        plan_in_cta(P, *reinterpret_cast<PlanTmp*>(smem), pa, a.err);
+        if (blockIdx.x == 0) {
+            // the list for the kernels that follow; the down kernel may read it as soon as every CTA here has triggered
+            for (int i = threadIdx.x; i < P.nsub[0]; i += NW * 32) { const PlanSub su = P.subs[i]; pa.subs_out[i] = {pa.slot_table[su.e], su.start, su.count}; }
+            for (int i = threadIdx.x; i < P.npairs; i += NW * 32) pa.pairs_out[i] = P.pair_at(i);
+            if (threadIdx.x < 2) pa.nsub_out[threadIdx.x] = P.nsub[threadIdx.x];
+            __threadfence();
+            __syncthreads();
+        }
+        pdl_trigger();
+        // the planning scratch was written through the generic proxy where the bulk copies (async proxy) are about to land
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    } else if (!DOWN) { pdl_wait(); pdl_trigger(); }
+    // the work list: the CTA's own (PLAN) or the one in global memory
+    auto sub_at = [&](int i) -> moexb_pair_item {
+        if constexpr (PLAN) { const PlanSub su = P.subs[i]; return {pa.slot_table[su.e], su.start, su.count}; }
+        else return a.subs[i];
+    };
+    auto pair_at = [&](int i) -> moexb_pair { if constexpr (PLAN) return P.pair_at(i); else return a.pairs[i]; };
+    const int nsub0 = PLAN ? P.nsub[0] : a.nsub[0], nsub1 = PLAN ? P.nsub[1] : a.nsub[1];
     // This CTA's contiguous range of rounds: an equal share of the cost, a round of a wide sub-item (more than 4 pairs,
     // they come first in subs[]) counting CW and any other CN.
     constexpr int CN = 10, CW = NB == 2 ? (DOWN ? 14 : 12) : 10;
-    const long long RW = NB == 2 ? (long long)a.nsub[1] * RPS : 0, R = (long long)a.nsub[0] * RPS;
+    const long long RW = NB == 2 ? (long long)nsub1 * RPS : 0, R = (long long)nsub0 * RPS;
     const long long C = RW * CW + (R - RW) * CN;
     auto round_at = [&](long long x) { return (int)(x < RW * CW ? x / CW : RW + (x - RW * CW) / CN); };
     const int r0 = round_at(C * blockIdx.x / gridDim.x), r1 = round_at(C * (blockIdx.x + 1) / gridDim.x);
@@ -137,7 +287,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     // slice q of this warp: round r0 + q / KS, row tile rin*NW + warp, K slice q % KS
     auto issue = [&](int q) {
         const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, wt = rin * NW + warp;
-        const uint8_t* src = a.subs[sub].slot + (size_t)(DOWN ? 256 + wt : wt * 4 + q % KS) * SB;
+        const uint8_t* src = sub_at(sub).slot + (size_t)(DOWN ? 256 + wt : wt * 4 + q % KS) * SB;
         const uint32_t bar = smem_u32(full + q % D);
         mbar_arrive_expect_tx(bar, SB);
         bulk_g2s(smem_u32(ring + (q % D) * SB), src, SB, bar);
@@ -148,23 +298,20 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};  // acd: the second column block
     int cur_sub = -1, n = 0, start = 0;
-    // A warp whose wait on a slice runs out stops computing and requesting, but keeps walking the same sequence of CTA
-    // barriers as the others (so nobody is left waiting for it), then waits (bounded) for its own copies in flight.
-    int issued = min(D, Q), landed = 0;   // slices requested / seen complete by this warp (the lanes agree)
-    bool dead = false;
+    int failed = -1;   // the slice this warp gave up waiting for
     const uint8_t* bcol = bsm + g * BCOL + t * 16;  // the lane's activation column (pair slot g >> 1, part g & 1)
     for (int q = 0; q < Q; q++) {
         const int r = r0 + q / KS, sub = r / RPS, rin = r % RPS, ks = q % KS;
         if (sub != cur_sub) {
             // new sub-item: the CTA's warps swap the activation columns together (their weight copies stay in flight)
             cur_sub = sub;
-            const moexb_pair_item it = a.subs[sub];
+            const moexb_pair_item it = sub_at(sub);
             n = it.count; start = it.start;
             __syncthreads();
             constexpr int CHUNKS16 = KB * 2 / 16;
             for (int i = threadIdx.x; i < 2 * n * CHUNKS16; i += NW * 32) {
                 const int col = i / CHUNKS16, ch = i % CHUNKS16;
-                const moexb_pair pr = a.pairs[start + (col >> 1)];
+                const moexb_pair pr = pair_at(start + (col >> 1));
                 const size_t row = DOWN ? (size_t)pr.p : (size_t)pr.t;
                 cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (row * 2 + (col & 1)) * KB + ch * 8);
             }
@@ -190,9 +337,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
                 __syncthreads();
             }
         }
-        if (dead) continue;   // gave up earlier: no more waits, math or copies - only the barriers above
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT))) { dead = true; continue; }
-        landed = q + 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT))) { failed = q; break; }
         if (ks == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; acd[0] = acd[1] = acd[2] = acd[3] = 0.f; }
         const uint8_t* sl = ring + (q % D) * SB;
         const uint8_t* bp = bcol + ks * 1024;  // 8 groups of 128 bytes per slice
@@ -268,14 +413,13 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(q + D);
         }
-        if (q + D < Q) issued = q + D + 1;
         if (ks == KS - 1) {
             // epilogue: the lane's columns 2t (hi) and 2t+1 (lo) of column block b belong to pair slot 4b + t
             const int wt = rin * NW + warp;
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 if (4 * b + t >= n) break;
-                const moexb_pair pr = a.pairs[start + 4 * b + t];
+                const moexb_pair pr = pair_at(start + 4 * b + t);
                 const float va = b ? acd[0] + acd[1] : acc[0] + acc[1], vb = b ? acd[2] + acd[3] : acc[2] + acc[3];
                 if (DOWN) {
                     const int d = 16 * wt + g;
@@ -293,12 +437,19 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             }
         }
     }
-    // after a time-out: no copy may still be on its way into this CTA's shared memory when the CTA leaves
-    if (dead)
-        for (int q = landed; q < issued; q++) mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT);
+    if (failed >= 0) {
+        // A wait ran out. The other warps of the CTA carry on, so this warp still takes part in every CTA barrier they will
+        // reach (three per change of sub-item with zero-point blobs, else two), without computing; then it waits (bounded) for
+        // the copies it has requested - slices [failed, failed + D) - so that none is in flight when the CTA leaves.
+        for (int q = failed + 1; q < Q; q++) {
+            const int sub = (r0 + q / KS) / RPS;
+            if (sub != cur_sub) { cur_sub = sub; __syncthreads(); __syncthreads(); if (Z) __syncthreads(); }
+        }
+        for (int q = failed; q < min(Q, failed + D); q++) mbar_wait(smem_u32(full + q % D), (q / D) & 1, a.err, ST_ERR_FULL_WAIT);
+    }
 }
 
-template <int FMT, bool DOWN, int NW, int D, int NB = 1>
-constexpr int tl_smem_bytes() { return NW * D * tl_slice_bytes<FMT>() + 8 * NB * st_bcol_bytes<DOWN>() + NW * D * 8 + 64; }
+template <int FMT, bool DOWN, int NW, int D, int NB = 1, bool PLAN = false>
+constexpr int tl_smem_bytes() { return NW * D * tl_slice_bytes<FMT>() + 8 * NB * st_bcol_bytes<DOWN>() + NW * D * 8 + 64 + (PLAN ? (int)sizeof(PlanSmem) + 16 : 0); }
 
 }  // namespace moexb
