@@ -266,6 +266,7 @@ class Env:
         self.dev = torch.device("cuda", self.local)
         self.first, self.count = ep.expert_range(E, self.rank, self.world)
         self.layer_sets = {}
+        self.fallback = None   # set when the peer-memory exchange could not be set up and the all-reduce form ran instead
 
     def barrier(self):
         if self.dist:
@@ -311,18 +312,37 @@ def measure(env, workload):
     else:
         # expert parallel: every rank gets the whole batch, owns 1/world of the tokens and returns their rows; the step of a
         # rank (kernels, pushes into the peers' buffers, bounded waits on their flags) is one graph
-        eps = env.ep.EPStack(ctx, layers, T, K, x_torch_dtype, residual=NL > 1)
-        kernel_count, out_rows = eps.kernel_count, eps.n_own
+        try:
+            eps = env.ep.EPStack(ctx, layers, T, K, x_torch_dtype, residual=NL > 1)
+        except RuntimeError as e:   # raised on every rank together: peer mapping is not available here
+            env.fallback = f"all-reduce form ({e})"
+            eps = None
+        if eps is not None:
+            kernel_count, out_rows = eps.kernel_count, eps.n_own
 
-        class _S:  # the Stack interface on top of the expert-parallel step
-            def run(self, X, out):
-                eps.stack.run(X, out)
+            class _S:  # the Stack interface on top of the expert-parallel step
+                def run(self, X, out):
+                    eps.stack.run(X, out)
 
-            def run_host(self, Xh_, out_h_):
-                eps.stack.run_host(Xh_, out_h_)
+                def run_host(self, Xh_, out_h_):
+                    eps.stack.run_host(Xh_, out_h_)
 
-            def close(self):
-                eps.close()
+                def close(self):
+                    eps.close()
+        else:
+            old = env.ep.EPStackAllReduce(ctx, layers, T, K, x_torch_dtype)
+            kernel_count, out_rows = 0, T
+
+            class _S:  # every rank carries all T rows; one NCCL all-reduce per layer
+                def run(self, X, out):
+                    out.copy_(old.run(X))
+
+                def run_host(self, Xh_, out_h_):
+                    out_h_.copy_(old.run(Xh_), non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+
+                def close(self):
+                    pass
         stack = _S()
     Xh = [torch.from_numpy(tokens(T, s % 8)).to(x_torch_dtype).pin_memory() for s in range(8)]
     Xd = [x.to(dev) for x in Xh]
@@ -366,6 +386,10 @@ def measure(env, workload):
         for l, L in enumerate(layers):
             if world == 1:
                 x = L.forward(x, T, K, out=bufs[l & 1], idx=idx[l], flags=2 if NL > 1 else 0)
+            elif eps is None:
+                part = L.forward_ep(x, T, K, bufs[l & 1], sh0, sh1, idx=idx[l])
+                env.dist.all_reduce(part)
+                x = x.float() + part
             else:
                 if l == 0:
                     eps.ep.begin_step()
@@ -531,6 +555,8 @@ def main():
     for k in ("cpu_baseline", "independent_inputs"):
         if k in head:
             line[k] = head[k]
+    if env.fallback:
+        line["config"]["parallelism"] += " - NOT USED in this run: " + env.fallback
     if others:
         line["workloads"] = others
     if env.rank == 0:

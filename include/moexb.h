@@ -57,7 +57,7 @@ enum { MOEXB_LAYOUT_TILED = 0, MOEXB_LAYOUT_REFERENCE = 1 };
 /* Activation element types accepted by the layer-level calls. */
 enum { MOEXB_F32 = 0, MOEXB_BF16 = 1 };
 
-typedef struct moexb_ctx moexb_ctx;     /* one per process and device: stream-ordered workspace, synthetic tables */
+typedef struct moexb_ctx moexb_ctx;     /* one per device (or more): stream-ordered workspace, synthetic tables */
 typedef struct moexb_layer moexb_layer; /* one MoE layer resident in HBM: E routed experts + 1 shared + router */
 
 /* Work list of the multi-token path, identical to kernels.cuh:688-689. */
@@ -91,6 +91,14 @@ int moexb_router_topk(const float* logits, int E, int K, int norm, int* idx, flo
  * Replaces experts_forward (kernels.cuh:597-673). K <= 16. */
 int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
                           float* out, void* stream, const int* nh);
+/* Which kernels moexb_experts_forward runs. Its reference signature carries no workspace, and the B200 streaming kernels
+ * (cp.async.bulk rings, tensor-core MMA, exact hi + lo activations) need one for the 16-bit activation columns and the
+ * per-expert rows; so an engine that wants them creates a context at start-up and names it here as the workspace of the
+ * pointer-level one-token entry point on that device (null takes it away again; moexb_ctx_destroy does that by itself).
+ * Without one - or with moexb_ctx_set_path(ctx, 1) - moexb_experts_forward runs the fp32 SIMT restatement of the
+ * reference's own two kernels, which is kept as the on-device cross-check. Calls that share a context must not overlap
+ * on the GPU. The multi-token counterpart with a workspace is moexb_pairs_forward_tc. */
+int moexb_set_default_ctx(moexb_ctx* ctx, int device);
 
 /* The same computation for callers that cannot allocate device memory (an engine that gave all free memory to its
  * expert cache at load time, or a decode thread that must never block in cudaMalloc). It has no counterpart in the
@@ -241,6 +249,14 @@ const char* moexb_gguf_tensor_name(const moexb_gguf* g, int i); /* null when i i
  * here). Any out pointer may be null. */
 int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_dims, long long* ne, const void** data,
                       long long* nbytes);
+/* The block formats other than Q4_K, on the host (no GPU): moexb_gguf_dequant_host stands behind gg_dequant (gguf.h:85-255)
+ * for ggml types F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, Q4_K, Q5_K, Q6_K, IQ4_NL and IQ4_XS (n a multiple of the
+ * block size); moexb_gguf_row_to_zp behind gg_zp_row (gguf.h:302-330): one row of `cols` weights (a multiple of 256) into
+ * the zero-point form - qb[cols / 2] nibble bytes, cs[cols / 32 * 2] = [sc, mn] per 32, sup[cols / 256 * 2] = (d, dm) as
+ * fp16 bits per 256 - bit for bit for Q4_K, by the reference's least-squares refit per 32 weights (gguf.h:272-300) for the
+ * others. Other ggml types give MOEXB_ERR_UNSUPPORTED. */
+int moexb_gguf_dequant_host(int ggml_type, const uint8_t* src_host, long long n, float* y_host);
+int moexb_gguf_row_to_zp(int ggml_type, const uint8_t* src_host, int cols, uint8_t* qb, uint8_t* cs, uint16_t* sup);
 /* Fills a MOEXB_FMT_ZP layer from block `block` of the file: blk.N.ffn_{gate,up,down}_exps.weight (Q4_K, shapes
  * [H, I, E], [H, I, E], [I, H, E] with E = the layer's n_routed) for the routed experts the layer holds, re-packed on
  * the device exactly as moexb_q4k_to_zp does; the role of gg_experts (gguf.h:666-694) without the pass through a
@@ -248,7 +264,9 @@ int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_d
  * are Q4_K, the router rows from blk.N.ffn_gate_inp.weight and the shared expert's gate vector from
  * blk.N.ffn_gate_inp_shexp.weight (F32, F16 or BF16, converted to the layer's router dtype). *loaded (may be null)
  * receives a bit set: 1 routed experts, 2 shared expert, 4 router rows, 8 shared gate vector; what a bit does not
- * name is left as it was. Expert tensors of another ggml type give MOEXB_ERR_UNSUPPORTED. Synchronous. */
+ * name is left as it was. Expert tensors in one of the other types moexb_gguf_row_to_zp reads are re-quantised to 4 bits on
+ * the host (all host threads) as the reference's importer does (gg_experts, gguf.h:666-694); any other ggml type gives
+ * MOEXB_ERR_UNSUPPORTED. Synchronous. */
 int moexb_layer_load_gguf(moexb_layer* layer, const moexb_gguf* g, int block, int* loaded);
 
 /* ---- safetensors container ingest ---------------------------------------------------------------------------------- */

@@ -8,5 +8,5 @@ from ._lib import (FMT_SYM_F32, FMT_SYM_F16, FMT_ZP, F32, BF16, F16, LAYOUT_TILE
                    PairItem, Pair, lib)
 from .api import (expert_bytes, gemv_f16, gemv_f32, router_topk, experts_forward, pairs_forward, pairs_forward_dev,
                   pairs_reduce, gated_add_rows, shared_expert_add, group_pairs, dequant, q4k_dequant, q4k_to_zp,
-                  synth_expert_host, synth_q4k_host, Context, Layer, Stack, Gguf, SafeTensors, launch_count, ep_residual_norm,
+                  synth_expert_host, synth_q4k_host, gguf_dequant_host, gguf_row_to_zp, Context, Layer, Stack, Gguf, SafeTensors, launch_count, ep_residual_norm,
                   ExchangeBuffer, EP)

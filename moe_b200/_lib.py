@@ -40,6 +40,7 @@ SIGNATURES = {
     "moexb_gemv_f32": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i]),
     "moexb_router_topk": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i]),
     "moexb_experts_forward": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "moexb_set_default_ctx": (_i, [_vp, _i]),
     "moexb_experts_forward_static": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "moexb_pairs_forward_dev": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
@@ -76,6 +77,8 @@ SIGNATURES = {
     "moexb_gguf_tensor_count": (_i, [_vp]),
     "moexb_gguf_tensor_name": (C.c_char_p, [_vp, _i]),
     "moexb_gguf_tensor": (_i, [_vp, C.c_char_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll), C.POINTER(_vp), C.POINTER(_ll)]),
+    "moexb_gguf_dequant_host": (_i, [_i, _vp, _ll, _vp]),
+    "moexb_gguf_row_to_zp": (_i, [_i, _vp, _i, _vp, _vp, _vp]),
     "moexb_layer_load_gguf": (_i, [_vp, _vp, _i, C.POINTER(_i)]),
     "moexb_st_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "moexb_st_close": (_i, [_vp]),

@@ -121,6 +121,22 @@ def q4k_to_zp(gate, up, down):
     return blob
 
 
+def gguf_dequant_host(ggml_type, raw, n):
+    """moexb_gguf_dequant_host: n values of ggml-typed blocks (numpy uint8) as float32, on the CPU."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    y = np.empty(n, np.float32)
+    check(lib().moexb_gguf_dequant_host(ggml_type, raw.ctypes.data, n, y.ctypes.data))
+    return y
+
+
+def gguf_row_to_zp(ggml_type, raw, cols):
+    """moexb_gguf_row_to_zp: (nibble bytes, [sc, mn] bytes, (d, dm) fp16 bits) of one row, on the CPU."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    qb = np.empty(cols // 2, np.uint8); cs = np.empty(cols // 32 * 2, np.uint8); sup = np.empty(cols // 256 * 2, np.uint16)
+    check(lib().moexb_gguf_row_to_zp(ggml_type, raw.ctypes.data, cols, qb.ctypes.data, cs.ctypes.data, sup.ctypes.data))
+    return qb, cs, sup
+
+
 def synth_expert_host(fmt, seed, layer, expert):
     """The synthetic expert (layer, expert) as a numpy uint8 blob; runs on the CPU."""
     out = np.empty(expert_bytes(fmt), dtype=np.uint8)
@@ -145,6 +161,11 @@ class Context:
 
     def synth_experts(self, fmt, seed, layer, e0, n, dst):
         check(lib().moexb_synth_experts(self.h, fmt, seed, layer, e0, n, _ptr(dst), _stream()))
+
+    def make_default(self, on=True):
+        """moexb_set_default_ctx: the pointer-level one-token entry point (experts_forward) uses this context's workspace and
+        runs the streaming kernels."""
+        check(lib().moexb_set_default_ctx(self.h if on else None, self.device))
 
     def set_path(self, path):
         """0 = streaming tensor-core kernels (default), 1 = fp32 SIMT kernels."""

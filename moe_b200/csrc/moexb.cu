@@ -11,6 +11,7 @@
 #include "ep.cuh"
 #include "gguf_ingest.h"
 #include "st_ingest.h"
+#include "gguf_quant.h"
 
 #include <cmath>
 #include <cstdarg>
@@ -21,6 +22,7 @@
 #include <atomic>
 #include <mutex>
 #include <new>
+#include <thread>
 #include <vector>
 
 using namespace moexb;
@@ -255,9 +257,48 @@ static int decode_launch(moexb_ctx* prof, int fmt, const uint8_t* const* slots, 
         return (int)MOEXB_OK;
     });
 }
+}  // extern "C"
+
+// The context whose workspace the pointer-level one-token entry point may use on each device (moexb_set_default_ctx).
+static std::mutex g_default_lock;
+static moexb_ctx* g_default_ctx[MAX_DEVICES] = {};
+static int stream_experts(moexb_ctx* c, int fmt, const moexb_pair* pairs, float* act32, float* ypair, void* stream);
+static int split_launch(moexb_ctx* c, const float* x, int rows, bool f16, void* stream);
+
+extern "C" {
+
+int moexb_set_default_ctx(moexb_ctx* ctx, int device) {
+    REQUIRE(device >= 0 && device < MAX_DEVICES, "set_default_ctx: device %d", device);
+    REQUIRE(!ctx || ctx->device == device, "set_default_ctx: the context belongs to device %d", ctx ? ctx->device : -1);
+    std::lock_guard<std::mutex> lock(g_default_lock);
+    g_default_ctx[device] = ctx;
+    return MOEXB_OK;
+}
+
 int moexb_experts_forward(int fmt, const uint8_t* const* slots, const float* w, int K, const float* x, float* act,
                           float* out, void* stream, const int* nh) {
-    return decode_launch(nullptr, fmt, slots, w, K, x, act, out, stream, nh);
+    moexb_ctx* c = nullptr;
+    {
+        int dev = -1;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < MAX_DEVICES) { std::lock_guard<std::mutex> lock(g_default_lock); c = g_default_ctx[dev]; }
+    }
+    if (!c || c->path == 1 || K > c->max_tokens * (c->top_k + 1)) return decode_launch(nullptr, fmt, slots, w, K, x, act, out, stream, nh);
+    // With a default context: the streaming tensor-core kernels on the caller's reference-layout blobs. The K experts are K
+    // one-pair sub-items of the one token; act receives the fp32 activations as the reference's scratch does.
+    REQUIRE(slots && w && x && act && out, "experts_forward: null pointer");
+    REQUIRE(K > 0 && K <= 16, "experts_forward: K=%d out of range 1..16", K);
+    REQUIRE(fmt_ok(fmt), "experts_forward: unknown expert format %d", fmt);
+    cudaStream_t st = S(stream);
+    plan_decode_k<<<1, 32, 0, st>>>(slots, w, K, nh, c->subs, c->pairs, c->nsub);
+    LAUNCHED("plan_decode");
+    int rc = split_launch(c, x, 1, false, stream);
+    if (rc != MOEXB_OK) return rc;
+    if (nh) CUDA_TRY(cudaMemsetAsync(c->ypair, 0, (size_t)K * EH * sizeof(float), st));   // rows of the experts beyond *nh stay zero
+    rc = stream_experts(c, fmt, c->pairs, act, c->ypair, stream);
+    if (rc != MOEXB_OK) return rc;
+    pairs_reduce_k<<<dim3((EH / 4 + 255) / 256, 1), 256, 0, st>>>(c->ypair, nullptr, out, K, EH, nullptr);
+    LAUNCHED("pairs_reduce");
+    return MOEXB_OK;
 }
 
 static int pairs_launch(moexb_ctx* prof, int fmt, const moexb_pair_item* items, const int* nitems, int grid_items, const moexb_pair* pairs,
@@ -455,6 +496,10 @@ int moexb_ctx_create(int device, int max_tokens, int max_experts, int top_k, moe
 
 int moexb_ctx_destroy(moexb_ctx* ctx) {
     if (!ctx) return MOEXB_OK;
+    {
+        std::lock_guard<std::mutex> lock(g_default_lock);
+        for (moexb_ctx*& d : g_default_ctx) if (d == ctx) d = nullptr;
+    }
     for (void* p : ctx->owned) cudaFree(p);
     for (auto& r : ctx->recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
     for (auto e : ctx->spare) cudaEventDestroy(e);
@@ -620,8 +665,10 @@ int moexb_gguf_tensor(const moexb_gguf* g, const char* name, int* type, int* n_d
 static int gguf_expect(const moexb_gguf* g, const std::string& name, std::initializer_list<long long> ne, const GgufTensor** out) {
     const GgufTensor* t = g->find(name);
     if (!t) return fail(MOEXB_ERR_ARG, "tensor %s is missing from the GGUF", name.c_str());
-    if (t->type != GGML_Q4_K)
-        return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: %s has ggml type %u; only Q4_K (12) expert tensors are carried over", name.c_str(), t->type);
+    int bn, bb;
+    if (!gq_block(t->type, bn, bb) || !t->data)
+        return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: %s has ggml type %u, which this loader cannot re-quantise (Q4_K is carried over bit for bit; "
+                    "Q5_K, Q6_K, Q8_0, IQ4_NL, IQ4_XS, Q4_0/1, Q5_0/1, F16, BF16 and F32 are refitted to 4 bits)", name.c_str(), t->type);
     bool same = t->n_dims == (int)ne.size();
     int d = 0;
     for (long long v : ne) same = same && t->ne[d++] == v;
@@ -629,6 +676,35 @@ static int gguf_expect(const moexb_gguf* g, const std::string& name, std::initia
                            name.c_str(), t->ne[0], t->ne[1], t->ne[2], t->ne[3], t->n_dims);
     *out = t;
     return MOEXB_OK;
+}
+
+// One expert from three GGUF tensors of any readable type (gate, up [I][H]; down [H][I]; row-major, `type[k]` blocks) into a
+// zero-point blob in the reference layout, on the host: Q4_K rows are carried over bit for bit, the others refitted
+// (gguf_quant.h). What gg_experts does per expert (gguf.h:666-694).
+static bool expert_to_zp_host(const uint32_t type[3], const uint8_t* const src[3], uint8_t* blob) {
+    std::vector<float> w(EH);
+    for (int k = 0; k < 3; k++) {
+        const int rows = k < 2 ? EI : EH, cols = k < 2 ? EH : EI;
+        int bn, bb;
+        if (!gq_block(type[k], bn, bb)) return false;
+        const size_t row_bytes = (size_t)cols / bn * bb;
+        for (int r = 0; r < rows; r++) {
+            const size_t row = (size_t)(k == 0 ? 0 : k == 1 ? EI : 0) + r;   // row inside [gate | up] or inside down
+            const size_t qoff = k < 2 ? row * (EH / 2) : DOWN_Q_OFF + row * (EI / 2);
+            const size_t c0 = k < 2 ? row * (EH / 32) : DOWN_C_OFF + row * (EI / 32);
+            uint8_t* qb = blob + qoff;
+            uint8_t* cs = blob + Q_BYTES + c0 * 2;
+            uint16_t* sup = reinterpret_cast<uint16_t*>(blob + Q_BYTES + CHUNKS * 2 + (c0 / 8) * 4);
+            const uint8_t* p = src[k] + (size_t)r * row_bytes;
+            if (type[k] == GQ_Q4_K) {
+                for (int b = 0; b < cols / 256; b++) q4k_block_to_zp(p + (size_t)b * 144, qb + b * 128, cs + b * 16, reinterpret_cast<uint8_t*>(sup + 2 * b));
+            } else {
+                if (!gq_dequant(type[k], p, cols, w.data())) return false;
+                zp_row_from_values(w.data(), cols, qb, cs, sup);
+            }
+        }
+    }
+    return true;
 }
 
 // `n` router values at src (F32, F16 or BF16, by ggml type id) into the layer's router dtype at dst (host).
@@ -654,7 +730,7 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
     REQUIRE(L && g, "layer_load_gguf: null pointer");
     REQUIRE(block >= 0, "layer_load_gguf: block %d", block);
     if (loaded) *loaded = 0;
-    if (L->fmt != FMT_ZP) return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: Q4_K tensors load into a MOEXB_FMT_ZP layer (this one has format %d)", L->fmt);
+    if (L->fmt != FMT_ZP) return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: GGUF expert tensors load into a MOEXB_FMT_ZP layer (this one has format %d)", L->fmt);
     const std::string p = "blk." + std::to_string(block) + ".";
     const long long E = L->n_routed;
     const GgufTensor* t[3];
@@ -680,7 +756,41 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
         }
         return to_layer_layout(L, c->staging + HALF * eb, dst, n, nullptr);
     };
+    // Any tensor in another type than Q4_K: the experts are re-quantised on the host (gguf_quant.h), a batch of them spread
+    // over the host threads, and uploaded as finished blobs. per[k]: bytes of one expert inside tensor k.
+    auto convert_host = [&](const GgufTensor* const tt[3], int first, int n, uint8_t* dst) -> int {
+        size_t per[3]; uint32_t ty[3];
+        for (int k = 0; k < 3; k++) { int bn, bb; gq_block(tt[k]->type, bn, bb); per[k] = (size_t)EH * EI / bn * bb; ty[k] = tt[k]->type; }
+        std::vector<uint8_t> blobs((size_t)STAGING_BLOBS * eb);
+        for (int i = 0; i < n; i += STAGING_BLOBS) {
+            const int m = min(STAGING_BLOBS, n - i);
+            std::atomic<int> next{0}, bad{0};
+            auto work = [&] {
+                for (int j; (j = next.fetch_add(1)) < m;) {
+                    const uint8_t* src3[3];
+                    for (int k = 0; k < 3; k++) src3[k] = tt[k]->data + (size_t)(first + i + j) * per[k];
+                    if (!expert_to_zp_host(ty, src3, blobs.data() + (size_t)j * eb)) bad = 1;
+                }
+            };
+            std::vector<std::thread> th;
+            const int nt = (int)std::min<unsigned>(std::max(1u, std::thread::hardware_concurrency()), (unsigned)m);
+            for (int q = 1; q < nt; q++) th.emplace_back(work);
+            work();
+            for (auto& x : th) x.join();
+            if (bad) return fail(MOEXB_ERR_UNSUPPORTED, "layer_load_gguf: a block of block %d could not be re-quantised", block);
+            CUDA_TRY(cudaMemcpy(c->staging, blobs.data(), (size_t)m * eb, cudaMemcpyHostToDevice));
+            const int rc2 = to_layer_layout(L, c->staging, dst + (size_t)i * eb, m, nullptr);
+            if (rc2 != MOEXB_OK) return rc2;
+            CUDA_TRY(cudaStreamSynchronize(nullptr));
+        }
+        return MOEXB_OK;
+    };
     const uint8_t* src[3 * HALF];
+    const bool all_q4k = t[0]->type == GGML_Q4_K && t[1]->type == GGML_Q4_K && t[2]->type == GGML_Q4_K;
+    if (!all_q4k) {
+        rc = convert_host(t, L->first_local, L->n_local, L->image);
+        if (rc != MOEXB_OK) return rc;
+    } else
     for (int i = 0; i < L->n_local; i += HALF) {
         const int n = min(HALF, L->n_local - i);
         for (int j = 0; j < n; j++)
@@ -693,10 +803,17 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
     for (int i = 0; i < L->n_local; i++) L->loaded[L->first_local + i] = 1;
     // the shared expert, when the file holds it as Q4_K too
     const GgufTensor *sg = g->find(p + "ffn_gate_shexp.weight"), *su = g->find(p + "ffn_up_shexp.weight"), *sd = g->find(p + "ffn_down_shexp.weight");
-    if (sg && su && sd && sg->type == GGML_Q4_K && su->type == GGML_Q4_K && sd->type == GGML_Q4_K && sg->n_dims == 2 && su->n_dims == 2 &&
+    int sbn, sbb;
+    if (sg && su && sd && sg->data && su->data && sd->data && gq_block(sg->type, sbn, sbb) && gq_block(su->type, sbn, sbb) && gq_block(sd->type, sbn, sbb) &&
+        sg->n_dims == 2 && su->n_dims == 2 &&
         sd->n_dims == 2 && sg->ne[0] == EH && sg->ne[1] == EI && su->ne[0] == EH && su->ne[1] == EI && sd->ne[0] == EI && sd->ne[1] == EH) {
-        src[0] = sg->data; src[1] = su->data; src[2] = sd->data;
-        rc = convert(src, 1, L->image + (size_t)L->n_local * eb);
+        if (sg->type == GGML_Q4_K && su->type == GGML_Q4_K && sd->type == GGML_Q4_K) {
+            src[0] = sg->data; src[1] = su->data; src[2] = sd->data;
+            rc = convert(src, 1, L->image + (size_t)L->n_local * eb);
+        } else {
+            const GgufTensor* st3[3] = {sg, su, sd};
+            rc = convert_host(st3, 0, 1, L->image + (size_t)L->n_local * eb);
+        }
         if (rc != MOEXB_OK) return rc;
         CUDA_TRY(cudaStreamSynchronize(nullptr));
         got |= 2;
@@ -715,6 +832,29 @@ int moexb_layer_load_gguf(moexb_layer* L, const moexb_gguf* g, int block, int* l
         got |= 8;
     }
     if (loaded) *loaded = got;
+    return MOEXB_OK;
+}
+
+// gg_dequant (gguf.h:85-255) for the block types this library reads, on the host: n values (a multiple of the block size).
+int moexb_gguf_dequant_host(int ggml_type, const uint8_t* src_host, long long n, float* y_host) {
+    REQUIRE(src_host && y_host && n > 0, "gguf_dequant_host: bad argument");
+    if (!gq_dequant((uint32_t)ggml_type, src_host, n, y_host))
+        return fail(MOEXB_ERR_UNSUPPORTED, "gguf_dequant_host: ggml type %d is not readable here, or n=%lld is not a multiple of its block size", ggml_type, n);
+    return MOEXB_OK;
+}
+
+// gg_zp_row (gguf.h:302-330) on the host: one row of `cols` weights (a multiple of 256) of a GGUF tensor into the zero-point
+// form - nibble bytes qb[cols / 2], [sc, mn] cs[cols / 32 * 2], (d, dm) fp16 bits sup[cols / 256 * 2].
+int moexb_gguf_row_to_zp(int ggml_type, const uint8_t* src_host, int cols, uint8_t* qb, uint8_t* cs, uint16_t* sup) {
+    REQUIRE(src_host && qb && cs && sup, "gguf_row_to_zp: null pointer");
+    REQUIRE(cols > 0 && cols % 256 == 0, "gguf_row_to_zp: cols=%d must be a positive multiple of 256", cols);
+    if (ggml_type == (int)GQ_Q4_K) {
+        for (int b = 0; b < cols / 256; b++) q4k_block_to_zp(src_host + (size_t)b * 144, qb + b * 128, cs + b * 16, reinterpret_cast<uint8_t*>(sup + 2 * b));
+        return MOEXB_OK;
+    }
+    std::vector<float> w(cols);
+    if (!gq_dequant((uint32_t)ggml_type, src_host, cols, w.data())) return fail(MOEXB_ERR_UNSUPPORTED, "gguf_row_to_zp: ggml type %d is not readable here", ggml_type);
+    zp_row_from_values(w.data(), cols, qb, cs, sup);
     return MOEXB_OK;
 }
 
@@ -908,7 +1048,7 @@ static int prefill_launch_one(moexb_ctx* c, const PrefillArgs& a, void* stream) 
     const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(prefill_k<FMT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "prefill kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
-    prefill_k<FMT, DOWN><<<c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
+    prefill_k<FMT, DOWN><<<2 * c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
     LAUNCHED(DOWN ? "prefill_down" : "prefill_gate_up");
     return MOEXB_OK;
 }

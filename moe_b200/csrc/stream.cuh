@@ -615,7 +615,7 @@ __global__ void __launch_bounds__(1024) plan_subitems_k(const moexb_pair_item* _
 // One token: the K (or *nh) decode experts as sub-items of one pair each, pair k = (token 0, row k, weight w[k]).
 __global__ void plan_decode_k(const uint8_t* const* __restrict__ slots, const float* __restrict__ w, int K, const int* __restrict__ nh,
                               moexb_pair_item* __restrict__ subs, moexb_pair* __restrict__ pairs, int* __restrict__ nsub) {
-    const int k = threadIdx.x, n = nh ? *nh : K;
+    const int k = threadIdx.x, n = nh ? min(max(*nh, 0), K) : K;
     if (k < n) { subs[k] = {slots[k], k, 1}; pairs[k] = {0, k, w[k]}; }
     if (k == 0) *nsub = n;
 }

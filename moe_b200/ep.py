@@ -101,7 +101,18 @@ class EPStack:
         self.buf = api.ExchangeBuffer(T, K, world)
         handles = [None] * world
         dist.all_gather_object(handles, self.buf.handle, group=group)
-        ptrs = [self.buf.ptr if r == rank else self.buf.open_peer(handles[r]) for r in range(world)]
+        # every rank maps every other rank's buffer; if that fails anywhere (no peer access, IPC closed to this process) all
+        # ranks learn of it and raise together, so that the caller can fall back as one
+        err, ptrs = None, None
+        try:
+            ptrs = [self.buf.ptr if r == rank else self.buf.open_peer(handles[r]) for r in range(world)]
+        except Exception as e:   # noqa: BLE001 - reported to every rank below
+            err = f"rank {rank}: {e}"
+        errs = [None] * world
+        dist.all_gather_object(errs, err, group=group)
+        if any(errs):
+            self.buf.close()
+            raise RuntimeError("peer mapping of the exchange buffers failed: " + "; ".join(e for e in errs if e))
         self.ep = api.EP(ctx, rank, world, T, K, layers[0].n_routed, ptrs)
         self.t0, self.n_own = self.ep.first_token, self.ep.n_own
         dist.barrier(group=group)   # every rank's buffer is mapped everywhere before the first store

@@ -6,6 +6,9 @@ reference tree (default /root/reference) and oracle/_ref built (make -C oracle):
 Outputs (all small, committed):
   q4k_fixture.bin      the Q4_K record of the reference's tests/gguf_blocks.bin (16 real super-blocks + the 4096 fp32
                        values the gguf Python package gives for them), same record framing: u32 type, u32 n, raw, f32
+  gguf_blocks_subset.bin  the records of the same fixture for the block formats the loader reads (F32, F16, BF16, Q8_0, Q4_0,
+                       Q4_1, Q5_0, Q5_1, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS), same framing
+  gguf_zp_ref.npz      gg_zp_row of the compiled reference on each of those records whose length is a multiple of 256
   q4k_zp_ref.npz       gg_zp_row(GG_Q4_K) of the compiled reference on that record: nibble bytes, [sc, mn], (d, dmin)
   run_pairs_ref.npz    CpuExperts::run_pairs / run_pairs_small / run of the compiled reference on seeded synthetic
                        experts (symmetric and zero-point), inputs included (X) or identified by CRC (blobs)
@@ -49,8 +52,35 @@ def q4k_record():
     raise SystemExit("no Q4_K record in the fixture")
 
 
+READ_TYPES = (0, 1, 30, 8, 2, 3, 6, 7, 20, 12, 13, 14, 23)
+
+
+def block_subset():
+    """The fixture's records of READ_TYPES, and the reference's zero-point refit of each."""
+    with open(os.path.join(REF, "tests", "gguf_blocks.bin"), "rb") as f:
+        data = f.read()
+    sizes = {0: (1, 4), 1: (1, 2), 30: (1, 2), 8: (32, 34), 2: (32, 18), 20: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24),
+             39: (32, 17), 10: (256, 84), 11: (256, 110), 23: (256, 136), 18: (256, 98), 21: (256, 110), 12: (256, 144),
+             13: (256, 176), 14: (256, 210)}
+    off, out, zp = 0, b"", {}
+    while off < len(data):
+        t, n = struct.unpack_from("<II", data, off)
+        bn, bb = sizes[t]
+        raw_len = n // bn * bb
+        if t in READ_TYPES:
+            out += data[off:off + 8 + raw_len + 4 * n]
+            if n % 256 == 0:
+                raw = np.frombuffer(data, np.uint8, raw_len, off + 8).copy()
+                qb, cs, sup = o.ref_gg_zp_row(t, raw, n)
+                zp[f"qb{t}"], zp[f"cs{t}"], zp[f"sup{t}"] = qb, cs, sup
+        off += 8 + raw_len + 4 * n
+    open(os.path.join(HERE, "gguf_blocks_subset.bin"), "wb").write(out)
+    np.savez_compressed(os.path.join(HERE, "gguf_zp_ref.npz"), **zp)
+
+
 def main():
     assert o.ref() is not None, "oracle/_ref is not built: make -C oracle"
+    block_subset()
     rec, n, raw_len = q4k_record()
     open(os.path.join(HERE, "q4k_fixture.bin"), "wb").write(rec)
     raw = np.frombuffer(rec, np.uint8, raw_len, 8).copy()

@@ -112,10 +112,32 @@ def test_bad_files_are_refused_with_a_reason(tmp_path):
 E_SMALL, SEED, BLOCK = 32, 21, 3
 
 
+def random_blocks(rng, n_blocks, block_bytes, d_offsets, scale_range=None):
+    """n_blocks blocks of random bytes with small positive fp16 values at the byte offsets of the block's d / dmin."""
+    b = rng.integers(0, 256, (n_blocks, block_bytes), dtype=np.uint8)
+    for off in d_offsets:
+        b[:, off:off + 2] = (rng.uniform(1e-3, 1e-2, n_blocks).astype(np.float16)).view(np.uint8).reshape(n_blocks, 2)
+    return b.reshape(-1)
+
+
+def other_format_experts(rng):
+    """Expert tensors of two distinct experts repeated to E_SMALL: gate as Q6_K (210-byte blocks, d at byte 208), up as Q5_K
+    (176 bytes, d and dmin at 0 and 2), down as IQ4_XS (136 bytes, d at 0); and an F16 shared expert."""
+    nb = EH * EI // 256
+    reps = E_SMALL // 2
+    gate = np.tile(random_blocks(rng, 2 * nb, 210, [208]), reps)
+    up = np.tile(random_blocks(rng, 2 * nb, 176, [0, 2]), reps)
+    down = np.tile(random_blocks(rng, 2 * nb, 136, [0]), reps)
+    sh = [(rng.standard_normal(EH * EI) * 0.05).astype(np.float16).view(np.uint8) for _ in range(3)]
+    return gate, up, down, sh[0], sh[1], sh[2]
+
+
 @pytest.fixture(scope="module")
 def expert_file(tmp_path_factory):
     """Block 3 of a GGUF with 32 routed Q4_K experts + a Q4_K shared expert, an F16 router and a BF16 shared gate vector;
-    block 4 with the same experts but an F32 router and no shared tensors; block 5 with Q6_K-typed expert tensors."""
+    block 4 with the same experts but an F32 router and no shared tensors; block 5 with Q2_K-typed expert tensors (a type the
+    loader does not read); block 6 with 32 experts in three other block formats - gate Q6_K, up Q5_K, down IQ4_XS - and an
+    F16 shared expert, which the loader re-quantises to 4 bits."""
     path = str(tmp_path_factory.mktemp("gguf") / "experts.gguf")
     parts = [m.synth_q4k_host(SEED, BLOCK, e) for e in range(E_SMALL + 1)]
     stack = [np.concatenate([p[k] for p in parts[:E_SMALL]]) for k in range(3)]
@@ -137,9 +159,17 @@ def expert_file(tmp_path_factory):
                         (p + "ffn_down_shexp.weight", (EI, EH), gf.GGML_Q4_K, parts[E_SMALL][2]),
                         (p + "ffn_gate_inp_shexp.weight", (EH,), gf.GGML_BF16, gate_bf16.tobytes())]
     p = f"blk.{BLOCK + 2}."
-    q6 = np.zeros(EH * EI // 256 * 210, np.uint8)  # one expert's worth of Q6_K blocks
-    tensors += [(p + "ffn_gate_exps.weight", (EH, EI, 1), 14, q6), (p + "ffn_up_exps.weight", (EH, EI, 1), 14, q6),
-                (p + "ffn_down_exps.weight", (EI, EH, 1), 14, q6)]
+    q2 = np.zeros(EH * EI // 256 * 84 * E_SMALL, np.uint8)  # Q2_K blocks
+    tensors += [(p + "ffn_gate_exps.weight", (EH, EI, E_SMALL), 10, q2), (p + "ffn_up_exps.weight", (EH, EI, E_SMALL), 10, q2),
+                (p + "ffn_down_exps.weight", (EI, EH, E_SMALL), 10, q2)]
+    p = f"blk.{BLOCK + 3}."
+    mixed = other_format_experts(rng)
+    tensors += [(p + "ffn_gate_exps.weight", (EH, EI, E_SMALL), 14, mixed[0]), (p + "ffn_up_exps.weight", (EH, EI, E_SMALL), 13, mixed[1]),
+                (p + "ffn_down_exps.weight", (EI, EH, E_SMALL), 23, mixed[2]),
+                (p + "ffn_gate_shexp.weight", (EH, EI), gf.GGML_F16, mixed[3]), (p + "ffn_up_shexp.weight", (EH, EI), gf.GGML_F16, mixed[4]),
+                (p + "ffn_down_shexp.weight", (EI, EH), gf.GGML_F16, mixed[5]),
+                (p + "ffn_gate_inp.weight", (EH, E_SMALL), gf.GGML_F32, W[:E_SMALL].tobytes()),
+                (p + "ffn_gate_inp_shexp.weight", (EH,), gf.GGML_F32, W[E_SMALL].tobytes())]
     gf.write_gguf(path, [("general.architecture", gf.STR, "qwen35moe")], tensors)
     Wr = np.concatenate([w16.astype(np.float32), W[E_SMALL:]])  # what a layer holds after loading block 3
     return path, Wr, W
@@ -198,7 +228,7 @@ def test_gguf_load_of_a_slice_of_experts_and_refusals(gctx, expert_file):
         L.export_blob(7)
     with pytest.raises(m.MoexbError, match="missing from the GGUF"):
         L.load_gguf(g, 9)
-    with pytest.raises(m.MoexbError, match="only Q4_K"):
+    with pytest.raises(m.MoexbError, match="cannot re-quantise"):
         L.load_gguf(g, BLOCK + 2)
     L.close()
     L = m.Layer(gctx, m.FMT_ZP, 64)
@@ -208,4 +238,38 @@ def test_gguf_load_of_a_slice_of_experts_and_refusals(gctx, expert_file):
     L = m.Layer(gctx, m.FMT_SYM_F16, E_SMALL)
     with pytest.raises(m.MoexbError, match="MOEXB_FMT_ZP"):
         L.load_gguf(g, BLOCK)
+    L.close(); g.close()
+
+
+@pytest.mark.gpu
+def test_gguf_block_in_other_formats_is_requantised_as_the_reference_does(gctx, expert_file):
+    """Expert tensors that are not Q4_K (here Q6_K, Q5_K, IQ4_XS and an F16 shared expert) are re-quantised to 4 bits at load
+    time by the per-32 least-squares refit: the loaded blobs hold, row for row, what moexb_gguf_row_to_zp gives - which is byte
+    for byte what the reference's gg_zp_row gives - and the layer computes on them what the oracle computes on the same blobs."""
+    import torch
+    path, _, W = expert_file
+    g = m.Gguf(path)
+    L = m.Layer(gctx, m.FMT_ZP, E_SMALL, router_dtype=m.F32)
+    assert L.load_gguf(g, BLOCK + 3) == 15
+    blobs = [L.export_blob(e) for e in range(E_SMALL + 1)]
+    assert np.array_equal(blobs[0], blobs[2]) and not np.array_equal(blobs[0], blobs[1])   # the file repeats two experts
+    names = ("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight")
+    for k, (name, cols, rows) in enumerate(zip(names, (EH, EH, EI), (EI, EI, EH))):
+        ty, ne, raw = g.tensor(f"blk.{BLOCK + 3}.{name}")
+        row_bytes = raw.size // (E_SMALL * rows)
+        for e, r in ((0, 0), (1, rows - 1), (5, 17)):
+            src = raw[(e * rows + r) * row_bytes:(e * rows + r + 1) * row_bytes]
+            qb, cs, sup = m.gguf_row_to_zp(ty, src, cols)
+            row = (0 if k == 0 else EI if k == 1 else 0) + r
+            qoff = row * (EH // 2) if k < 2 else 2 * EI * (EH // 2) + row * (EI // 2)
+            assert np.array_equal(blobs[e][qoff:qoff + cols // 2], qb), (name, e, r)
+            if o.ref() is not None:
+                rq, rc, rs = o.ref_gg_zp_row(ty, src, cols)
+                assert np.array_equal(qb, rq) and np.array_equal(cs, rc) and np.array_equal(sup, rs), (name, e, r)
+    X = np.random.default_rng(3).standard_normal((5, EH)).astype(np.float32)
+    idx = torch.empty(5, 8, dtype=torch.int32, device="cuda:0")
+    out = L.forward(torch.from_numpy(X).to("cuda:0"), 5, idx=idx).cpu().numpy()
+    ref, ri, _, _ = o.layer_forward(m.FMT_ZP, blobs, W, X, 8)
+    assert np.array_equal(idx.cpu().numpy(), ri)
+    assert np.linalg.norm(out - ref) <= 1e-3 * np.linalg.norm(ref)
     L.close(); g.close()

@@ -116,8 +116,20 @@ def make_work(rng, blobs_dev, counts, T):
     return items, pairs, jobs, p
 
 
+@pytest.mark.parametrize("kernels", ["simt", "streaming"])
 @pytest.mark.parametrize("fmt", FMTS)
-def test_experts_forward_decode(experts, fmt):
+def test_experts_forward_decode(ctx, experts, fmt, kernels):
+    """moexb_experts_forward with the reference's arguments: on the fp32 SIMT restatement (no workspace named) and on the
+    streaming tensor-core kernels (a default context named as its workspace)."""
+    ctx.make_default(kernels == "streaming")
+    try:
+        _experts_forward_decode(experts, fmt)
+        assert ctx.status() == 0
+    finally:
+        ctx.make_default(False)
+
+
+def _experts_forward_decode(experts, fmt):
     host, devb = experts[fmt]
     rng = np.random.default_rng(3)
     K = 6
