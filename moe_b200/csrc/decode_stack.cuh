@@ -193,6 +193,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
     __shared__ unsigned s_keys[DS_THREADS];   // the candidates' logits as ordered integer keys
     __shared__ int s_cidx[DS_THREADS];        // and their expert ids
     __shared__ unsigned s_wmax[DS_WARPS];
+    __shared__ unsigned s_tau;
     __shared__ int s_wcnt[DS_WARPS];
     __shared__ int s_idx2[DS_MAXK];
     __shared__ const uint8_t* s_slot2[DS_MAXK + 1];
@@ -347,15 +348,20 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             const unsigned wmax = __reduce_max_sync(0xffffffffu, key);
             if (lane == 0) s_wmax[warp] = wmax;
             __syncthreads();
-            unsigned tau = 0u;   // fewer warps than K: every logit is a candidate
-            if (nw >= K) {
-                for (int w2 = 0; w2 < nw; w2++) {   // the warp maximum with exactly K - 1 maxima before it
-                    const unsigned m2 = s_wmax[w2];
+            // the threshold: the warp maximum with exactly K - 1 maxima before it (lane w2 of warp 0 ranks maximum w2); with fewer
+            // warps than K every logit is a candidate
+            if (tid < 32) {
+                if (tid == 0) s_tau = 0u;
+                __syncwarp();
+                if (nw >= K && tid < nw) {
+                    const unsigned m2 = s_wmax[tid];
                     int before = 0;
-                    for (int w3 = 0; w3 < nw; w3++) before += s_wmax[w3] > m2 || (s_wmax[w3] == m2 && w3 < w2);
-                    if (before == K - 1) tau = m2;
+                    for (int w3 = 0; w3 < nw; w3++) before += s_wmax[w3] > m2 || (s_wmax[w3] == m2 && w3 < tid);
+                    if (before == K - 1) s_tau = m2;
                 }
             }
+            __syncthreads();
+            const unsigned tau = s_tau;
             const bool cand = tid < E && key >= tau;
             const unsigned mask = __ballot_sync(0xffffffffu, cand);
             if (lane == 0) s_wcnt[warp] = __popc(mask);
@@ -386,13 +392,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             if (lane < K && a.w_out) a.w_out[(size_t)l * K + lane] = s_w[lane];
         }
         // ---- P3: gate/up. All copies this layer needs that fit the ring are requested now, the down slices included ----
+        // Only the gate/up slices are requested now: the down slices are not needed before the next grid barrier, and asked for
+        // together with the others they would take a third of the HBM bandwidth that P3 is waiting on. They are requested as the
+        // warp's gate/up passes complete (below), and land while the grid waits at the barrier.
         issued = 0; consumed = 0;
         if (lane == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the buffers were read by the warp in the layer before
-            for (; issued < nS && issued < DS_D; issued++) issue(issued);
-            if (warp == 0) issue_shared(0);
+            for (; issued < n3 && issued < DS_D; issued++) issue(issued);
         }
-        sh_inflight = worker && b < U4;
         issued = __shfl_sync(0xffffffffu, issued, 0);
         if (l + 1 < a.n_layers) stage_layer(l + 1);   // lands while the experts stream; waited for at the end of the layer
         for (int pass = 0; pass < n3 && ok; pass++) {
@@ -406,6 +413,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stack_k(const DecodeStac
             __syncwarp();
             if (lane == 0 && issued < nS) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue(issued); }
             if (issued < nS) issued++;
+            if (pass == 0) {   // the shared expert's down slice of this CTA's row tile: behind the first gate/up pass as well
+                if (tid == 0) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); issue_shared(0); }
+                sh_inflight = worker && b < U4;
+            }
             if (t == 0 && u < U3) {
                 float* p = part + (((warp >> 2) * 4 + (warp & 3)) * 16 + g) * 2;
                 p[0] = acc[0] + acc[1]; p[1] = acc[2] + acc[3];

@@ -1048,7 +1048,7 @@ static int prefill_launch_one(moexb_ctx* c, const PrefillArgs& a, void* stream) 
     const cudaError_t attr_err = once.run([] { return cudaFuncSetAttribute(prefill_k<FMT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); });
     if (attr_err != cudaSuccess) return fail(MOEXB_ERR_CUDA, "prefill kernel shared memory: %s", cudaGetErrorString(attr_err));
     PROF(c, DOWN ? MOEXB_PROF_DOWN : MOEXB_PROF_GATE_UP, stream);
-    prefill_k<FMT, DOWN><<<2 * c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
+    prefill_k<FMT, DOWN><<<c->sms, PF_THREADS, SMEM, S(stream)>>>(a);
     LAUNCHED(DOWN ? "prefill_down" : "prefill_gate_up");
     return MOEXB_OK;
 }

@@ -1,25 +1,22 @@
 // Grouped expert GEMM for prefill-size batches on the 5th-generation tensor cores (tcgen05.mma, weights and accumulators
 // in tensor memory).
 //
-// One CTA of 256 threads owns a 128-row weight block of one expert (64 gate rows and the same 64 up rows, interleaved in
-// groups of 8 as the tiled image stores them; or 128 consecutive down rows) and one tile of up to 128 activation columns
-// (tokens of that expert, as fp16: one column per token when the input is exactly bf16, hi + lo columns when it is fp32).
-// TWO such CTAs share an SM (256 tensor-memory columns and about 85 KB of shared memory each): each of them alternates
-// between unpacking a group and waiting for its MMAs behind one CTA barrier per group, and the two run out of phase by
-// themselves, so one CTA's unpacking fills the issue slots while the other's MMAs fill the tensor pipe. Per 64-input
-// scale group:
+// One CTA of 512 threads owns a 256-row weight block of one expert (gate rows r..r+127 and the same up rows; or 256
+// consecutive down rows) and one tile of up to 128 activation columns (tokens of that expert, as fp16: one column per
+// token when the input is exactly bf16, hi + lo columns when it is fp32). Per 64-input scale group:
 //   1. every thread takes 32 weights of one row (16 bytes of the tiled weight image, requested several groups earlier
 //      with cp.async into a ring in shared memory), unpacks them to exact fp16 integers, multiplies by the group's fp16
 //      scale and splits the product into hi = fp16(q*s) and lo = q*s - hi (one fused multiply-add; both halves together
 //      are the exact weight), and writes them with tcgen05.st into tensor memory, where a thread's TMEM lane is its
 //      weight row - the A operand never passes through shared memory; the group's activation rows (B operand) arrive in
 //      shared memory with cp.async;
-//   2. one thread issues 8 tcgen05.mma (M = 128, N = columns, K = 16, A from tensor memory; hi and lo weights x four K
-//      steps) that accumulate over all groups in TMEM, and commits them to an mbarrier, which frees the stage.
+//   2. one thread issues 16 tcgen05.mma (M = 128, N = columns, K = 16, A from tensor memory; hi and lo weights x two
+//      weight halves x four K steps) that accumulate over all groups in TMEM, and commits them to an mbarrier, which
+//      frees the stage.
 // The unpacking of group G+1 runs while the tensor core works on group G. After the last group every thread reads its
 // row's sums out of TMEM (tcgen05.ld) for the epilogue. Every mbarrier wait is bounded; on a time-out the CTA still
-// frees its TMEM and leaves. Tensor memory (256 columns per CTA): columns 0-127 the accumulator, 128-255 two stages of A
-// (per stage: (hi, lo) x 32 columns = 64 inputs, two fp16 per column).
+// frees its TMEM and leaves. Tensor memory: columns 0-255 the two accumulators (128 columns each), 256-511 two stages of
+// A (per stage: weight half x (hi, lo) x 32 columns = 64 inputs, two fp16 per column).
 //
 // Inputs are permuted inside every block of 8: position 8b + j holds input 8b + p(j), p = (0,4,1,5,2,6,3,7) - the order in
 // which the unpacking produces weights - for the activations as well, so no shuffling is needed at run time.
@@ -30,7 +27,7 @@
 
 namespace moexb {
 
-constexpr int PF_THREADS = 256;
+constexpr int PF_THREADS = 512;
 constexpr int PF_NMAX = 128;            // activation columns per tile (MMA N)
 constexpr int PF_B_STAGE = PF_NMAX * 128;
 
@@ -96,22 +93,20 @@ struct PrefillArgs {
 
 constexpr int PF_RING = 8;      // raw weight groups in flight (cp.async), each 8 KB of nibbles + the group's scales
 constexpr int PF_AHEAD = 6;     // a group's raw bytes are requested this many groups before they are unpacked (2 <= AHEAD < RING)
-constexpr int PF_ROWS = 128;            // weight rows of a CTA = TMEM lanes = MMA M
-constexpr int PF_RAW = PF_ROWS * 32 + 256;  // bytes of one ring slot: [slice 8][row 16][32 bytes = 64 nibbles] | [slice 8][row pair 8] x (fp16, fp16)
-constexpr int PF_TMEM_COLS = 256;
-constexpr int PF_TMEM_A = 128;  // first column of the A stages
+constexpr int PF_RAW = 256 * 32 + 512;  // bytes of one ring slot: [slice 16][row 16][32 bytes = 64 nibbles] | [slice 16][row pair 8] x (fp16, fp16)
+constexpr int PF_TMEM_COLS = 512;
+constexpr int PF_TMEM_A = 256;  // first column of the A stages
 
-// DOWN = false: weight block = 8 slices of 8 gate + 8 up rows: gate rows 64*rt..+63 and the same up rows; TMEM lane 16j + m is
-//               gate row 64*rt + 8j + m (m < 8) or up row 64*rt + 8j + m - 8 (m >= 8); K = 2048 = 32 groups.
-// DOWN = true : weight block = down rows 128*rt..+127 (8 slices of 16 rows); K = 512 = 8 groups; parts = 2.
-// Two CTAs per SM (256 TMEM columns each).
+// DOWN = false: weight block = gate rows 128*rt..+127 (half 0) and the same up rows (half 1); K = 2048 = 32 groups.
+// DOWN = true : weight block = down rows 256*rt..+127 (half 0) and +128..+255 (half 1); K = 512 = 8 groups; parts = 2.
+// One CTA per SM (the launch asks for more than half of the shared memory, and the CTA takes all 512 TMEM columns).
 template <int FMT, bool DOWN>
-__global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) {
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) {
     static_assert(FMT == FMT_SYM_F16, "the grouped GEMM takes fp16 group scales; other formats use the streaming kernels");
     static_assert(PF_AHEAD >= 2 && PF_AHEAD < PF_RING, "ring depth");
     constexpr int GB = tl_group_bytes<FMT>(), SB = tl_slice_bytes<FMT>();
     constexpr int NG = DOWN ? EI / 64 : EH / 64;   // scale groups along K
-    constexpr int RT = DOWN ? EH / PF_ROWS : EI / (PF_ROWS / 2); // row blocks per expert
+    constexpr int RT = DOWN ? EH / 256 : EI / 128; // row blocks per expert
     constexpr int KB = DOWN ? EI : EH;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sB = smem;                                 // 3 stages x [k-block 8][column N][16 B]
@@ -120,7 +115,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 2);
     int* s_fail = reinterpret_cast<int*>(s_tmem + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) { mbar_init(smem_u32(bars), 1); mbar_init(smem_u32(bars + 1), 1); *s_fail = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    if (tid == 0) { mbar_init(smem_u32(bars), 2); mbar_init(smem_u32(bars + 1), 2); *s_fail = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "n"(PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -130,15 +125,15 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
 
-    // copy role: slice cj of the 8 in the block, 16-byte unit cl = 4*g + t of the slice's group = 8 bytes of row g (inputs
+    // copy role: slice cj of the 16 in the block, 16-byte unit cl = 4*g + t of the slice's group = 8 bytes of row g (inputs
     // 16t..16t+15 of the group) and 8 bytes of row g + 8
     const int cj = tid >> 5, cg = (tid & 31) >> 2, ct = tid & 3;
-    // unpack role: a warp reaches only the TMEM lanes 32*(warp & 3)..+31, lane = weight row of the block; the two warps of
-    // a lane quarter split the two 32-input halves of the group
-    const int uq = warp & 3, ukh = warp >> 2, ui = 32 * uq + lane;
-    const int uj = ui >> 4, um = ui & 15;   // slice and row of the slice
+    // unpack role: a warp reaches only the TMEM lanes 32*(warp & 3)..+31, lane = weight row inside its half; the four
+    // warps of a lane quarter split the two weight halves and the two 32-input halves of the group
+    const int uq = warp & 3, uh = warp >> 3, ukh = (warp >> 2) & 1, ui = 32 * uq + lane;
+    const int uj = DOWN ? 8 * uh + (ui >> 4) : ui >> 3, um = DOWN ? ui & 15 : (ui & 7) + 8 * uh;   // slice and row of the slice
     const uint32_t lane_base = (uint32_t)(32 * uq) << 16;
-    // epilogue role: row ui, column half ecq
+    // epilogue role: row ui of both halves, column quarter ecq
     const int ecq = warp >> 2;
     uint32_t ph0 = 0, ph1 = 0;
     pdl_wait();
@@ -155,43 +150,44 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
         // activation rows of this tile's columns: copy unit u = (column c, k-block kb of 8 inputs), N*8 units, threads take
         // u = tid and tid + 512. kb = (u & 1) + 2 * ((u >> 1) / N), c = (u >> 1) % N: a lane pair reads one 32-byte sector of a
         // column, consecutive pairs write consecutive 16-byte rows of the core-matrix layout.
-        constexpr int UPT = PF_NMAX * 8 / PF_THREADS;   // copy units per thread
-        const uint16_t* xcol[UPT];
-        int dofs[UPT];  // byte offsets inside a B stage, -1 = no unit
-#pragma unroll
-        for (int i = 0; i < UPT; i++) {
-            const int u = tid + i * PF_THREADS;
-            xcol[i] = nullptr; dofs[i] = -1;
-            if (u < N * 8) {
-                const int c = (u >> 1) % N, kb = (u & 1) + 2 * ((u >> 1) / N);
-                dofs[i] = kb * (N * 16) + c * 16;
-                if (c < ncol) { const moexb_pair pr = a.pairs[it.start + c / a.parts]; xcol[i] = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
+        const uint16_t* xcol0 = nullptr; const uint16_t* xcol1 = nullptr;
+        int d0 = -1, d1 = -1;  // byte offsets inside a B stage
+        {
+            const int u0 = tid, u1 = tid + PF_THREADS;
+            if (u0 < N * 8) {
+                const int c = (u0 >> 1) % N, kb = (u0 & 1) + 2 * ((u0 >> 1) / N);
+                d0 = kb * (N * 16) + c * 16;
+                if (c < ncol) { const moexb_pair pr = a.pairs[it.start + c / a.parts]; xcol0 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
+            }
+            if (u1 < N * 8) {
+                const int c = (u1 >> 1) % N, kb = (u1 & 1) + 2 * ((u1 >> 1) / N);
+                d1 = kb * (N * 16) + c * 16;
+                if (c < ncol) { const moexb_pair pr = a.pairs[it.start + c / a.parts]; xcol1 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
             }
         }
 
         // request group G's raw bytes: the thread's unit as two 8-byte pieces, each to its row's 32 bytes of the ring slot
         // (so that the unpacking reads one row with one 16-byte load), and (one thread per row pair) the pair's two scales
         auto prefetch = [&](int G) {
-            const uint8_t* gb = blob + (size_t)(DOWN ? 256 + 8 * rt + cj : (8 * rt + cj) * 4 + (G >> 3)) * SB + (G & 7) * GB;
+            const uint8_t* gb = blob + (size_t)(DOWN ? 256 + 16 * rt + cj : (16 * rt + cj) * 4 + (G >> 3)) * SB + (G & 7) * GB;
             uint8_t* slot = sR + (G % PF_RING) * PF_RAW;
             const uint8_t* src = gb + (4 * cg + ct) * 16;
             cp_async8(smem_u32(slot + (cj * 16 + cg) * 32 + ct * 8), src);
             cp_async8(smem_u32(slot + (cj * 16 + cg + 8) * 32 + ct * 8), src + 8);
-            if (ct == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slot + PF_ROWS * 32 + (cj * 8 + cg) * 4)), "l"(gb + 512 + 4 * cg) : "memory");
+            if (ct == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slot + 8192 + (cj * 8 + cg) * 4)), "l"(gb + 512 + 4 * cg) : "memory");
         };
         // request group G's activation rows into B stage G % 3
         auto fill_b = [&](int G) {
             uint8_t* bb = sB + (G % 3) * PF_B_STAGE;
-#pragma unroll
-            for (int i = 0; i < UPT; i++)
-                if (dofs[i] >= 0) { if (xcol[i]) cp_async16(smem_u32(bb + dofs[i]), xcol[i] + G * 64); else *reinterpret_cast<uint4*>(bb + dofs[i]) = make_uint4(0, 0, 0, 0); }
+            if (d0 >= 0) { if (xcol0) cp_async16(smem_u32(bb + d0), xcol0 + G * 64); else *reinterpret_cast<uint4*>(bb + d0) = make_uint4(0, 0, 0, 0); }
+            if (d1 >= 0) { if (xcol1) cp_async16(smem_u32(bb + d1), xcol1 + G * 64); else *reinterpret_cast<uint4*>(bb + d1) = make_uint4(0, 0, 0, 0); }
         };
         // unpack 32 weights of this thread's row of group G (the raw bytes have landed and are visible) into A stage G & 1 in
         // tensor memory: nh = -fp16(q*s) (the MMA negates it back) and lo = q*s + nh, two fp16 per column
         auto unpack = [&](int G) {
             const uint8_t* slot = sR + (G % PF_RING) * PF_RAW;
             const uint4 q = *reinterpret_cast<const uint4*>(slot + (uj * 16 + um) * 32 + ukh * 16);
-            const uint32_t s1 = *reinterpret_cast<const uint16_t*>(slot + PF_ROWS * 32 + (uj * 8 + (um & 7)) * 4 + 2 * (um >> 3));
+            const uint32_t s1 = *reinterpret_cast<const uint16_t*>(slot + 8192 + (uj * 8 + (um & 7)) * 4 + 2 * (um >> 3));
             const uint32_t s2 = s1 | (s1 << 16), ns2 = s2 ^ 0x80008000u;
             uint32_t nh[16], lo[16];
             auto put = [&](uint32_t word, int at) {
@@ -204,19 +200,20 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
                 }
             };
             put(q.x, 0); put(q.y, 4); put(q.z, 8); put(q.w, 12);
-            const uint32_t col = (uint32_t)(PF_TMEM_A + (G & 1) * 64 + ukh * 16);
+            const uint32_t col = (uint32_t)(PF_TMEM_A + (G & 1) * 128 + uh * 64 + ukh * 16);
             tmem_st16(tmem + lane_base + col, nh);
             tmem_st16(tmem + lane_base + col + 32, lo);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         };
-        // issue the 8 MMAs of group G (one thread): D += (-A_nh + A_lo) * B over the four K steps
-        auto issue = [&](int G) {
-            const uint32_t aT = tmem + (uint32_t)(PF_TMEM_A + (G & 1) * 64), bB = smem_u32(sB + (G % 3) * PF_B_STAGE);
+        // issue the 8 MMAs of weight half h of group G (one thread per half - issuing an MMA costs its thread about 90 cycles
+        // whatever N is, so the two halves are issued from two warps): D[h] += (-A_nh + A_lo)[h] * B over the four K steps
+        auto issue = [&](int G, int h) {
+            const uint32_t aT = tmem + (uint32_t)(PF_TMEM_A + (G & 1) * 128), bB = smem_u32(sB + (G % 3) * PF_B_STAGE);
 #pragma unroll
             for (int hl = 0; hl < 2; hl++)
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
-                    umma_f16_ts(tmem, aT + (uint32_t)(hl * 32 + ks * 8),
+                    umma_f16_ts(tmem + (uint32_t)(h * PF_NMAX), aT + (uint32_t)(h * 64 + hl * 32 + ks * 8),
                                 umma_desc(bB + ks * 2 * (N * 16), N * 16, 128), hl ? idesc : (idesc | UMMA_NEGATE_A), G > 0 || hl > 0 || ks > 0);
             umma_commit(smem_u32(bars + (G & 1)));
         };
@@ -238,7 +235,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
         unpack(0);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        if (tid == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(0); }
+        if ((tid & ~32) == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(0, tid >> 5); }
         for (int G = 0; G < NG; G++) {
             // group G is on the tensor core. Meanwhile: unpack group G+1 (visible since the previous barrier), request what
             // comes later, and make sure that everything requested before this iteration has landed before the next barrier.
@@ -253,25 +250,22 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             if (*s_fail) break;
-            if (G + 1 < NG && tid == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(G + 1); }
+            if (G + 1 < NG && (tid & ~32) == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(G + 1, tid >> 5); }
         }
         if (*s_fail) break;
         wait_mma(NG - 1);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-        // epilogue. The thread reads row ui, columns ecq*N/2 .. +N/2-1, 8 at a time. Gate/up: lanes L (a gate row) and L ^ 8 (the up
-        // row of the same index) exchange their sums, and the gate lane finishes SiLU(gate) * up and stores.
-        const int cbase = ecq * (N >> 1);
+        // epilogue. The thread reads row ui of both halves, columns ecq*N/4 .. +N/4-1, 8 at a time.
+        const int cbase = ecq * (N >> 2);
         const uint32_t t0 = tmem + lane_base + (uint32_t)cbase;
         const bool two = a.parts == 2;
 #pragma unroll
-        for (int cb = 0; cb < PF_NMAX / 16; cb++) {
-            if (cb * 8 < (N >> 1)) {
+        for (int cb = 0; cb < 4; cb++) {
+            if (cb * 8 < (N >> 2)) {
                 float v0[8], v1[8];
                 tmem_ld8(t0 + cb * 8, v0);
-#pragma unroll
-                for (int i = 0; i < 8; i++) v1[i] = DOWN ? 0.f : __shfl_xor_sync(0xffffffffu, v0[i], 8);
-                if (!DOWN && um >= 8) continue;   // up rows: their sums went to the gate lanes
+                tmem_ld8(t0 + PF_NMAX + cb * 8, v1);
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const int col = cbase + cb * 8 + i;
@@ -281,9 +275,11 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
                     if (DOWN || two) { x0 += v0[i | 1]; x1 += v1[i | 1]; }   // columns (2j, 2j+1) = (hi, lo) of pair j
                     const moexb_pair pr = a.pairs[it.start + j];
                     if (DOWN) {
-                        a.ypair[(size_t)pr.p * EH + PF_ROWS * rt + ui] = pr.w * x0;
+                        const int d = 256 * rt + ui;
+                        a.ypair[(size_t)pr.p * EH + d] = pr.w * x0;
+                        a.ypair[(size_t)pr.p * EH + d + 128] = pr.w * x1;
                     } else {
-                        const int row = (PF_ROWS / 2) * rt + 8 * uj + um;
+                        const int row = 128 * rt + ui;
                         const float val = x0 / (1.f + expf(-x0)) * x1;
                         if (a.act32) a.act32[(size_t)pr.p * EI + row] = val;
                         uint16_t hi, lo;
@@ -303,7 +299,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) prefill_k(const PrefillArgs a) 
 
 template <int FMT, bool DOWN>
 constexpr int pf_smem_bytes() { return 3 * PF_B_STAGE + PF_RING * PF_RAW + 64 + 1024; }
-static_assert(2 * pf_smem_bytes<FMT_SYM_F16, false>() + 2048 <= 227 * 1024, "two CTAs (256 TMEM columns each) share an SM");
+static_assert(pf_smem_bytes<FMT_SYM_F16, false>() > 114 * 1024, "more than half of an SM's shared memory, so that two CTAs (2 x 512 TMEM columns) never share an SM");
 
 // x [rows][K] fp32 -> xs [rows][parts][K] fp16 in perm8 order: parts = 1 keeps fp16(x) (exact when x came from bf16 and is
 // in fp16's normal range), parts = 2 adds lo = fp16(x - hi).
