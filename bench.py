@@ -511,6 +511,54 @@ def independent_inputs(env, ctx, layers, T, eb):
             "whole_layer_frac": layer_bytes / (ms * 1e-3 / NL) / 1e9 / hbm_peak}
 
 
+def emulate_ranks(args):
+    """The expert-parallel step with all ranks on ONE GPU (for profiling its kernels with a single-GPU tool): R contexts whose
+    exchange buffers are each other's peers; the phases of a step are enqueued rank after rank, so that every flag a kernel
+    waits for has been raised. Prints one JSON line with the step time of that serialised execution (not a throughput)."""
+    import torch
+    import moe_b200 as m
+    from moe_b200 import ep
+    R = args.emulate_ranks
+    T, NL, fmtname, xdt, _ = WORKLOADS[args.workload]
+    fmt = m.FMT_ZP if fmtname == "zp" else m.FMT_SYM_F16
+    ctxs, layers, bufs, eps = [], [], [], []
+    for r in range(R):
+        c = m.Context(0, max_tokens=max(T, 64), max_experts=E, top_k=K)
+        first, count = ep.expert_range(E, r, R)
+        ls = []
+        for l in range(NL):
+            L = m.Layer(c, fmt, E, first_local=first, n_local=count)
+            L.fill_synth(SEED, l); L.set_router(router_weights(l))
+            ls.append(L)
+        ctxs.append(c); layers.append(ls); bufs.append(m.ExchangeBuffer(T, K, R))
+    for r in range(R):
+        eps.append(m.EP(ctxs[r], r, R, T, K, E, [b.ptr for b in bufs]))
+    X = torch.from_numpy(tokens(T, 0)).to(torch.bfloat16 if xdt == "bf16" else torch.float32).cuda()
+    outs = [torch.zeros(e.n_own, EH, device="cuda") for e in eps]
+    residual = NL > 1
+
+    def step():
+        for e in eps:
+            e.begin_step()
+        for l in range(NL):
+            for r, e in enumerate(eps):
+                e.dispatch(layers[r][l], l, X if l == 0 else None, residual)
+            for r, e in enumerate(eps):
+                e.experts(layers[r][l], l)
+        for r, e in enumerate(eps):
+            e.finish(NL, outs[r], residual)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    print(json.dumps({"emulated_ranks": R, "workload": args.workload, "layers": NL, "ms_per_serialised_step": ms,
+                      "status": [c.status() for c in ctxs], "finite": bool(all(torch.isfinite(o).all() for o in outs))}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -522,6 +570,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--pairs-per-pass", type=int, default=8, choices=[4, 8], help="sub-item width of the streaming kernels")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (small profiling cases)")
+    ap.add_argument("--emulate-ranks", type=int, default=0, help="run the expert-parallel step with this many ranks emulated on one GPU (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.layers > 0:
@@ -529,6 +578,8 @@ def main():
         WORKLOADS[args.workload] = (T_, args.layers, f_, x_, c_)
     if args.impl == "reference":
         return run_reference(args)
+    if args.emulate_ranks > 1:
+        return emulate_ranks(args)
 
     env = Env(args)
     torch = env.torch

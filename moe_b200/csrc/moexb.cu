@@ -1173,7 +1173,9 @@ static int route_launch(moexb_ctx* c, moexb_layer* L, const float* xf, int T, in
               decode ? c->subs : nullptr, decode ? c->pairs : nullptr, decode ? c->nsub : nullptr};
     if (rep) { o.ep = rep->dev; o.ep_row_bytes = rep->row_bytes; o.ep_phase = rep->phase; o.ep_step = rep->step; }
     auto run = [&]<int NJ>() -> int {
-        if (T < 8) {
+        // expert parallelism with few own tokens: one token per block row, so that each token's selection and dispatch stores are
+        // done by a block of their own instead of one block sending a whole tile of 8
+        if (T < 8 || (rep && T <= 16)) {
             constexpr int WARPS = 8;
             CUDA_TRY(launch_dep(route_gemv_k<WT, WARPS, NJ>, dim3((E + 1 + WARPS - 1) / WARPS, T), WARPS * 32, 0, S(stream), W, xf, logits, EH, E, K, 1, c->route_done, o));
         } else {
