@@ -47,7 +47,7 @@ WORKLOADS = {
 SEED = 0
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the roofline kernel, from the ncu captures
 # summarised under profiles/ (gate/up kernel on a 2-layer case of serve64; the one-token stack kernel; the grouped GEMM)
-TRAFFIC_RATIO = {"serve64": 1.015, "decode1": 1.003, "prefill2048": 1.07}
+TRAFFIC_RATIO = {"serve64": 1.01, "decode1": 1.015, "prefill2048": 1.105}
 
 
 def router_weights(layer):
