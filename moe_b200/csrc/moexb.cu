@@ -1019,9 +1019,11 @@ static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* strea
 static int tiled_maxp(const moexb_ctx* c, int fmt, int T) { return (T >= 8 && fmt != FMT_ZP) ? c->pairs_per_pass : 4; }
 // Whether the gate/up kernel can make the work list of this batch itself (tiled.cuh: plan_in_cta).
 // (fp16-scale format: with the wider slices of the other formats the list does not fit beside two CTAs' rings.)
-static bool plan_in_kernel(const moexb_ctx* c, int fmt, int T, int K, int E) {
+// With a handful of tokens (2-7) the one-block planning launch is the cheaper of the two on one GPU (measured on the 4-token
+// workload); across GPUs the in-kernel list always wins, because the planning launch would sit behind the wait for the peers.
+static bool plan_in_kernel(const moexb_ctx* c, int fmt, int T, int K, int E, bool ep = false) {
     static const bool on = [] { const char* e = getenv("MOEXB_PLAN_IN_KERNEL"); return !(e && e[0] == '0'); }();
-    return on && fmt == FMT_SYM_F16 && T <= PL_MAX_TOKENS && K <= PL_MAX_K && E <= PL_MAX_E;
+    return on && fmt == FMT_SYM_F16 && (T >= 8 || ep) && T <= PL_MAX_TOKENS && K <= PL_MAX_K && E <= PL_MAX_E;
 }
 
 // The same on blobs in the tiled layout (sub-item slots point into a tiled layer image). plan: null = the list is already
@@ -1724,7 +1726,7 @@ int moexb_ep_experts(moexb_ep* e, moexb_layer* L, int l, void* stream) {
     const bool tiled = L->layout == MOEXB_LAYOUT_TILED, prefill = e->prefill;
     const int maxp = prefill ? PF_NMAX / e->parts : (tiled ? tiled_maxp(c, L->fmt, T) : ST_MAXP);
     const unsigned* flags = reinterpret_cast<const unsigned*>(e->peers.base[e->g.rank] + e->lay.flag_a);
-    const bool in_kernel = tiled && !prefill && plan_in_kernel(c, L->fmt, T, K, E);
+    const bool in_kernel = tiled && !prefill && plan_in_kernel(c, L->fmt, T, K, E, true);
     // the dispatch flags of all tokens are waited for by whoever makes the work list: the gate/up CTAs, or the planning kernel
     const PlanArgs plan{c->idx, c->w, T, K, E, L->slot_table, L->first_local, L->first_local + L->n_local, c->logits + E, E + 1, t0, t1, maxp, c->subs, c->pairs, c->nsub, flags, e->step, (unsigned)(l + 1)};
     if (!in_kernel) {
