@@ -97,10 +97,11 @@ struct PlanArgs {
     moexb_pair_item* subs_out; moexb_pair* pairs_out; int* nsub_out;   // the list in global memory (written by CTA 0)
     const unsigned* ep_flags; const unsigned* ep_step; unsigned ep_phase;   // expert parallelism: per-token dispatch flags to wait for, or null
 };
-// The list as the CTA keeps it (8 KB): a sub-item as (expert id, first pair, pairs), a pair as (p, weight) with the token
+// The list as the CTA keeps it (10 KB): a sub-item as (expert id, first pair, pairs), a pair as (p, weight) with the token
 // derived from p (routed pairs p = t * K + rank, the shared expert's p = T * K + t).
 struct PlanSub { uint16_t e, start, count, pad; };
 struct PlanSmem {
+    const uint8_t* slot[PL_MAX_E + 1];   // the layer's blob pointers (copied before the wait for the kernel before this one)
     PlanSub subs[PL_MAX_SUBS];
     uint2 pairs[PL_MAX_PAIRS + PL_MAX_TOKENS];
     int nsub[2], npairs, n, K;
@@ -117,17 +118,27 @@ struct PlanTmp {
     int np, nw, nn;
 };
 
+// What does not depend on the router: cleared tables and the layer's blob pointers. Runs before the wait for the kernel
+// before this one; a CTA barrier must follow before plan_in_cta.
+__device__ __forceinline__ void plan_prepare(PlanSmem& L, PlanTmp& P, const PlanArgs& a) {
+    const int tid = threadIdx.x, NT = blockDim.x;
+    for (int i = tid; i < PL_MAX_E; i += NT) P.cnt[i] = 0;
+    for (int i = tid; i < (int)sizeof(P.chunk) / 4; i += NT) reinterpret_cast<uint32_t*>(P.chunk)[i] = 0;
+    for (int i = tid; i <= a.E; i += NT) L.slot[i] = a.slot_table[i];
+}
+
 __device__ __forceinline__ void plan_in_cta(PlanSmem& L, PlanTmp& P, const PlanArgs& a, int* err) {
     const int tid = threadIdx.x, NT = blockDim.x, lane = tid & 31;
-    const int n = a.T * a.K, E = a.E, maxp = a.maxp;
+    const int n = a.T * a.K, E = a.E, maxp = a.maxp, lgp = __ffs(maxp) - 1;   // maxp is 4 or 8
     if (a.ep_flags) {
         const unsigned target = *a.ep_step * EP_PHASES + a.ep_phase;
         for (int t = tid; t < a.T; t += NT)
             if (t < a.sh0 || t >= a.sh1) ep_wait_flag(a.ep_flags + t, target, err, EP_ERR_DISPATCH_WAIT);
+        __syncthreads();   // the peers' ids are read by other threads than the ones that saw the flags
     }
-    for (int i = tid; i < PL_MAX_E; i += NT) P.cnt[i] = 0;
-    for (int i = tid; i < (int)sizeof(P.chunk) / 4; i += NT) reinterpret_cast<uint32_t*>(P.chunk)[i] = 0;
-    __syncthreads();
+    // the shared expert's gate logits: requested now, used when the list is written
+    const int Ts = (a.gate_logits && L.slot[E] && a.sh1 > a.sh0) ? a.sh1 - a.sh0 : 0;
+    const float gl = tid < Ts ? __ldcg(a.gate_logits + (size_t)(a.sh0 + tid) * a.gl_stride) : 0.f;
     constexpr int MAXPT = PL_MAX_PAIRS / 128;   // pairs per thread with the smallest CTA (4 warps)
     int ex[MAXPT], rk[MAXPT];
     float wv[MAXPT];
@@ -152,8 +163,8 @@ __device__ __forceinline__ void plan_in_cta(PlanSmem& L, PlanTmp& P, const PlanA
         P.cnt[e] = c;
     }
     __syncthreads();
-    auto wide = [maxp](int c) { return c / maxp + (c % maxp > maxp / 2); };
-    auto narrow = [maxp](int c) { return (int)(c % maxp > 0 && c % maxp <= maxp / 2); };
+    auto wide = [maxp, lgp](int c) { return (c >> lgp) + ((c & (maxp - 1)) > maxp / 2); };
+    auto narrow = [maxp](int c) { return (int)((c & (maxp - 1)) > 0 && (c & (maxp - 1)) <= maxp / 2); };
     if (tid < 32) {   // exclusive scans over the experts: pairs, wide sub-items, narrow sub-items; a lane takes 8 experts
         int c[8], sp = 0, sw = 0, sn = 0;
 #pragma unroll
@@ -174,8 +185,6 @@ __device__ __forceinline__ void plan_in_cta(PlanSmem& L, PlanTmp& P, const PlanA
         }
     }
     __syncthreads();
-    const uint8_t* sslot = a.slot_table[E];
-    const int Ts = (a.gate_logits && sslot && a.sh1 > a.sh0) ? a.sh1 - a.sh0 : 0;
     const int np = P.np, nw = P.nw, nn = P.nn, all_wide = nw + wide(Ts);
     for (int e = tid; e < E; e += NT) {
         const int c = P.cnt[e];
@@ -192,10 +201,7 @@ __device__ __forceinline__ void plan_in_cta(PlanSmem& L, PlanTmp& P, const PlanA
         }
     if (Ts) {
         const int cw = wide(Ts), ns = all_wide + nn;
-        for (int t = tid; t < Ts; t += NT) {
-            const float gl = a.gate_logits[(size_t)(a.sh0 + t) * a.gl_stride];
-            L.pairs[np + t] = make_uint2((unsigned)(n + a.sh0 + t), __float_as_uint(1.f / (1.f + expf(-gl))));
-        }
+        if (tid < Ts) L.pairs[np + tid] = make_uint2((unsigned)(n + a.sh0 + tid), __float_as_uint(1.f / (1.f + expf(-gl))));   // Ts <= PL_MAX_TOKENS <= NT
         for (int j = tid; j * maxp < Ts; j += NT)
             L.subs[j < cw ? nw + j : ns] = {(uint16_t)E, (uint16_t)(np + j * maxp), (uint16_t)min(maxp, Ts - j * maxp), 0};
     }
@@ -246,6 +252,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x < NW * D) mbar_init(smem_u32(bars + threadIdx.x), 1);
     if (threadIdx.x == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if constexpr (PLAN) plan_prepare(P, *reinterpret_cast<PlanTmp*>(smem), pa);
     __syncthreads();
     // Gate/up: the sub-items come from the kernel before this one. Down: they are older (the gate/up kernel read them
     // too), so the weight copies start while gate/up still runs; only the activation columns wait for it.
@@ -256,7 +263,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
         plan_in_cta(P, *reinterpret_cast<PlanTmp*>(smem), pa, a.err);
         if (blockIdx.x == 0) {
             // the list for the kernels that follow; the down kernel may read it as soon as every CTA here has triggered
-            for (int i = threadIdx.x; i < P.nsub[0]; i += NW * 32) { const PlanSub su = P.subs[i]; pa.subs_out[i] = {pa.slot_table[su.e], su.start, su.count}; }
+            for (int i = threadIdx.x; i < P.nsub[0]; i += NW * 32) { const PlanSub su = P.subs[i]; pa.subs_out[i] = {P.slot[su.e], su.start, su.count}; }
             for (int i = threadIdx.x; i < P.npairs; i += NW * 32) pa.pairs_out[i] = P.pair_at(i);
             if (threadIdx.x < 2) pa.nsub_out[threadIdx.x] = P.nsub[threadIdx.x];
             __threadfence();
@@ -268,7 +275,7 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
     } else if (!DOWN) { pdl_wait(); pdl_trigger(); }
     // the work list: the CTA's own (PLAN) or the one in global memory
     auto sub_at = [&](int i) -> moexb_pair_item {
-        if constexpr (PLAN) { const PlanSub su = P.subs[i]; return {pa.slot_table[su.e], su.start, su.count}; }
+        if constexpr (PLAN) { const PlanSub su = P.subs[i]; return {P.slot[su.e], su.start, su.count}; }
         else return a.subs[i];
     };
     auto pair_at = [&](int i) -> moexb_pair { if constexpr (PLAN) return P.pair_at(i); else return a.pairs[i]; };
@@ -292,6 +299,20 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
         mbar_arrive_expect_tx(bar, SB);
         bulk_g2s(smem_u32(ring + (q % D) * SB), src, SB, bar);
     };
+    // the activation columns of a sub-item: 2 * count columns of KB 16-bit values, requested with 16-byte asynchronous copies
+    auto request_columns = [&](const moexb_pair_item& it) {
+        constexpr int CHUNKS16 = KB * 2 / 16;
+        for (int i = threadIdx.x; i < 2 * it.count * CHUNKS16; i += NW * 32) {
+            const int col = i / CHUNKS16, ch = i % CHUNKS16;
+            const moexb_pair pr = pair_at(it.start + (col >> 1));
+            const size_t row = DOWN ? (size_t)pr.p : (size_t)pr.t;
+            cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (row * 2 + (col & 1)) * KB + ch * 8);
+        }
+    };
+    // Gate/up: the first sub-item's columns are requested before the weight copies (they take longer to set up than to arrive).
+    // Down: the weight copies go out first, before the wait for the gate/up kernel whose output the columns are.
+    bool columns_requested = false;
+    if (!DOWN && Q > 0) { request_columns(sub_at(r0 / RPS)); columns_requested = true; }
     if (lane == 0)
         for (int q = 0; q < D && q < Q; q++) issue(q);
     if (DOWN) { pdl_wait(); pdl_trigger(); }
@@ -307,14 +328,11 @@ __global__ void __launch_bounds__(NW * 32, CPS) stream_tiled_k(const TiledArgs a
             cur_sub = sub;
             const moexb_pair_item it = sub_at(sub);
             n = it.count; start = it.start;
-            __syncthreads();
-            constexpr int CHUNKS16 = KB * 2 / 16;
-            for (int i = threadIdx.x; i < 2 * n * CHUNKS16; i += NW * 32) {
-                const int col = i / CHUNKS16, ch = i % CHUNKS16;
-                const moexb_pair pr = pair_at(start + (col >> 1));
-                const size_t row = DOWN ? (size_t)pr.p : (size_t)pr.t;
-                cp_async16(smem_u32(bsm + col * BCOL + ch * 16), a.xs + (row * 2 + (col & 1)) * KB + ch * 8);
+            if (!columns_requested) {
+                __syncthreads();   // every warp is done with the columns that are about to be overwritten
+                request_columns(it);
             }
+            columns_requested = false;
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncthreads();
             if constexpr (Z) {
