@@ -141,29 +141,46 @@ __device__ __forceinline__ void topk_token(const float* __restrict__ l, int t, i
     const float gate_logit = (o.slots_out && lane == K) ? (CG ? __ldcg(l + E) : l[E]) : 0.f;
 #pragma unroll
     for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    float sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < NJ; j++) if (j < nj) sum += expf(v[j] - m);
-    sum = warp_sum(sum);
     unsigned key[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; j++) key[j] = j < nj ? f2key(v[j]) : 0u;  // 0 = not a candidate (below every real key)
-    float mine = 0.f, total = 0.f;  // lane k keeps the k-th probability
+    // K rounds, each two warp reductions: the largest remaining key, then the lowest index that holds it. Between them a lane
+    // only has to know its own best remaining key, kept by a tree of comparisons that every lane runs without branching (the
+    // lower slot wins among equals). The softmax denominator is summed inside the rounds, where the reductions leave issue
+    // slots free: one term per round, the rest after the last one.
     int mine_i = 0;
-    for (int k = 0; k < K; k++) {
-        unsigned bk = 0; int bj = 0;
+    unsigned mine_key = 0u;
+    unsigned bk; int bj;
+    auto best = [&] {   // (bk, bj) = the lane's largest key and its lowest slot
+        unsigned k2[NJ / 2 > 0 ? NJ / 2 : 1]; int j2[NJ / 2 > 0 ? NJ / 2 : 1];
 #pragma unroll
-        for (int j = 0; j < NJ; j++) if (key[j] > bk) { bk = key[j]; bj = j; }
+        for (int j = 0; j < NJ / 2; j++) { const bool l = key[2 * j] >= key[2 * j + 1]; k2[j] = l ? key[2 * j] : key[2 * j + 1]; j2[j] = l ? 2 * j : 2 * j + 1; }
+#pragma unroll
+        for (int w = NJ / 2; w > 1; w >>= 1)
+#pragma unroll
+            for (int j = 0; j < w / 2; j++) { const bool l = k2[2 * j] >= k2[2 * j + 1]; k2[j] = l ? k2[2 * j] : k2[2 * j + 1]; j2[j] = l ? j2[2 * j] : j2[2 * j + 1]; }
+        bk = k2[0]; bj = j2[0];
+    };
+    best();
+    float sum = 0.f;
+    for (int k = 0; k < K; k++) {
         const unsigned top = __reduce_max_sync(0xffffffffu, bk);
         const unsigned win = __reduce_min_sync(0xffffffffu, bk == top ? (unsigned)(lane + 32 * bj) : 0x7fffffffu);
-        if ((int)(win & 31) == lane) {
+        const bool won = (int)(win & 31) == lane;
 #pragma unroll
-            for (int j = 0; j < NJ; j++) if (j == (int)(win >> 5)) key[j] = 0u;
-        }
-        const float p = expf(key2f(top) - m) / sum;
-        total += p;
-        if (lane == k) { mine = p; mine_i = (int)win; }
+        for (int j = 0; j < NJ; j++) if (won && j == (int)(win >> 5)) key[j] = 0u;
+        best();
+        if (lane == k) { mine_key = top; mine_i = (int)win; }
+#pragma unroll
+        for (int j = 0; j < NJ; j++) if (j == k && j < nj) sum += expf(v[j] - m);
     }
+#pragma unroll
+    for (int j = 0; j < NJ; j++) if (j >= K && j < nj) sum += expf(v[j] - m);
+    sum = warp_sum(sum);
+    // the K probabilities at once, and their sum in selection order
+    float mine = 0.f, total = 0.f;  // lane k keeps the k-th probability
+    if (lane < K) mine = expf(key2f(mine_key) - m) / sum;
+    for (int k = 0; k < K; k++) total += __shfl_sync(0xffffffffu, mine, k);
     if (lane < K) {
         const float wk = norm ? mine / total : mine;
         o.idx[(size_t)t * K + lane] = mine_i;
@@ -305,7 +322,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
                                                            int E, int K, int norm, int T, int* __restrict__ done, const TopkOut o) {
     extern __shared__ __align__(16) float xsm[];  // [TR][I]
     // steps per batch of weights: the small tile takes 8 (half of I = 2048) - the first batch, requested before the wait,
-    // arrives while the kernel before this one still runs
+    // arrives while the kernel before this one still runs (all 16 at once would spill)
     constexpr int U = TO <= 2 ? 8 : 4;
     const int O = E + 1, r0 = blockIdx.y * TR, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int o0 = (blockIdx.x * WARPS + warp) * TO;
@@ -323,10 +340,11 @@ __global__ void __launch_bounds__(WARPS * 32) route_gemm_k(const WT* __restrict_
     load_w(0);  // weights do not depend on the kernel before this one
     pdl_wait();
     pdl_trigger();
-    for (int i = threadIdx.x * 4; i < TR * I; i += WARPS * 128) {
-        const int r = min(r0 + i / I, T - 1);
-        *reinterpret_cast<float4*>(xsm + i) = __ldg(reinterpret_cast<const float4*>(x + (size_t)r * I + i % I));
+    for (int r = 0; r < TR; r++) {   // the tile's token rows: 16-byte asynchronous copies, all in flight at once
+        const float* src = x + (size_t)min(r0 + r, T - 1) * I;
+        for (int c = threadIdx.x * 4; c < I; c += WARPS * 128) cp_async16(smem_u32(xsm + r * I + c), src + c);
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     float acc[TR][TO];
 #pragma unroll

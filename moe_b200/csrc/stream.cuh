@@ -432,15 +432,27 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
         for (int r = 0; r < K; r++) { const int e = idx[t * K + r]; if (e >= e_lo && e < e_hi) have |= 1u << r; }
     }
     float v[8];
+    // both halves of the row in one round trip: the shared expert's row, the residual row and the first eight pair rows of
+    // either half are requested before the first addition
+    float4 ye[2], yx[2], y0[2][8];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int k0 = 1024 * h + 4 * threadIdx.x;
+        ye[h] = yx[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (extra) ye[h] = *reinterpret_cast<const float4*>(extra + t * EH + k0);
+        if (x) yx[h] = *reinterpret_cast<const float4*>(x + t * EH + k0);
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (u < K && (have >> u & 1)) y0[h][u] = *reinterpret_cast<const float4*>(ypair + (t * K + u) * EH + k0);
+    }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int k0 = 1024 * h + 4 * threadIdx.x;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        // the shared expert's row and the residual row are requested with the first batch of pair rows: one round trip
-        float4 ye = make_float4(0.f, 0.f, 0.f, 0.f), yx = ye;
-        if (extra) ye = *reinterpret_cast<const float4*>(extra + t * EH + k0);
-        if (x) yx = *reinterpret_cast<const float4*>(x + t * EH + k0);
-        for (int rb = 0; rb < K; rb += 8) {  // eight rows in flight, added in rank order
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (u < K && (have >> u & 1)) { acc.x += y0[h][u].x; acc.y += y0[h][u].y; acc.z += y0[h][u].z; acc.w += y0[h][u].w; }
+        for (int rb = 8; rb < K; rb += 8) {  // more than eight ranks: eight rows in flight at a time, added in rank order
             float4 y[8];
 #pragma unroll
             for (int u = 0; u < 8; u++)
@@ -449,8 +461,8 @@ __global__ void __launch_bounds__(256) reduce_residual_norm_k(const float* __res
             for (int u = 0; u < 8; u++)
                 if (rb + u < K && (have >> (rb + u) & 1)) { acc.x += y[u].x; acc.y += y[u].y; acc.z += y[u].z; acc.w += y[u].w; }
         }
-        if (extra) { acc.x += ye.x; acc.y += ye.y; acc.z += ye.z; acc.w += ye.w; }
-        if (x) { acc.x = yx.x + acc.x; acc.y = yx.y + acc.y; acc.z = yx.z + acc.z; acc.w = yx.w + acc.w; }
+        if (extra) { acc.x += ye[h].x; acc.y += ye[h].y; acc.z += ye[h].z; acc.w += ye[h].w; }
+        if (x) { acc.x = yx[h].x + acc.x; acc.y = yx[h].y + acc.y; acc.z = yx[h].z + acc.z; acc.w = yx[h].w + acc.w; }
         *reinterpret_cast<float4*>(out + t * EH + k0) = acc;
         v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
     }
