@@ -121,21 +121,27 @@ __global__ void __launch_bounds__(256) ep_combine_norm_k(const EpGeom g, const u
     }
     const float* part = reinterpret_cast<const float*>(local + lay.part);
     float v[8];
+    // both halves of the row in one round trip: every load is requested before the first addition
+    float4 ye[2], yx[2], y[2][EP_MAX_RANKS];
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int k0 = 1024 * h + 4 * threadIdx.x;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), ye = acc, yx = acc;
-        if (extra) ye = *reinterpret_cast<const float4*>(extra + (size_t)t * EH + k0);
-        if (x) yx = *reinterpret_cast<const float4*>(x + (size_t)i * EH + k0);
-        float4 y[EP_MAX_RANKS];
+        ye[h] = yx[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (extra) ye[h] = *reinterpret_cast<const float4*>(extra + (size_t)t * EH + k0);
+        if (x) yx[h] = *reinterpret_cast<const float4*>(x + (size_t)i * EH + k0);
 #pragma unroll
         for (int s = 0; s < EP_MAX_RANKS; s++)
-            if (s < g.world && (need >> s & 1)) y[s] = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)s * g.n_own_max + i) * EH + k0));
+            if (s < g.world && (need >> s & 1)) y[h][s] = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)s * g.n_own_max + i) * EH + k0));
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int k0 = 1024 * h + 4 * threadIdx.x;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int s = 0; s < EP_MAX_RANKS; s++)
-            if (s < g.world && (need >> s & 1)) { acc.x += y[s].x; acc.y += y[s].y; acc.z += y[s].z; acc.w += y[s].w; }
-        if (extra) { acc.x += ye.x; acc.y += ye.y; acc.z += ye.z; acc.w += ye.w; }
-        if (x) { acc.x = yx.x + acc.x; acc.y = yx.y + acc.y; acc.z = yx.z + acc.z; acc.w = yx.w + acc.w; }
+            if (s < g.world && (need >> s & 1)) { acc.x += y[h][s].x; acc.y += y[h][s].y; acc.z += y[h][s].z; acc.w += y[h][s].w; }
+        if (extra) { acc.x += ye[h].x; acc.y += ye[h].y; acc.z += ye[h].z; acc.w += ye[h].w; }
+        if (x) { acc.x = yx[h].x + acc.x; acc.y = yx[h].y + acc.y; acc.z = yx[h].z + acc.z; acc.w = yx[h].w + acc.w; }
         if (x) *reinterpret_cast<float4*>(x + (size_t)i * EH + k0) = acc;
         if (out) *reinterpret_cast<float4*>(out + (size_t)i * EH + k0) = acc;
         v[4 * h] = acc.x; v[4 * h + 1] = acc.y; v[4 * h + 2] = acc.z; v[4 * h + 3] = acc.w;
