@@ -1019,11 +1019,11 @@ static int tiled_launch_one(moexb_ctx* c, const TiledArgs& a, int T, void* strea
 static int tiled_maxp(const moexb_ctx* c, int fmt, int T) { return (T >= 8 && fmt != FMT_ZP) ? c->pairs_per_pass : 4; }
 // Whether the gate/up kernel can make the work list of this batch itself (tiled.cuh: plan_in_cta).
 // (fp16-scale format: with the wider slices of the other formats the list does not fit beside two CTAs' rings.)
-// With a handful of tokens (2-7) the one-block planning launch is the cheaper of the two on one GPU (measured on the 4-token
-// workload); across GPUs the in-kernel list always wins, because the planning launch would sit behind the wait for the peers.
+// One token on one GPU needs no list (the routing kernel writes the nine one-pair sub-items itself); across GPUs the list is
+// made in the kernel for any batch, because a planning launch would sit behind the wait for the peers.
 static bool plan_in_kernel(const moexb_ctx* c, int fmt, int T, int K, int E, bool ep = false) {
     static const bool on = [] { const char* e = getenv("MOEXB_PLAN_IN_KERNEL"); return !(e && e[0] == '0'); }();
-    return on && fmt == FMT_SYM_F16 && (T >= 8 || ep) && T <= PL_MAX_TOKENS && K <= PL_MAX_K && E <= PL_MAX_E;
+    return on && fmt == FMT_SYM_F16 && (T >= 2 || ep) && T <= PL_MAX_TOKENS && K <= PL_MAX_K && E <= PL_MAX_E;
 }
 
 // The same on blobs in the tiled layout (sub-item slots point into a tiled layer image). plan: null = the list is already
