@@ -140,48 +140,68 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
     pdl_trigger();
     const int ntiles = *a.ntiles * RT;
 
-    for (int tile = blockIdx.x; tile < ntiles && !*s_fail; tile += gridDim.x) {
-        const moexb_pair_item it = a.tiles[tile / RT];
-        const int rt = tile % RT;
-        const int ncol = it.count * a.parts;                 // real activation columns
-        const int N = (ncol + 31) & ~31;                     // MMA N: a multiple of 32, so each column quarter is a multiple of 8
-        const uint32_t idesc = umma_idesc_f16(128, N);
-        const uint8_t* blob = it.slot;
+    // What a tile's copies, MMAs and epilogue need to know. The first groups of the NEXT tile are requested before the epilogue
+    // of the current one (the ring and the activation stages are free by then), so that the start of a tile does not wait for
+    // a memory round trip with nothing else to do; hence two of these are alive at a time.
+    struct Tile {
+        moexb_pair_item it; int rt, ncol, N;
+        const uint16_t* xcol0; const uint16_t* xcol1;   // the thread's two copy units of an activation stage (null = padding column)
+        int d0, d1;                                     // their byte offsets inside a B stage, -1 = none
+    };
+    auto setup = [&](int tile) {
+        Tile p;
+        p.it = a.tiles[tile / RT];
+        p.rt = tile % RT;
+        p.ncol = p.it.count * a.parts;                 // real activation columns
+        p.N = (p.ncol + 31) & ~31;                     // MMA N: a multiple of 32, so each column quarter is a multiple of 8
         // activation rows of this tile's columns: copy unit u = (column c, k-block kb of 8 inputs), N*8 units, threads take
         // u = tid and tid + 512. kb = (u & 1) + 2 * ((u >> 1) / N), c = (u >> 1) % N: a lane pair reads one 32-byte sector of a
         // column, consecutive pairs write consecutive 16-byte rows of the core-matrix layout.
-        const uint16_t* xcol0 = nullptr; const uint16_t* xcol1 = nullptr;
-        int d0 = -1, d1 = -1;  // byte offsets inside a B stage
-        {
-            const int u0 = tid, u1 = tid + PF_THREADS;
-            if (u0 < N * 8) {
-                const int c = (u0 >> 1) % N, kb = (u0 & 1) + 2 * ((u0 >> 1) / N);
-                d0 = kb * (N * 16) + c * 16;
-                if (c < ncol) { const moexb_pair pr = a.pairs[it.start + c / a.parts]; xcol0 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
-            }
-            if (u1 < N * 8) {
-                const int c = (u1 >> 1) % N, kb = (u1 & 1) + 2 * ((u1 >> 1) / N);
-                d1 = kb * (N * 16) + c * 16;
-                if (c < ncol) { const moexb_pair pr = a.pairs[it.start + c / a.parts]; xcol1 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
-            }
+        p.xcol0 = nullptr; p.xcol1 = nullptr; p.d0 = -1; p.d1 = -1;
+        const int N = p.N, u0 = tid, u1 = tid + PF_THREADS;
+        if (u0 < N * 8) {
+            const int c = (u0 >> 1) % N, kb = (u0 & 1) + 2 * ((u0 >> 1) / N);
+            p.d0 = kb * (N * 16) + c * 16;
+            if (c < p.ncol) { const moexb_pair pr = a.pairs[p.it.start + c / a.parts]; p.xcol0 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
         }
+        if (u1 < N * 8) {
+            const int c = (u1 >> 1) % N, kb = (u1 & 1) + 2 * ((u1 >> 1) / N);
+            p.d1 = kb * (N * 16) + c * 16;
+            if (c < p.ncol) { const moexb_pair pr = a.pairs[p.it.start + c / a.parts]; p.xcol1 = a.xs + ((size_t)(DOWN ? pr.p : pr.t) * a.parts + c % a.parts) * KB + kb * 8; }
+        }
+        return p;
+    };
+    // request group G's raw bytes: the thread's unit as two 8-byte pieces, each to its row's 32 bytes of the ring slot
+    // (so that the unpacking reads one row with one 16-byte load), and (one thread per row pair) the pair's two scales
+    auto prefetch = [&](const Tile& p, int G) {
+        const uint8_t* gb = p.it.slot + (size_t)(DOWN ? 256 + 16 * p.rt + cj : (16 * p.rt + cj) * 4 + (G >> 3)) * SB + (G & 7) * GB;
+        uint8_t* slot = sR + (G % PF_RING) * PF_RAW;
+        const uint8_t* src = gb + (4 * cg + ct) * 16;
+        cp_async8(smem_u32(slot + (cj * 16 + cg) * 32 + ct * 8), src);
+        cp_async8(smem_u32(slot + (cj * 16 + cg + 8) * 32 + ct * 8), src + 8);
+        if (ct == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slot + 8192 + (cj * 8 + cg) * 4)), "l"(gb + 512 + 4 * cg) : "memory");
+    };
+    // request group G's activation rows into B stage G % 3
+    auto fill_b = [&](const Tile& p, int G) {
+        uint8_t* bb = sB + (G % 3) * PF_B_STAGE;
+        if (p.d0 >= 0) { if (p.xcol0) cp_async16(smem_u32(bb + p.d0), p.xcol0 + G * 64); else *reinterpret_cast<uint4*>(bb + p.d0) = make_uint4(0, 0, 0, 0); }
+        if (p.d1 >= 0) { if (p.xcol1) cp_async16(smem_u32(bb + p.d1), p.xcol1 + G * 64); else *reinterpret_cast<uint4*>(bb + p.d1) = make_uint4(0, 0, 0, 0); }
+    };
+    // the first copies of a tile: raw groups 0..AHEAD and the activation rows of groups 0 and 1
+    auto prime = [&](const Tile& p) {
+        for (int G = 0; G <= PF_AHEAD && G < NG; G++) prefetch(p, G);
+        fill_b(p, 0); fill_b(p, 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
 
-        // request group G's raw bytes: the thread's unit as two 8-byte pieces, each to its row's 32 bytes of the ring slot
-        // (so that the unpacking reads one row with one 16-byte load), and (one thread per row pair) the pair's two scales
-        auto prefetch = [&](int G) {
-            const uint8_t* gb = blob + (size_t)(DOWN ? 256 + 16 * rt + cj : (16 * rt + cj) * 4 + (G >> 3)) * SB + (G & 7) * GB;
-            uint8_t* slot = sR + (G % PF_RING) * PF_RAW;
-            const uint8_t* src = gb + (4 * cg + ct) * 16;
-            cp_async8(smem_u32(slot + (cj * 16 + cg) * 32 + ct * 8), src);
-            cp_async8(smem_u32(slot + (cj * 16 + cg + 8) * 32 + ct * 8), src + 8);
-            if (ct == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(slot + 8192 + (cj * 8 + cg) * 4)), "l"(gb + 512 + 4 * cg) : "memory");
-        };
-        // request group G's activation rows into B stage G % 3
-        auto fill_b = [&](int G) {
-            uint8_t* bb = sB + (G % 3) * PF_B_STAGE;
-            if (d0 >= 0) { if (xcol0) cp_async16(smem_u32(bb + d0), xcol0 + G * 64); else *reinterpret_cast<uint4*>(bb + d0) = make_uint4(0, 0, 0, 0); }
-            if (d1 >= 0) { if (xcol1) cp_async16(smem_u32(bb + d1), xcol1 + G * 64); else *reinterpret_cast<uint4*>(bb + d1) = make_uint4(0, 0, 0, 0); }
-        };
+    Tile cur;
+    bool primed = false;   // the copies of `cur` have been requested already (during the epilogue of the tile before)
+    for (int tile = blockIdx.x; tile < ntiles && !*s_fail; tile += gridDim.x) {
+        if (!primed) cur = setup(tile);
+        const moexb_pair_item it = cur.it;
+        const int rt = cur.rt, N = cur.N;
+        const uint32_t idesc = umma_idesc_f16(128, N);
+
         // unpack 32 weights of this thread's row of group G (the raw bytes have landed and are visible) into A stage G & 1 in
         // tensor memory: nh = -fp16(q*s) (the MMA negates it back) and lo = q*s + nh, two fp16 per column
         auto unpack = [&](int G) {
@@ -226,9 +246,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
 
         __syncthreads();  // the previous tile's readers are done with the B stages, the ring and TMEM
         // prologue: raw groups 0..AHEAD and activations of groups 0, 1 on their way; group 0 unpacked and issued
-        for (int G = 0; G <= PF_AHEAD && G < NG; G++) prefetch(G);
-        fill_b(0); fill_b(1);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (!primed) prime(cur);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();  // every thread's copies have landed: the rows are read by other threads than copied them
@@ -240,9 +258,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
             // group G is on the tensor core. Meanwhile: unpack group G+1 (visible since the previous barrier), request what
             // comes later, and make sure that everything requested before this iteration has landed before the next barrier.
             if (G >= 1) wait_mma(G - 1);   // frees A stage (G+1)&1 and B stage (G+2)%3
-            if (G + 2 < NG) fill_b(G + 2);
+            if (G + 2 < NG) fill_b(cur, G + 2);
             asm volatile("cp.async.commit_group;" ::: "memory");
-            if (G + 1 + PF_AHEAD < NG) prefetch(G + 1 + PF_AHEAD);
+            if (G + 1 + PF_AHEAD < NG) prefetch(cur, G + 1 + PF_AHEAD);
             asm volatile("cp.async.commit_group;" ::: "memory");
             if (G + 1 < NG) unpack(G + 1);
             asm volatile("cp.async.wait_group 2;" ::: "memory");
@@ -254,7 +272,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
         }
         if (*s_fail) break;
         wait_mma(NG - 1);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // every MMA of this tile is done and every raw group unpacked: the ring and the activation stages are free, and the
+        // next tile's first copies travel while this tile's sums are read out and stored
+        primed = false;
+        Tile nxt = cur;
+        if (!*s_fail && tile + (int)gridDim.x < ntiles) { nxt = setup(tile + gridDim.x); prime(nxt); primed = true; }
 
         // epilogue. The thread reads row ui of both halves, columns ecq*N/4 .. +N/4-1, 8 at a time.
         const int cbase = ecq * (N >> 2);
@@ -291,7 +313,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        cur = nxt;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");   // none of this thread's copies is in flight when the CTA leaves
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(PF_TMEM_COLS) : "memory");
