@@ -254,6 +254,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_k(const PrefillArgs a) 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if ((tid & ~32) == 0) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue(0, tid >> 5); }
+#pragma unroll 8
         for (int G = 0; G < NG; G++) {
             // group G is on the tensor core. Meanwhile: unpack group G+1 (visible since the previous barrier), request what
             // comes later, and make sure that everything requested before this iteration has landed before the next barrier.
